@@ -1,0 +1,471 @@
+// scaled_mm for sm_100a: C[M,N] = cast(cast((A[M,K] @ upcast(B)) * scale) + bias)
+//
+//   A     fp16 or bf16, row-major, K contiguous
+//   B     fp8 (e5m2 or e4m3fn), prepacked as [K_pad/16][N][16] bytes: the 16 bytes of one (k16, n) cell are the
+//         sixteen consecutive k of column n, and K is zero padded to a multiple of 128
+//   C     fp16 or bf16, row-major
+//
+// This is the B200 counterpart of `scaled_mm_kernel` / `launch_scaled_mm` in the reference's
+// csrc/hip_kernel.cu (kernel :148-572, C ABI :687-713). Same contract, different machine:
+//
+//   * one persistent CTA per SM walks 128 x BN output tiles (m fastest so concurrently running CTAs share
+//     a weight panel in L2);
+//   * warp 0 is the TMA producer: per 64-wide k block it brings a 128 x 64 activation tile (128-byte
+//     swizzle, zero fill past M and K) and the raw fp8 cells [4][BN][16] into a ring of load slots;
+//   * eight upcast warps turn the raw cells into a K-major, 128-byte swizzled fp16 operand tile
+//     (e5m2 -> fp16 is a byte placement, e4m3 -> fp16 one cvt per pair; both exact for every code)
+//     in a second, shorter ring, fence it for the async proxy and hand it to the MMA warp;
+//   * one thread of warp 1 issues tcgen05.mma kind::f16 (M=128, N=BN, K=16) into one of two TMEM
+//     accumulators and commits to the barriers that recycle the slots;
+//   * four epilogue warps read the finished accumulator (thread = output row), apply the scale, round,
+//     add the bias in the output dtype, round again and store 64 contiguous bytes per thread per
+//     32-column step, while the MMA warp already fills the other accumulator.
+//
+// The UMMA wants both operands in one 16-bit format (a bf16 x fp16 instruction descriptor is rejected as an
+// illegal instruction), so the weights are decoded to the activation's format: fp16 by byte placement,
+// bf16 through an exact fp16 -> fp32 -> bf16 conversion. Nothing is rounded before the fp32 accumulation.
+#include "feather_host.h"
+#include "feather_tiles_gen.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace feather {
+namespace smm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;            // one 128-byte swizzle span of 16-bit elements
+constexpr int kSlabsPerBlock = kBlockK / 16;
+constexpr int kLoadStages = 4;
+constexpr int kOperandStages = 2;
+constexpr int kUpcastWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kFirstEpilogueWarp = 2;
+constexpr int kFirstUpcastWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstUpcastWarp + kUpcastWarps);
+constexpr int kATileBytes = kBlockM * kBlockK * 2;
+
+__device__ uint32_t g_status[2];
+
+struct Params {
+    const float* scale;
+    const uint16_t* bias;
+    uint16_t* c;
+    int M;
+    int N;
+    int K;
+    int tiles_m;
+    int tiles_n;
+    uint32_t idesc;
+    int bias_vec;  // bias pointer is 16-byte aligned
+};
+
+template <int BN>
+struct Smem {
+    static constexpr int kRawBytes = kSlabsPerBlock * BN * 16;
+    static constexpr int kOperandBytes = BN * 128;
+    static constexpr int kAOff = 0;
+    static constexpr int kOperandOff = kAOff + kLoadStages * kATileBytes;
+    static constexpr int kRawOff = kOperandOff + kOperandStages * kOperandBytes;
+    static constexpr int kBarOff = kRawOff + kLoadStages * kRawBytes;
+    // load full/empty, operand full/empty, tmem full/empty
+    static constexpr int kNumBars = 2 * kLoadStages + 2 * kOperandStages + 4;
+    static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;  // slack for the 1024-byte alignment of the base
+};
+
+struct Ring {
+    uint32_t idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(uint32_t depth) {
+        if (++idx == depth) {
+            idx = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+// Two fp8 bytes -> two fp16 in one register. `kE5M2`: the byte is the high byte of the fp16 pattern.
+template <bool kE5M2>
+__device__ __forceinline__ void fp8x4_to_f16x4(uint32_t p, uint32_t& lo, uint32_t& hi) {
+    if constexpr (kE5M2) {
+        lo = __byte_perm(p, 0u, 0x1404u);
+        hi = __byte_perm(p, 0u, 0x3424u);
+    } else {
+        const __half2_raw l = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(p & 0xffffu), __NV_E4M3);
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(p >> 16), __NV_E4M3);
+        lo = static_cast<uint32_t>(l.x) | (static_cast<uint32_t>(l.y) << 16);
+        hi = static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+    }
+}
+
+// fp16 pair -> bf16 pair, exact for every value an fp8 code can take (used only when the activation and
+// weight operand formats have to match).
+__device__ __forceinline__ uint32_t f16x2_to_bf16x2(uint32_t v) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&v);
+    const float2 f = __half22float2(h);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+template <bool kOutBf16>
+__device__ __forceinline__ uint32_t pack_out(float a, float b) {
+    if constexpr (kOutBf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
+template <bool kOutBf16>
+__device__ __forceinline__ float2 unpack_out(uint32_t v) {
+    if constexpr (kOutBf16) {
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+    } else {
+        return __half22float2(*reinterpret_cast<const __half2*>(&v));
+    }
+}
+
+template <int BN, bool kE5M2, bool kOperandBf16, bool kOutBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    using L = Smem<BN>;
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint64_t* const load_full = bars;
+    uint64_t* const load_empty = load_full + kLoadStages;
+    uint64_t* const operand_full = load_empty + kLoadStages;
+    uint64_t* const operand_empty = operand_full + kOperandStages;
+    uint64_t* const tmem_full = operand_empty + kOperandStages;
+    uint64_t* const tmem_empty = tmem_full + 2;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kLoadStages; ++s) {
+            mbar_init(&load_full[s], 1);
+            mbar_init(&load_empty[s], 1);
+        }
+        for (int s = 0; s < kOperandStages; ++s) {
+            mbar_init(&operand_full[s], kUpcastWarps);
+            mbar_init(&operand_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            Ring slot;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                const int m0 = (tile % p.tiles_m) * kBlockM;
+                const int n0 = (tile / p.tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
+                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
+                    tma_load_3d(smem + L::kRawOff + slot.idx * L::kRawBytes, &map_b, &load_full[slot.idx], 0, n0, kb * kSlabsPerBlock);
+                    slot.advance(kLoadStages);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            Ring slot, operand, acc;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                ok = guard.wait(&tmem_empty[acc.idx], acc.phase ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc.idx * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 1) &&
+                         guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
+                    const uint32_t b_addr = smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        umma_f16(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
+                                 (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&load_empty[slot.idx]);
+                    umma_commit(&operand_empty[operand.idx]);
+                    slot.advance(kLoadStages);
+                    operand.advance(kOperandStages);
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full[acc.idx]);
+                acc.advance(2);
+            }
+        }
+    } else if (warp < kFirstUpcastWarp) {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp % 4;  // the TMEM lane quarter this warp is allowed to read
+        const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+        Ring acc;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            const int m0 = (tile % p.tiles_m) * kBlockM;
+            const int n0 = (tile / p.tiles_m) * BN;
+            ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * BN;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_wait_ld();
+                if (c == BN / 32 - 1) {
+                    // the accumulator is in registers: hand the TMEM buffer back before the stores
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
+                }
+                const int col0 = n0 + c * 32;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int col = col0 + g * 8;
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        o[i] = pack_out<kOutBf16>(__uint_as_float(v[g * 8 + 2 * i]) * scale, __uint_as_float(v[g * 8 + 2 * i + 1]) * scale);
+                    }
+                    if (p.bias != nullptr && col < p.N) {
+                        uint32_t bw[4];
+                        if (p.bias_vec) {
+                            const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                            bw[0] = b4.x;
+                            bw[1] = b4.y;
+                            bw[2] = b4.z;
+                            bw[3] = b4.w;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                bw[i] = static_cast<uint32_t>(__ldg(p.bias + col + 2 * i)) | (static_cast<uint32_t>(__ldg(p.bias + col + 2 * i + 1)) << 16);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 x = unpack_out<kOutBf16>(o[i]);
+                            const float2 b = unpack_out<kOutBf16>(bw[i]);
+                            o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
+                        }
+                    }
+                    if (row < p.M && col < p.N) {
+                        *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            acc.advance(2);
+        }
+    } else {
+        // ------------------------------------------------------------------ upcast warps
+        const int t = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
+        constexpr int kRowGroups = (kUpcastWarps * 32) / BN;            // threads sharing one row
+        constexpr int kSlabsPerThread = kSlabsPerBlock / kRowGroups;
+        static_assert(kRowGroups >= 1 && kSlabsPerThread >= 1, "tile too narrow for the upcast warp layout");
+        const int row = t % BN;
+        const int first_slab = (t / BN) * kSlabsPerThread;
+        Ring slot, operand;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                     guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                if (!ok) break;
+                const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                uint4 cells[kSlabsPerThread];
+#pragma unroll
+                for (int j = 0; j < kSlabsPerThread; ++j) {
+                    cells[j] = *reinterpret_cast<const uint4*>(raw + ((first_slab + j) * BN + row) * 16);
+                }
+#pragma unroll
+                for (int j = 0; j < kSlabsPerThread; ++j) {
+                    const uint32_t w[4] = {cells[j].x, cells[j].y, cells[j].z, cells[j].w};
+                    uint32_t h[8];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        fp8x4_to_f16x4<kE5M2>(w[i], h[2 * i], h[2 * i + 1]);
+                        if constexpr (kOperandBf16) {
+                            h[2 * i] = f16x2_to_bf16x2(h[2 * i]);
+                            h[2 * i + 1] = f16x2_to_bf16x2(h[2 * i + 1]);
+                        }
+                    }
+                    const int chunk = 2 * (first_slab + j);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, chunk)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, chunk + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&operand_full[operand.idx]);
+                slot.advance(kLoadStages);
+                operand.advance(kOperandStages);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        // give copies and MMAs that were in flight when a wait ran out time to land before the CTA's
+        // shared and tensor memory go away
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+struct LaunchArgs {
+    const uint16_t* a;
+    const uint8_t* b;
+    const float* scale;
+    const uint16_t* bias;
+    uint16_t* c;
+    int64_t M, N, K;
+    bool e5m2, a_bf16, out_bf16;
+    cudaStream_t stream;
+};
+
+template <int BN, bool kE5M2, bool kOperandBf16, bool kOutBf16>
+bool launch_instance(const LaunchArgs& args) {
+    using L = Smem<BN>;
+    auto* kernel = &scaled_mm_kernel<BN, kE5M2, kOperandBf16, kOutBf16>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+
+    CUtensorMap map_a, map_b;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.K) * 2};
+        const uint32_t box[2] = {kBlockK, kBlockM};
+        if (!encode_map(&map_a, args.a_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.a, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B)) {
+            return false;
+        }
+    }
+    {
+        const uint64_t k16_rows = static_cast<uint64_t>((args.K + 127) / 128) * 8;  // the prepack pads K to 128
+        const uint64_t dims[3] = {16, static_cast<uint64_t>(args.N), k16_rows};
+        const uint64_t strides[2] = {16, static_cast<uint64_t>(args.N) * 16};
+        const uint32_t box[3] = {16, BN, kSlabsPerBlock};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    }
+
+    Params p{};
+    p.scale = args.scale;
+    p.bias = args.bias;
+    p.c = args.c;
+    p.M = static_cast<int>(args.M);
+    p.N = static_cast<int>(args.N);
+    p.K = static_cast<int>(args.K);
+    p.tiles_m = static_cast<int>((args.M + kBlockM - 1) / kBlockM);
+    p.tiles_n = static_cast<int>((args.N + BN - 1) / BN);
+    p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, kBlockM, BN);
+    p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int sms = device_info().sm_count;
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+template <int BN>
+bool launch_for_block_n(const LaunchArgs& args) {
+    const bool operand_bf16 = args.a_bf16;  // the weights are decoded to the activation's format
+#define FEATHER_SMM_CASE(E5, OB, OUT)                                      \
+    if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
+        return launch_instance<BN, E5, OB, OUT>(args);                      \
+    }
+    FEATHER_SMM_CASE(true, false, true)
+    FEATHER_SMM_CASE(true, false, false)
+    FEATHER_SMM_CASE(false, false, true)
+    FEATHER_SMM_CASE(false, false, false)
+    FEATHER_SMM_CASE(true, true, true)
+    FEATHER_SMM_CASE(true, true, false)
+    FEATHER_SMM_CASE(false, true, true)
+    FEATHER_SMM_CASE(false, true, false)
+#undef FEATHER_SMM_CASE
+    return false;
+}
+
+}  // namespace smm
+}  // namespace feather
+
+// C ABI, same signature as the reference's `launch_scaled_mm` (csrc/hip_kernel.cu:687-713) with a CUDA
+// stream. The six tile integers are the reference's `(warps_m, warps_n, unroll_k, repeat_m, repeat_n,
+// prefetch)` tuple: it must be a row of the tile table, and its `16 * warps_n * repeat_n` width picks the
+// UMMA tile width. Returns false for an unknown tuple or unsupported shape; never synchronizes.
+extern "C" bool launch_scaled_mm(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
+                                 int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
+                                 bool output_bf16, int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n,
+                                 bool prefetch, cudaStream_t stream) {
+    using namespace feather;
+    const int block_n = scaled_mm_tile_block_n(block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n, prefetch ? 1 : 0);
+    if (block_n == 0) return false;
+    if (M < 0 || N <= 0 || K <= 0 || N % 16 != 0 || K % 16 != 0) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+    if (M == 0) return true;
+    const smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
+                               use_fp8_e5m2, a_bf16, output_bf16, stream};
+    if (block_n >= 256) return smm::launch_for_block_n<256>(args);
+    if (block_n >= 128) return smm::launch_for_block_n<128>(args);
+    return smm::launch_for_block_n<64>(args);
+}
+
+// Reads (and clears) the status record the kernel's bounded waits report into: out[0] = wait site
+// (0 = every wait completed) | tag << 8, out[1] = block index. Synchronizes the device.
+extern "C" int feather_scaled_mm_status(uint32_t* out) {
+    uint32_t zero[2] = {0u, 0u};
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    if (cudaMemcpyFromSymbol(out, feather::smm::g_status, sizeof(zero)) != cudaSuccess) return 1;
+    if (cudaMemcpyToSymbol(feather::smm::g_status, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}
