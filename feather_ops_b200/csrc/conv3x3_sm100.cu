@@ -1,0 +1,438 @@
+// 3x3, stride 1, padding 1, NCHW conv2d (fp16 / bf16) for sm_100a as an implicit GEMM on tcgen05.
+//
+// GEMM view, as in the reference (csrc/hip_conv2d_3x3.cu:1-26): M = C_out, N = pixels, K = 9 * C_in with
+// the contraction ordered (16-channel group, tap, channel % 16). The weight is the reference's prepack
+// [ceil(C_in / 16) * 18][C_out][8]: row g * 18 + tap * 2 + half holds, per output channel, eight
+// consecutive input channels, i.e. one 16-byte K-major core-matrix row. B200 counterpart of
+// `conv3x3_kernel` / `feather_conv3x3_launch` (kernel :100-476, C ABI :561-575).
+//
+// One persistent CTA per SM walks tiles of 128 output channels x (rows x BN) pixels, one launch for the
+// whole batch. Per 16-channel group (one pipeline slot):
+//   * warp 0 (TMA): the group's 18 weight rows x 128 channels land as [18][128][16 B], which already is
+//     the no-swizzle K-major UMMA layout (8-channel core matrices 128 B apart, K-adjacent ones 2 KB apart).
+//     Output channels past C_out are zero filled by the TMA unit.
+//   * sixteen gather warps in two alternating teams: read the (rows + 2) x (BN + 2) halo tile of the
+//     group's 16 input channels straight from global memory, interleave eight channels per pixel and
+//     store [plane][halo row][halo col][8 channels]. A pixel is one 16-byte record, so eight consecutive
+//     pixels are a core matrix and tap (kh, kw) of output row r is nothing but a start-address offset of
+//     ((r + kh) * (BN + 2) + kw) records. Out-of-image pixels and channels past C_in are written as zeros,
+//     which is the padding.
+//   * warp 1: one thread issues 9 x rows tcgen05.mma kind::f16 (M = 128, N = BN, K = 16) per group into
+//     one of two fp32 TMEM accumulators (k order: groups ascending, taps 0..8 inside, as the reference).
+//   * four epilogue warps: TMEM lane = output channel, columns = consecutive pixels of one output row;
+//     add the bias in fp32, round once, 64-byte contiguous NCHW stores.
+#include "feather_host.h"
+#include "feather_tiles_gen.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace feather {
+namespace conv {
+
+constexpr int kBlockM = 128;
+constexpr int kStages = 3;
+constexpr int kTeamWarps = 8;
+constexpr int kTeams = 2;
+constexpr int kEpilogueWarps = 4;
+constexpr int kFirstEpilogueWarp = 2;
+constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstGatherWarp + kTeams * kTeamWarps);
+constexpr int kWeightRows = 18;                                  // 9 taps x 2 eight-channel halves
+constexpr int kWeightStageBytes = kWeightRows * kBlockM * 16;    // 36864
+constexpr int kMaxItems = 4;                                     // pixel-pair gather items per thread per slot
+constexpr int kAccColumns = 256;                                 // TMEM columns per accumulator buffer
+
+__device__ uint32_t g_status[2];
+
+struct Params {
+    const uint16_t* x;
+    const uint16_t* bias;
+    uint16_t* y;
+    int B, C_in, C_out, H, W;
+    int groups;       // ceil(C_in / 16)
+    int bn;           // pixels per output row segment (UMMA N): 64, 128 or 256
+    int rows;         // output rows per tile: 1 or 2
+    int tiles_m, tiles_w, tiles_h;
+    int act_stage_bytes;
+    uint32_t idesc;
+    int pairs;        // W is even: gather two pixels per 4-byte load
+};
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_out(float a, float b) {
+    if constexpr (kBf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ float bits_to_float(uint16_t bits) {
+    if constexpr (kBf16) {
+        return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    } else {
+        return __half2float(__ushort_as_half(bits));
+    }
+}
+
+struct TileCoord {
+    int b, m0, h0, w0;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(const Params& p, int tile) {
+    TileCoord t;
+    t.m0 = (tile % p.tiles_m) * kBlockM;
+    tile /= p.tiles_m;
+    t.w0 = (tile % p.tiles_w) * p.bn;
+    tile /= p.tiles_w;
+    t.h0 = (tile % p.tiles_h) * p.rows;
+    t.b = tile / p.tiles_h;
+    return t;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* const weight_smem = smem;
+    uint8_t* const act_smem = smem + kStages * kWeightStageBytes;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(act_smem + kStages * p.act_stage_bytes);
+    uint64_t* const weight_full = bars;
+    uint64_t* const act_full = weight_full + kStages;
+    uint64_t* const stage_empty = act_full + kStages;
+    uint64_t* const tmem_full = stage_empty + kStages;
+    uint64_t* const tmem_empty = tmem_full + 2;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&weight_full[s], 1);
+            mbar_init(&act_full[s], kTeamWarps);
+            mbar_init(&stage_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * kAccColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.B * p.tiles_m * p.tiles_h * p.tiles_w;
+    const int halo_cols = p.bn + 2;
+    const int halo_rows = p.rows + 2;
+    const int plane_bytes = halo_rows * halo_cols * 16;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (weights)
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                const TileCoord tc = tile_coord(p, tile);
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t phase = (it / kStages) & 1u;
+                    ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes);
+                    tma_load_3d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], 0, tc.m0, g * kWeightRows);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            uint32_t it = 0;
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x), ++acc_it) {
+                const uint32_t acc = acc_it & 1u;
+                ok = guard.wait(&tmem_empty[acc], ((acc_it >> 1) & 1u) ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc * kAccColumns;
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    const uint32_t s = it % kStages;
+                    const uint32_t phase = (it / kStages) & 1u;
+                    ok = guard.wait(&weight_full[s], phase, kSiteLoadFull) && guard.wait(&act_full[s], phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t w_addr = smem_u32(weight_smem + s * kWeightStageBytes);
+                    const uint32_t x_addr = smem_u32(act_smem + s * p.act_stage_bytes);
+#pragma unroll 1
+                    for (int tap = 0; tap < 9; ++tap) {
+                        const int kh = tap / 3;
+                        const int kw = tap % 3;
+                        const uint64_t desc_w = make_smem_desc(w_addr + tap * 2 * (kBlockM * 16), kBlockM * 16, 128, kSwizzleNone);
+                        for (int r = 0; r < p.rows; ++r) {
+                            const uint64_t desc_x = make_smem_desc(x_addr + ((r + kh) * halo_cols + kw) * 16, plane_bytes, 128, kSwizzleNone);
+                            umma_f16(tmem_d + r * p.bn, desc_w, desc_x, p.idesc, (g | tap) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&stage_empty[s]);
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full[acc]);
+            }
+        }
+    } else if (warp < kFirstGatherWarp) {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp % 4;
+        const bool vector_rows = (p.W % 8) == 0;
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x), ++acc_it) {
+            const TileCoord tc = tile_coord(p, tile);
+            const uint32_t acc = acc_it & 1u;
+            ok = guard.wait(&tmem_full[acc], (acc_it >> 1) & 1u, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int co = tc.m0 + quarter * 32 + lane;
+            const bool co_live = co < p.C_out;
+            const float bias = (p.bias != nullptr && co_live) ? bits_to_float<kBf16>(__ldg(p.bias + co)) : 0.0f;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccColumns;
+            const int chunks = p.bn / 32;
+            for (int r = 0; r < p.rows; ++r) {
+                const int h = tc.h0 + r;
+                uint16_t* const y_row = p.y + ((static_cast<int64_t>(tc.b) * p.C_out + (co_live ? co : 0)) * p.H + (h < p.H ? h : 0)) * p.W;
+#pragma unroll 1
+                for (int c = 0; c < chunks; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + r * p.bn + c * 32, v);
+                    tmem_wait_ld();
+                    if (r == p.rows - 1 && c == chunks - 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+                    }
+                    if (!co_live || h >= p.H) continue;
+                    const int w_first = tc.w0 + c * 32;
+                    if (vector_rows) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (w_first + g * 8 < p.W) {
+                                uint32_t o[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    o[i] = pack_out<kBf16>(__uint_as_float(v[g * 8 + 2 * i]) + bias, __uint_as_float(v[g * 8 + 2 * i + 1]) + bias);
+                                }
+                                *reinterpret_cast<uint4*>(y_row + w_first + g * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (w_first + i < p.W) {
+                                const uint32_t o = pack_out<kBf16>(__uint_as_float(v[i]) + bias, 0.0f);
+                                y_row[w_first + i] = static_cast<uint16_t>(o & 0xffffu);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ activation gather warps
+        const int team = (warp - kFirstGatherWarp) / kTeamWarps;
+        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kTeamWarps) * 32;
+        constexpr int kTeamThreads = kTeamWarps * 32;
+        const int64_t hw = static_cast<int64_t>(p.H) * p.W;
+        // Work items of one slot. With `pairs`: per (plane, halo row) the halo columns 1..BN as BN / 2 aligned
+        // pixel pairs, then the two edge columns 0 and BN + 1 as single pixels. Without: every column alone.
+        const int per_row = p.pairs ? p.bn / 2 + 2 : halo_cols;
+        const int items = 2 * halo_rows * per_row;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            const TileCoord tc = tile_coord(p, tile);
+            const uint16_t* const x_img = p.x + static_cast<int64_t>(tc.b) * p.C_in * hw;
+            for (int g = 0; g < p.groups; ++g, ++it) {
+                if (static_cast<int>(it & 1u) != team) continue;
+                const uint32_t s = it % kStages;
+                const uint32_t phase = (it / kStages) & 1u;
+                // issue every load of this thread's items first, so they are all in flight together
+                uint32_t v[kMaxItems][8];
+                int dst_off[kMaxItems];
+                int kind[kMaxItems];  // 0 = nothing, 1 = single pixel, 2 = pixel pair
+#pragma unroll
+                for (int j = 0; j < kMaxItems; ++j) {
+                    const int item = t + j * kTeamThreads;
+                    kind[j] = 0;
+                    dst_off[j] = 0;
+                    if (item < items) {
+                        const int plane = item / (halo_rows * per_row);
+                        const int rem = item % (halo_rows * per_row);
+                        const int hr = rem / per_row;
+                        const int e = rem % per_row;
+                        int hc;       // first halo column of the item
+                        bool pair;
+                        if (p.pairs) {
+                            pair = e < p.bn / 2;
+                            hc = pair ? 1 + 2 * e : (e == p.bn / 2 ? 0 : p.bn + 1);
+                        } else {
+                            pair = false;
+                            hc = e;
+                        }
+                        const int h = tc.h0 - 1 + hr;
+                        const int w = tc.w0 - 1 + hc;
+                        const bool in_image = h >= 0 && h < p.H && w >= 0 && w < p.W;
+                        const int c_first = g * 16 + plane * 8;
+                        const uint16_t* const src = x_img + static_cast<int64_t>(c_first) * hw + static_cast<int64_t>(in_image ? h : 0) * p.W + (in_image ? w : 0);
+                        kind[j] = pair ? 2 : 1;
+                        dst_off[j] = plane * plane_bytes + (hr * halo_cols + hc) * 16;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const bool live = in_image && c_first + c < p.C_in;
+                            if (pair) {
+                                v[j][c] = live ? __ldg(reinterpret_cast<const uint32_t*>(src + c * hw)) : 0u;
+                            } else {
+                                v[j][c] = live ? static_cast<uint32_t>(__ldg(src + c * hw)) : 0u;
+                            }
+                        }
+                    }
+                }
+                ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteOperandEmpty);
+                if (!ok) break;
+                uint8_t* const dst = act_smem + s * p.act_stage_bytes;
+#pragma unroll
+                for (int j = 0; j < kMaxItems; ++j) {
+                    if (kind[j] == 0) continue;
+                    // low halves = this pixel (the only one of a single), high halves = the pair's second pixel
+                    const uint4 first = make_uint4(__byte_perm(v[j][0], v[j][1], 0x5410u), __byte_perm(v[j][2], v[j][3], 0x5410u),
+                                                   __byte_perm(v[j][4], v[j][5], 0x5410u), __byte_perm(v[j][6], v[j][7], 0x5410u));
+                    *reinterpret_cast<uint4*>(dst + dst_off[j]) = first;
+                    if (kind[j] == 2) {
+                        const uint4 second = make_uint4(__byte_perm(v[j][0], v[j][1], 0x7632u), __byte_perm(v[j][2], v[j][3], 0x7632u),
+                                                        __byte_perm(v[j][4], v[j][5], 0x7632u), __byte_perm(v[j][6], v[j][7], 0x7632u));
+                        *reinterpret_cast<uint4*>(dst + dst_off[j] + 16) = second;
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&act_full[s]);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * kAccColumns);
+    }
+}
+
+template <bool kBf16>
+int launch(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W, int bn, int rows,
+           cudaStream_t stream) {
+    auto* kernel = &conv3x3_kernel<kBf16>;
+    Params p{};
+    p.x = static_cast<const uint16_t*>(x);
+    p.bias = static_cast<const uint16_t*>(bias);
+    p.y = static_cast<uint16_t*>(y);
+    p.B = B;
+    p.C_in = C_in;
+    p.C_out = C_out;
+    p.H = H;
+    p.W = W;
+    p.groups = (C_in + 15) / 16;
+    p.bn = bn;
+    p.rows = rows;
+    p.tiles_m = (C_out + kBlockM - 1) / kBlockM;
+    p.tiles_w = (W + bn - 1) / bn;
+    p.tiles_h = (H + rows - 1) / rows;
+    p.act_stage_bytes = ((2 * (rows + 2) * (bn + 2) * 16) + 127) / 128 * 128;
+    p.idesc = make_idesc(kAccF32, kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16, kBlockM, bn);
+    p.pairs = (W % 2 == 0) ? 1 : 0;
+    const int per_row = p.pairs ? bn / 2 + 2 : bn + 2;
+    if (2 * (rows + 2) * per_row > kMaxItems * kTeamWarps * 32) return 1;
+
+    const int smem_bytes = kStages * (kWeightStageBytes + p.act_stage_bytes) + (3 * kStages + 4) * 8 + 16 + 1024;
+    static int configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && configured[dev] < smem_bytes) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 1;
+        configured[dev] = smem_bytes;
+    }
+
+    CUtensorMap map_w;
+    const uint64_t dims[3] = {8, static_cast<uint64_t>(C_out), static_cast<uint64_t>(p.groups) * kWeightRows};
+    const uint64_t strides[2] = {16, static_cast<uint64_t>(C_out) * 16};
+    const uint32_t box[3] = {8, kBlockM, kWeightRows};
+    if (!encode_map(&map_w, kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, wp, dims, strides, box,
+                    CU_TENSOR_MAP_SWIZZLE_NONE)) {
+        return 1;
+    }
+    const int64_t num_tiles = static_cast<int64_t>(B) * p.tiles_m * p.tiles_h * p.tiles_w;
+    if (num_tiles > (1ll << 30)) return 1;
+    const int sms = device_info().sm_count;
+    const int grid = num_tiles < sms ? static_cast<int>(num_tiles) : sms;
+    kernel<<<grid, kThreads, smem_bytes, stream>>>(map_w, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+}  // namespace conv
+}  // namespace feather
+
+// C ABI, same signature as the reference's `feather_conv3x3_launch` (csrc/hip_conv2d_3x3.cu:561-575).
+// x: [B, C_in, H, W]; wp: prepacked weight [ceil(C_in / 16) * 18, C_out, 8]; bias: [C_out] or NULL;
+// y: [B, C_out, H, W]; all in one 16-bit dtype (is_bf16), contiguous, 16-byte aligned; C_in % 8 == 0.
+// `(warps_m, warps_n, repeat_m, repeat_n, rows)` must be a row of the conv tile table: its
+// `16 * warps_n * repeat_n` picks the pixel-segment width and `rows` the rows per tile. `prefetch` is
+// accepted and ignored (the pipeline always runs ahead). Returns 0 on success, 1 for an unknown tile, a
+// two-row tile with an odd W, or an unsupported shape.
+extern "C" int feather_conv3x3_launch(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W,
+                                      int has_bias, int warps_m, int warps_n, int repeat_m, int repeat_n, int rows, int is_bf16,
+                                      int prefetch, void* stream_ptr) {
+    using namespace feather;
+    (void)prefetch;
+    if (!conv_tile_known(warps_m, warps_n, repeat_m, repeat_n, rows)) return 1;
+    if (rows == 2 && (W & 1) != 0) return 1;
+    if (B < 0 || C_in <= 0 || C_out <= 0 || H <= 0 || W <= 0 || C_in % 8 != 0) return 1;
+    if (B == 0) return 0;
+    const int block_n = 16 * warps_n * repeat_n;
+    int bn = block_n <= 64 ? 64 : block_n <= 128 ? 128 : 256;
+    if (rows == 2 && bn == 256) bn = 128;  // two rows of 256 pixels do not fit one accumulator buffer
+    if ((W & 1) != 0 && bn == 256) bn = 128;  // odd widths gather pixel by pixel: keep the item count per thread bounded
+    const cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+    const void* const bias_ptr = has_bias ? bias : nullptr;
+    return is_bf16 != 0 ? conv::launch<true>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, bn, rows, stream)
+                        : conv::launch<false>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, bn, rows, stream);
+}
+
+// Reads and clears the conv kernel's wait-status record (see feather_scaled_mm_status).
+extern "C" int feather_conv3x3_status(uint32_t* out) {
+    uint32_t zero[2] = {0u, 0u};
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    if (cudaMemcpyFromSymbol(out, feather::conv::g_status, sizeof(zero)) != cudaSuccess) return 1;
+    if (cudaMemcpyToSymbol(feather::conv::g_status, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}

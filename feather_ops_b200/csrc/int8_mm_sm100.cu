@@ -1,0 +1,502 @@
+// int8 ConvRot GEMM for sm_100a, both directions over one prepacked weight:
+//
+//   forward   C[M, N] = A[M, K] @ W[N, K]^T,  out = cast(float(acc) * a_scale[m] * w_scale[n] + bias[n])
+//   backward  C[M, K] = A[M, N] @ W[N, K],    out = cast(float(acc) * a_scale[m])      (`transposed_b`)
+//
+// The weight is the reference's 4x4 byte micro-tile prepack: micro-tile (k4, n4) is 16 bytes, byte
+// (n % 4) * 4 + (k % 4) holds W[n][k], and micro-tile (k4, n4) sits at index k4 * (N / 4) + n4. The launcher
+// receives the two micro-tile strides of the contraction and the output axis, so one kernel serves both
+// directions. B200 counterpart of `int8_scaled_mm_kernel` / `launch_int8_scaled_mm` in the reference's
+// csrc/hip_kernel_int8.cu (kernel :88-361, C ABI :413-471).
+//
+// Structure (one persistent CTA per SM, 128 x BN output tiles, 128 contraction bytes per pipeline slot):
+//   * warp 0: TMA producer for the int8 activation tile (128 rows x 128 bytes, 128-byte swizzle, zero fill
+//     past M and past the contraction length);
+//   * eight re-layout warps: read the weight micro-tiles straight from global memory (L2), re-select
+//     their bytes into K-major 16-byte rows (forward: four dwords of four consecutive k4; backward: a 4x4
+//     byte transpose of four consecutive n4) and write the 128-byte swizzled UMMA operand tile;
+//   * warp 1: one thread issues tcgen05.mma kind::i8 (M=128, N=BN, K=32) into one of two int32 TMEM
+//     accumulators;
+//   * four epilogue warps: int32 -> float, both scales, bias, one rounding, 16-byte stores.
+// A ragged M is handled by the TMA zero fill and a row predicate on the stores, so there is no second
+// launch for the M tail.
+#include "feather_host.h"
+#include "feather_tiles_gen.h"
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace feather {
+namespace i8mm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;  // contraction bytes per slot: one 128-byte swizzle span
+constexpr int kAStages = 4;
+constexpr int kOperandStages = 3;
+constexpr int kRelayoutWarps = 8;
+constexpr int kEpilogueWarps = 4;
+constexpr int kFirstEpilogueWarp = 2;
+constexpr int kFirstRelayoutWarp = kFirstEpilogueWarp + kEpilogueWarps;
+constexpr int kThreads = 32 * (kFirstRelayoutWarp + kRelayoutWarps);
+constexpr int kATileBytes = kBlockM * kBlockK;
+
+__device__ uint32_t g_status[2];
+
+struct Params {
+    const uint8_t* b;      // prepacked weight, 16-byte micro-tiles
+    const float* a_scale;  // [M]
+    const float* b_scale;  // [N_out] or null
+    const uint16_t* bias;  // [N_out] or null
+    uint16_t* c;           // [M, N_out]
+    int M;
+    int N_out;
+    int K;                  // contraction length in bytes
+    int64_t stride_kc;      // micro-tile stride of one 4-wide contraction step
+    int64_t stride_out;     // micro-tile stride of one 4-wide output step
+    int tiles_m;
+    int tiles_n;
+    uint32_t idesc;
+};
+
+template <int BN>
+struct Smem {
+    static constexpr int kOperandBytes = BN * 128;
+    static constexpr int kAOff = 0;
+    static constexpr int kOperandOff = kAOff + kAStages * kATileBytes;
+    static constexpr int kBarOff = kOperandOff + kOperandStages * kOperandBytes;
+    static constexpr int kNumBars = 2 * kAStages + 2 * kOperandStages + 4;
+    static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+struct Ring {
+    uint32_t idx = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(uint32_t depth) {
+        if (++idx == depth) {
+            idx = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+template <bool kOutBf16>
+__device__ __forceinline__ uint32_t pack_out(float a, float b) {
+    if constexpr (kOutBf16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    } else {
+        const __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
+template <bool kOutBf16>
+__device__ __forceinline__ float out_bits_to_float(uint16_t bits) {
+    if constexpr (kOutBf16) {
+        return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    } else {
+        return __half2float(__ushort_as_half(bits));
+    }
+}
+
+// 4x4 byte transpose: in[i] byte j -> out[j] byte i.
+__device__ __forceinline__ void transpose4x4(const uint32_t (&in)[4], uint32_t (&out)[4]) {
+    const uint32_t t0 = __byte_perm(in[0], in[1], 0x5140u);
+    const uint32_t t1 = __byte_perm(in[0], in[1], 0x7362u);
+    const uint32_t t2 = __byte_perm(in[2], in[3], 0x5140u);
+    const uint32_t t3 = __byte_perm(in[2], in[3], 0x7362u);
+    out[0] = __byte_perm(t0, t2, 0x5410u);
+    out[1] = __byte_perm(t0, t2, 0x7632u);
+    out[2] = __byte_perm(t1, t3, 0x5410u);
+    out[3] = __byte_perm(t1, t3, 0x7632u);
+}
+
+template <int BN, bool kTransposedB, bool kOutBf16>
+__global__ void __launch_bounds__(kThreads, 1) int8_mm_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
+    using L = Smem<BN>;
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint64_t* const a_full = bars;
+    uint64_t* const a_empty = a_full + kAStages;
+    uint64_t* const operand_full = a_empty + kAStages;
+    uint64_t* const operand_empty = operand_full + kOperandStages;
+    uint64_t* const tmem_full = operand_empty + kOperandStages;
+    uint64_t* const tmem_empty = tmem_full + 2;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < kOperandStages; ++s) {
+            mbar_init(&operand_full[s], kRelayoutWarps);
+            mbar_init(&operand_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_a);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 2 * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (activations)
+        if (elect_one()) {
+            Ring slot;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                const int m0 = (tile % p.tiles_m) * kBlockM;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&a_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&a_full[slot.idx], kATileBytes);
+                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &a_full[slot.idx], kb * kBlockK, m0);
+                    slot.advance(kAStages);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            Ring slot, operand, acc;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                ok = guard.wait(&tmem_empty[acc.idx], acc.phase ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc.idx * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&a_full[slot.idx], slot.phase, kSiteLoadFull) &&
+                         guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
+                    const uint32_t b_addr = smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 32; ++k) {
+                        umma_i8(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&a_empty[slot.idx]);
+                    umma_commit(&operand_empty[operand.idx]);
+                    slot.advance(kAStages);
+                    operand.advance(kOperandStages);
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full[acc.idx]);
+                acc.advance(2);
+            }
+        }
+    } else if (warp < kFirstRelayoutWarp) {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp % 4;
+        const bool wide_rows = (p.N_out % 8) == 0;  // rows are 16-byte aligned
+        Ring acc;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            const int m0 = (tile % p.tiles_m) * kBlockM;
+            const int n0 = (tile / p.tiles_m) * BN;
+            ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
+            const float row_scale = row < p.M ? __ldg(p.a_scale + row) : 0.0f;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * BN;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N_out;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_wait_ld();
+                if (c == BN / 32 - 1) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
+                }
+                const int col0 = n0 + c * 32;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int col = col0 + g * 4;  // N_out is a multiple of 4
+                    if (col >= p.N_out) continue;
+                    float f[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float value = static_cast<float>(static_cast<int32_t>(v[g * 4 + i])) * row_scale;
+                        if constexpr (!kTransposedB) {
+                            if (p.b_scale != nullptr) value *= __ldg(p.b_scale + col + i);
+                            if (p.bias != nullptr) value += out_bits_to_float<kOutBf16>(__ldg(p.bias + col + i));
+                        }
+                        f[i] = value;
+                    }
+                    v[g * 4] = pack_out<kOutBf16>(f[0], f[1]);
+                    v[g * 4 + 1] = pack_out<kOutBf16>(f[2], f[3]);
+                }
+                if (row < p.M) {
+                    if (wide_rows) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col0 + g * 8 < p.N_out) {
+                                *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = make_uint4(v[g * 8], v[g * 8 + 1], v[g * 8 + 4], v[g * 8 + 5]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            if (col0 + g * 4 < p.N_out) {
+                                *reinterpret_cast<uint2*>(c_row + col0 + g * 4) = make_uint2(v[g * 4], v[g * 4 + 1]);
+                            }
+                        }
+                    }
+                }
+            }
+            acc.advance(2);
+        }
+    } else {
+        // ------------------------------------------------------------------ weight re-layout warps
+        const int t = static_cast<int>(threadIdx.x) - kFirstRelayoutWarp * 32;
+        const int k4_total = p.K / 4;
+        if constexpr (!kTransposedB) {
+            // Thread = operand row (output channel n). Dword (k4, n) of the prepack holds W[n][4 k4 .. 4 k4 + 3],
+            // which is exactly four consecutive bytes of the K-major operand row, so the re-layout is a
+            // 4-byte asynchronous copy per dword, straight from global (L2) to its swizzled position.
+            // `kOperandStages - 1` slots of copies are kept in flight per thread.
+            constexpr int kThreadsPerRow = (kRelayoutWarps * 32) / BN;
+            constexpr int kChunksPerThread = 8 / kThreadsPerRow;
+            constexpr int kInFlight = kOperandStages - 1;
+            const uint32_t* const dwords = reinterpret_cast<const uint32_t*>(p.b);
+            const int row = t % BN;
+            const int first_chunk = (t / BN) * kChunksPerThread;
+            Ring issue, landed;
+            int tile = static_cast<int>(blockIdx.x);
+            int kb = 0;
+            bool ok = true;
+            bool more = tile < num_tiles;
+            int pending = 0;  // committed groups not yet published
+            while (ok && (more || pending > 0)) {
+                if (more) {
+                    const int n = (tile / p.tiles_m) * BN + row;
+                    const bool n_live = n < p.N_out;
+                    const int64_t col_off = static_cast<int64_t>(n / 4) * p.stride_out * 4 + (n % 4);
+                    ok = guard.wait(&operand_empty[issue.idx], issue.phase ^ 1u, kSiteOperandEmpty);
+                    if (!ok) break;
+                    const uint32_t dst = smem_u32(smem + L::kOperandOff + issue.idx * L::kOperandBytes);
+#pragma unroll
+                    for (int c = 0; c < kChunksPerThread; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int k4 = kb * (kBlockK / 4) + (first_chunk + c) * 4 + j;
+                            const bool live = n_live && k4 < k4_total;
+                            const uint32_t* const src = live ? dwords + static_cast<int64_t>(k4) * p.stride_kc * 4 + col_off : dwords;
+                            cp_async_4(dst + sw128_offset(row, first_chunk + c) + j * 4, src, live);
+                        }
+                    }
+                    issue.advance(kOperandStages);
+                    if (++kb == num_kb) {
+                        kb = 0;
+                        tile += static_cast<int>(gridDim.x);
+                        more = tile < num_tiles;
+                    }
+                }
+                cp_async_commit();
+                ++pending;
+                if (pending > kInFlight || !more) {
+                    if (more) {
+                        cp_async_wait<kInFlight>();
+                    } else {
+                        cp_async_wait<0>();
+                    }
+                    // everything but the newest `kInFlight` groups (all groups once the work is issued) has landed
+                    const int publish = more ? 1 : pending;
+                    for (int i = 0; i < publish; ++i) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&operand_full[landed.idx]);
+                        landed.advance(kOperandStages);
+                    }
+                    pending -= publish;
+                }
+            }
+        } else {
+            // Thread = four operand rows (output columns 4 k4 .. 4 k4 + 3) x some 16-byte chunks.
+            // Micro-tile (k4, n4) dword i holds W[4 n4 + i][4 k4 .. + 3]: the rows need byte r of every
+            // dword, i.e. a 4x4 byte transpose per micro-tile, done in registers.
+            constexpr int kColumns = BN / 4;
+            constexpr int kThreadsPerColumn = (kRelayoutWarps * 32) / kColumns;
+            constexpr int kChunksPerThread = (8 + kThreadsPerColumn - 1) / kThreadsPerColumn;
+            const uint4* const tiles = reinterpret_cast<const uint4*>(p.b);
+            const int column = t % kColumns;
+            const int first_chunk = (t / kColumns) * kChunksPerThread;
+            Ring operand;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                const int out4 = ((tile / p.tiles_m) * BN) / 4 + column;
+                const bool out_live = out4 * 4 < p.N_out;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    uint4 m[kChunksPerThread][4];
+#pragma unroll
+                    for (int c = 0; c < kChunksPerThread; ++c) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int kc4 = kb * (kBlockK / 4) + (first_chunk + c) * 4 + j;
+                            const bool live = out_live && kc4 < k4_total && first_chunk + c < 8;
+                            m[c][j] = live ? __ldg(tiles + static_cast<int64_t>(kc4) * p.stride_kc + static_cast<int64_t>(out4) * p.stride_out)
+                                           : make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                    ok = guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                    if (!ok) break;
+                    uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+#pragma unroll
+                    for (int c = 0; c < kChunksPerThread; ++c) {
+                        if (first_chunk + c < 8) {
+                            uint32_t rows[4][4];  // rows[j][r]: 4 contraction bytes of output row r from micro-tile j
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t in[4] = {m[c][j].x, m[c][j].y, m[c][j].z, m[c][j].w};
+                                transpose4x4(in, rows[j]);
+                            }
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) {
+                                *reinterpret_cast<uint4*>(dst + sw128_offset(column * 4 + r, first_chunk + c)) =
+                                    make_uint4(rows[0][r], rows[1][r], rows[2][r], rows[3][r]);
+                            }
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&operand_full[operand.idx]);
+                    operand.advance(kOperandStages);
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 2 * BN);
+    }
+}
+
+struct LaunchArgs {
+    const int8_t* a;
+    const uint8_t* b;
+    const float* a_scale;
+    const float* b_scale;
+    const uint16_t* bias;
+    uint16_t* c;
+    int64_t M, N_out, K;
+    int64_t stride_kc, stride_out;
+    bool transposed_b;
+    bool out_bf16;
+    cudaStream_t stream;
+};
+
+template <int BN, bool kTransposedB, bool kOutBf16>
+bool launch_instance(const LaunchArgs& args) {
+    using L = Smem<BN>;
+    auto* kernel = &int8_mm_kernel<BN, kTransposedB, kOutBf16>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+    CUtensorMap map_a;
+    const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(args.K)};
+    const uint32_t box[2] = {kBlockK, kBlockM};
+    if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+
+    Params p{};
+    p.b = args.b;
+    p.a_scale = args.a_scale;
+    p.b_scale = args.b_scale;
+    p.bias = args.bias;
+    p.c = args.c;
+    p.M = static_cast<int>(args.M);
+    p.N_out = static_cast<int>(args.N_out);
+    p.K = static_cast<int>(args.K);
+    p.stride_kc = args.stride_kc;
+    p.stride_out = args.stride_out;
+    p.tiles_m = static_cast<int>((args.M + kBlockM - 1) / kBlockM);
+    p.tiles_n = static_cast<int>((args.N_out + BN - 1) / BN);
+    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, kBlockM, BN);
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int sms = device_info().sm_count;
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, p);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+template <int BN>
+bool launch_for_block_n(const LaunchArgs& args) {
+    if (args.transposed_b) {
+        return args.out_bf16 ? launch_instance<BN, true, true>(args) : launch_instance<BN, true, false>(args);
+    }
+    return args.out_bf16 ? launch_instance<BN, false, true>(args) : launch_instance<BN, false, false>(args);
+}
+
+}  // namespace i8mm
+}  // namespace feather
+
+// C ABI, same signature as the reference's `launch_int8_scaled_mm` (csrc/hip_kernel_int8.cu:413-432).
+// `b_stride_kc` / `b_stride_out` are the micro-tile strides of one 4-wide step along the contraction
+// and the output axis of the weight. `output_dtype`: 0 = fp16, 1 = bf16. `a` must be 16-byte aligned and
+// `K_contract` a multiple of 16; `N_out` a multiple of 4. Returns false for an unknown tile tuple.
+extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const float* a_scale, const float* b_scale, const uint16_t* bias,
+                                      uint16_t* c, int64_t M, int64_t N_out, int64_t K_contract, int64_t b_stride_kc, int64_t b_stride_out,
+                                      bool transposed_b, int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n,
+                                      int output_dtype, cudaStream_t stream) {
+    using namespace feather;
+    const int block_n = int8_tile_block_n(block_warps_m, block_warps_n, unroll_k, repeat_m, repeat_n);
+    if (block_n == 0) return false;
+    if (M < 0 || N_out <= 0 || K_contract <= 0 || N_out % 4 != 0 || K_contract % 16 != 0) return false;
+    if (M > (1 << 30) || N_out > (1 << 30) || K_contract > (1 << 30)) return false;
+    if (M == 0) return true;
+    const i8mm::LaunchArgs args{a, b, a_scale, b_scale, bias, c, M, N_out, K_contract, b_stride_kc, b_stride_out,
+                                transposed_b, output_dtype != 0, stream};
+    if (block_n >= 256) return i8mm::launch_for_block_n<256>(args);
+    if (block_n >= 128) return i8mm::launch_for_block_n<128>(args);
+    return i8mm::launch_for_block_n<64>(args);
+}
+
+// Reads and clears the int8 GEMM's wait-status record (see feather_scaled_mm_status).
+extern "C" int feather_int8_mm_status(uint32_t* out) {
+    uint32_t zero[2] = {0u, 0u};
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    if (cudaMemcpyFromSymbol(out, feather::i8mm::g_status, sizeof(zero)) != cudaSuccess) return 1;
+    if (cudaMemcpyToSymbol(feather::i8mm::g_status, zero, sizeof(zero)) != cudaSuccess) return 1;
+    return 0;
+}

@@ -118,6 +118,23 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Per-thread asynchronous copies (cp.async, generic proxy)
+// ---------------------------------------------------------------------------------------------------------
+// 4 bytes global -> shared. `live == false` writes zeros without reading `src` (which must still be a
+// valid address).
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* src, bool live) {
+    const uint32_t src_bytes = live ? 4u : 0u;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // TMA loads / stores (never with cluster multicast)
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {

@@ -36,6 +36,39 @@ bool launch_scaled_mm(const uint16_t* a, const uint8_t* b_prepacked, const float
  * Returns 0 on success. No counterpart in the reference (its kernels have no device-side waits). */
 int feather_scaled_mm_status(uint32_t* out);
 
+/* ConvRot activation quantizer: per row, group-256 regular Hadamard rotation (fp32 radix-4, one rounding to the
+ * input dtype), row absmax, int8 codes in [-127, 127] and one fp32 scale per row (absmax / 127, divided by 16
+ * when rotating). x: [M, K] fp16 (input_fp16 != 0) or bf16, K % 256 == 0. col_scale: [K] multiplier applied
+ * (and rounded to the input dtype) only when rotate is false, or NULL. q: [M, K] int8. row_scale: [M].
+ * Replaces `launch_convrot_quantize`, reference csrc/hip_kernel_int8.cu:869-878. */
+bool launch_convrot_quantize(const void* x, const float* col_scale, int8_t* q, float* row_scale, int64_t M, int64_t K, int input_fp16,
+                             bool rotate, feather_stream_t stream);
+
+/* int8 GEMM over the 4x4 micro-tile prepacked weight, int32 accumulation.
+ * forward (transposed_b false): c[M, N_out] = cast(float(a[M, K] . W[N_out, K]^T) * a_scale[m] * b_scale[n] + bias[n]);
+ * backward (transposed_b true): c[M, N_out] = cast(float(a[M, K] . W[K, N_out]) * a_scale[m]), b_scale and bias unused.
+ * b_stride_kc / b_stride_out: micro-tile strides of one 4-wide step along the contraction / the output axis.
+ * K_contract % 16 == 0, N_out % 4 == 0. output_dtype: 0 = fp16, 1 = bf16.
+ * Replaces `launch_int8_scaled_mm`, reference csrc/hip_kernel_int8.cu:413-432. */
+bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const float* a_scale, const float* b_scale, const uint16_t* bias,
+                           uint16_t* c, int64_t M, int64_t N_out, int64_t K_contract, int64_t b_stride_kc, int64_t b_stride_out,
+                           bool transposed_b, int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n,
+                           int output_dtype, feather_stream_t stream);
+
+/* Diagnostic for the int8 GEMM's bounded waits, as feather_scaled_mm_status. No counterpart in the reference. */
+int feather_int8_mm_status(uint32_t* out);
+
+/* 3x3, stride 1, padding 1, NCHW conv2d with fp32 accumulation, bias added in fp32, one rounding.
+ * x: [B, C_in, H, W]; wp: prepacked weight [ceil(C_in / 16) * 18, C_out, 8]; bias: [C_out] or NULL; y: [B, C_out, H, W];
+ * one 16-bit dtype for all (is_bf16), C_in % 8 == 0. Tile = (warps_m, warps_n, repeat_m, repeat_n, rows).
+ * Returns 0 on success, 1 for an unknown tile or an unsupported problem.
+ * Replaces `feather_conv3x3_launch`, reference csrc/hip_conv2d_3x3.cu:561-575. */
+int feather_conv3x3_launch(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W, int has_bias,
+                           int warps_m, int warps_n, int repeat_m, int repeat_n, int rows, int is_bf16, int prefetch, void* stream);
+
+/* Diagnostic for the conv kernel's bounded waits, as feather_scaled_mm_status. No counterpart in the reference. */
+int feather_conv3x3_status(uint32_t* out);
+
 #ifdef __cplusplus
 }
 #endif
