@@ -121,6 +121,7 @@ def build_extension(force: bool = False) -> None:
         "-shared",
         "-DTORCH_TARGET_VERSION=0x020A000000000000",
         "-DTORCH_STABLE_ONLY",
+        "-DUSE_CUDA",
         "-D_GLIBCXX_USE_CXX11_ABI=" + str(int(torch.compiled_with_cxx11_abi())),
         "-I",
         str(torch_dir / "include"),
@@ -140,6 +141,7 @@ def build_extension(force: bool = False) -> None:
         str(torch_dir / "lib"),
         "-ltorch",
         "-ltorch_cpu",
+        "-ltorch_cuda",
         "-lc10",
         "-Wl,-rpath,$ORIGIN",
         "-Wl,-rpath," + str(torch_dir / "lib"),

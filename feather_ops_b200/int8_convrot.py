@@ -1,0 +1,224 @@
+"""Int8 ConvRot linear layers: fused rotate+quantize of the activation, int8 GEMM over a prepacked weight.
+
+The weight format is the released one (`weight` int8 `[N, K]` in the rotated basis plus a float32 scale per
+output channel). `prepack_int8_weight` permutes it into 4x4 byte micro-tiles once, and both GEMMs of a
+training step read that copy:
+
+    forward   C[M, N] = A[M, K] @ W[N, K]^T
+    backward  C[M, K] = A[M, N] @ W[N, K]      (`transposed_b=True`)
+
+Function names, arguments and error behaviour follow the reference module (`feather_ops/int8_convrot.py`).
+"""
+
+import torch
+from torch.library import custom_op
+
+from .tiles import INT8_UMMA
+
+CONVROT_GROUP = 256  # the quantizer implements the regular Hadamard over 256 channels only
+
+_TILE_N256 = (4, 4, 2, 4, 4)
+_TILE_N128 = (2, 4, 2, 4, 2)
+_TILE_N64 = (2, 2, 2, 2, 2)
+_SM_COUNT = 148
+_TILE_COST = {256: 1.0, 128: 0.56, 64: 0.34}
+_TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
+
+
+def select_int8_config(M: int, N: int, K: int, transposed_b: bool):
+    """Tile tuple for one `(M, N, K)` cell and direction (`N`/`K` are the weight's output/input axes, as
+    in the reference's `select_int8_config`, `feather_ops/int8_convrot.py:28-82`). Same wave-count rule as
+    `scaled_mm`: the widest UMMA tile unless a narrower one fills the SMs better."""
+    out = K if transposed_b else N
+    tiles_m = -(-M // 128)
+    best = None
+    for width in (256, 128, 64):
+        cost = -(-(tiles_m * -(-out // width)) // _SM_COUNT) * _TILE_COST[width]
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, width)
+    return _TILE_OF_WIDTH[best[1]]
+
+
+def prepack_int8_weight(weight: torch.Tensor) -> torch.Tensor:
+    """`[N, K]` int8 -> `[K // 4, N // 4, 4, 4]`: micro-tile `(k4, n4)` holds `W[4 n4 : 4 n4 + 4, 4 k4 : 4 k4 + 4]`
+    with `k` fastest. A pure byte permutation."""
+    n, k = weight.shape
+    return weight.view(n // 4, 4, k // 4, 4).permute(2, 0, 1, 3).contiguous()
+
+
+def unpack_int8_weight(prepacked: torch.Tensor) -> torch.Tensor:
+    """Back to the released `[N, K]` form."""
+    if prepacked.ndim != 4 or tuple(prepacked.shape[2:]) != (4, 4):
+        raise ValueError(f"prepacked weight must end in (4, 4), got {tuple(prepacked.shape)}")
+    k4, n4 = prepacked.shape[:2]
+    return prepacked.permute(1, 2, 0, 3).reshape(n4 * 4, k4 * 4)
+
+
+def quantize_convrot_activation(x: torch.Tensor, rotate: bool = True, col_scale: torch.Tensor | None = None):
+    """Rotate each 256-wide group by the regular Hadamard and quantize per row to int8, in one kernel.
+
+    `x` is `[M, K]` bf16/fp16 with `K % 256 == 0`. `rotate=False` quantizes as is (the input-gradient path,
+    which rotates after the GEMM) and may fold a `[K]` float32 `col_scale` in first. Returns
+    `(q int8 [M, K], scale float32 [M])` with `q * scale` the normalized rotated values.
+    """
+    q = torch.empty(x.shape, device=x.device, dtype=torch.int8)
+    scale = torch.empty(x.shape[0], device=x.device, dtype=torch.float32)
+    folded = None if col_scale is None else col_scale.reshape(-1).to(device=x.device, dtype=torch.float32).contiguous()
+    torch.ops.feather_ops.convrot_quantize.default(x, folded, q, scale, rotate)
+    return q, scale
+
+
+def _launch(a, weight_prepacked, a_scale, weight_scale, bias, out, transposed_b, tile) -> None:
+    torch.ops.feather_ops.int8_scaled_mm.default(
+        a,
+        weight_prepacked.reshape(-1),
+        a_scale.reshape(-1).to(torch.float32),
+        None if weight_scale is None else weight_scale.reshape(-1).to(torch.float32),
+        bias,
+        out,
+        transposed_b,
+        *tile,
+    )
+
+
+@custom_op("feather_ops::int8_scaled_mm_auto", mutates_args=("out",))
+def _int8_scaled_mm_auto(
+    a: torch.Tensor,
+    weight_prepacked: torch.Tensor,
+    a_scale: torch.Tensor,
+    weight_scale: torch.Tensor | None,
+    bias: torch.Tensor | None,
+    out: torch.Tensor,
+    transposed_b: bool,
+) -> None:
+    """Tile choice + launch as one opaque node."""
+    other = weight_prepacked.numel() // a.shape[1]
+    n, k = (a.shape[1], other) if transposed_b else (other, a.shape[1])
+    _launch(a, weight_prepacked, a_scale, weight_scale, bias, out, transposed_b, select_int8_config(a.shape[0], n, k, transposed_b))
+
+
+def int8_scaled_mm(a, weight_prepacked, a_scale, weight_scale=None, bias=None, out_dtype=torch.bfloat16, transposed_b=False, tile=None):
+    """`A @ W^T` (or `A @ W` with `transposed_b`) with a per-row activation scale and, forward only, a
+    per-output-channel weight scale and a bias. `a` is `[M, K]` int8, `weight_prepacked` the micro-tile
+    prepack in any shape. Returns `[M, N_out]` in `out_dtype`."""
+    m, k = a.shape
+    if k == 0:
+        raise ValueError("a must have a nonzero contraction axis")
+    if transposed_b and weight_scale is not None:
+        raise ValueError("transposed_b folds the weight scale into the activation quantization, so weight_scale must be None")
+    out = torch.empty((m, weight_prepacked.numel() // k), device=a.device, dtype=out_dtype)
+    if tile is None:
+        _int8_scaled_mm_auto(a, weight_prepacked, a_scale, weight_scale, bias, out, transposed_b)
+    else:
+        _launch(a, weight_prepacked, a_scale, weight_scale, bias, out, transposed_b, tile)
+    return out
+
+
+_HADAMARD_CACHE: dict = {}
+
+
+def build_hadamard(size: int = CONVROT_GROUP, device="cpu", dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Normalized regular Hadamard of a power-of-four `size`: the Kronecker power of the 4x4 matrix whose rows
+    have a single -1 on the anti-diagonal, divided by `sqrt(size)`. Symmetric and orthogonal. Cached."""
+    probe = size
+    while probe > 1 and probe % 4 == 0:
+        probe //= 4
+    if probe != 1:
+        raise ValueError(f"the regular Hadamard size must be a power of four, got {size}")
+    key = (size, str(device), dtype)
+    if key not in _HADAMARD_CACHE:
+        base = torch.ones((4, 4), dtype=dtype, device=device)
+        for i in range(4):
+            base[i, 3 - i] = -1
+        h = base
+        while h.shape[0] < size:
+            h = torch.kron(h, base)
+        _HADAMARD_CACHE[key] = h / (size**0.5)
+    return _HADAMARD_CACHE[key]
+
+
+def rotate(x: torch.Tensor, hadamard: torch.Tensor, groupsize: int = CONVROT_GROUP) -> torch.Tensor:
+    """Group-wise `x @ H^T` along the last axis (its own inverse, `H` being orthogonal and symmetric)."""
+    width = x.shape[-1]
+    if width % groupsize:
+        raise ValueError(f"last axis {width} is not divisible by the group size {groupsize}")
+    grouped = x.reshape(*x.shape[:-1], width // groupsize, groupsize)
+    return torch.matmul(grouped, hadamard.T.to(dtype=x.dtype, device=x.device)).reshape(x.shape)
+
+
+def quantize_rowwise_int8(x: torch.Tensor, scale=None):
+    """Per-row int8 codes of an already rotated tensor, `scale = absmax / 127` unless given. Codes are clamped
+    to the symmetric range [-127, 127]."""
+    if scale is None:
+        scale = (x.abs().amax(dim=-1).float() / 127.0).clamp(min=1e-30)
+    elif isinstance(scale, torch.Tensor):
+        scale = scale.reshape(-1).to(device=x.device, dtype=torch.float32)
+    else:
+        scale = torch.tensor(scale, device=x.device, dtype=torch.float32)
+    per_row = scale.reshape(-1, *([1] * (x.ndim - 1)))
+    return torch.clamp(torch.round(x.float() / per_row), -127.0, 127.0).to(torch.int8), scale
+
+
+def quantize_convrot_weight(weight: torch.Tensor, groupsize: int = CONVROT_GROUP, rotate_dtype: torch.dtype | None = None):
+    """Offline weight quantization: rotate per group with a matmul (in `rotate_dtype`, default the weight's
+    own dtype), then `quantize_rowwise_int8`."""
+    hadamard = build_hadamard(groupsize, device=weight.device, dtype=torch.float32)
+    return quantize_rowwise_int8(rotate(weight.to(rotate_dtype or weight.dtype), hadamard, groupsize))
+
+
+def dequantize_convrot_weight(q: torch.Tensor, scale: torch.Tensor, groupsize: int = CONVROT_GROUP) -> torch.Tensor:
+    """`code * scale` rotated back to the original basis, float32."""
+    hadamard = build_hadamard(groupsize, device=q.device, dtype=torch.float32)
+    return rotate(q.float() * scale.reshape(-1, 1), hadamard, groupsize)
+
+
+def convrot_int8_supported(shape, groupsize: int = CONVROT_GROUP, backward: bool = True) -> tuple[bool, str]:
+    """Whether the kernels can run an `[N, K]` ConvRot weight, with the reason if not."""
+    n, k = int(shape[0]), int(shape[1])
+    if groupsize != CONVROT_GROUP:
+        return False, f"only group size {CONVROT_GROUP} is implemented, got {groupsize}"
+    if k % groupsize:
+        return False, f"in_features {k} is not a multiple of the group size {groupsize}"
+    if k % 16:
+        return False, f"in_features {k} is not a multiple of the 16-wide reduction step"
+    if n % 4:
+        return False, f"out_features {n} is not a multiple of 4"
+    if backward and n % 16:
+        return False, f"out_features {n} is not a multiple of 16, which the input gradient contracts"
+    return True, ""
+
+
+def _weight_extent(weight: torch.Tensor, weight_scale: torch.Tensor) -> tuple[int, int]:
+    """`(N, K)` from the byte count and the number of per-channel scales (works for both weight layouts)."""
+    n_out = int(weight_scale.numel())
+    if n_out == 0 or weight.numel() % n_out:
+        raise ValueError(f"weight of {weight.numel()} bytes does not divide into {n_out} output channels")
+    return n_out, int(weight.numel() // n_out)
+
+
+def convrot_int8_linear(x, weight, weight_scale, bias=None, out_dtype=torch.bfloat16, groupsize=CONVROT_GROUP, rotate_activation=True, weight_packed=False):
+    """Forward `x @ W^T + bias`: fused rotate+quantize of `x`, then the int8 GEMM with both scales."""
+    n_out, k_in = _weight_extent(weight, weight_scale)
+    if x.shape[-1] != k_in:
+        raise ValueError(f"activation has {x.shape[-1]} features, the weight {k_in}")
+    q, scale = quantize_convrot_activation(x.reshape(-1, k_in), rotate=rotate_activation)
+    packed = weight if weight_packed else prepack_int8_weight(weight)
+    out = int8_scaled_mm(q, packed, scale, weight_scale.reshape(-1), bias, out_dtype, False)
+    return out.reshape(*x.shape[:-1], n_out)
+
+
+def convrot_int8_dgrad(grad_out, weight, weight_scale, out_dtype=torch.bfloat16, groupsize=CONVROT_GROUP, rotate_activation=True, weight_packed=False):
+    """Input gradient `g @ W` (then rotated back): the per-channel weight scale cannot leave a sum over
+    channels, so it is folded into the row-wise quantization of `grad_out`."""
+    _, k_in = _weight_extent(weight, weight_scale)
+    q, scale = quantize_convrot_activation(grad_out.reshape(-1, grad_out.shape[-1]), False, col_scale=weight_scale.reshape(-1))
+    packed = weight if weight_packed else prepack_int8_weight(weight)
+    out = int8_scaled_mm(q, packed, scale, None, None, out_dtype, True)
+    if rotate_activation:
+        out = rotate(out, build_hadamard(groupsize, device=out.device, dtype=out.dtype), groupsize)
+    return out.reshape(*grad_out.shape[:-1], k_in)
+
+
+def umma_tile(tile):
+    """The sm_100a tile the tuple runs on."""
+    return INT8_UMMA[tuple(tile)]

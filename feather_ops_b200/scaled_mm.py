@@ -1,0 +1,87 @@
+"""`Y = (X @ W) * scale + bias` with fp16/bf16 activations and a prepacked fp8 weight.
+
+Python side of the `scaled_mm` operator: output allocation, tile choice, and the weight prepack. The API
+is the reference's (`feather_ops/scaled_mm.py` there): `scaled_mm_hip(a, b_prepacked, scale, bias,
+out_dtype, tile=None)` keeps its name so callers switch by changing the import.
+`X` is `[M, K]`, the weight is `[K_pad/16, N, 16]` fp8 (e5m2 or e4m3fn), `scale` a one-element float32
+tensor or None, `bias` `[N]` in the output dtype or None. Any `M >= 1`; `N` and `K` multiples of 16.
+"""
+
+import torch
+from torch.library import custom_op
+
+from .tiles import SCALED_MM_UMMA, gemm_block_sizes
+
+# One public tuple per UMMA width (all rows of the tile table).
+_TILE_N256 = (1, 8, 4, 8, 2, 0)
+_TILE_N128 = (2, 2, 2, 4, 4, 0)
+_TILE_N64 = (1, 2, 4, 1, 2, 1)
+
+_SM_COUNT = 148
+# Time of one 128 x BN tile relative to the 256-wide one, per k step: the narrow tiles pay the same
+# activation traffic and pipeline overhead for fewer columns.
+_TILE_COST = {256: 1.0, 128: 0.56, 64: 0.34}
+_TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
+
+
+def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dtype=torch.float8_e5m2, out_dtype=torch.bfloat16):
+    """Tile tuple for one shape (same signature as the reference's `select_scaled_mm_config`,
+    `feather_ops/scaled_mm.py:35-90`; the dtypes do not matter).
+
+    The kernel is persistent with one CTA per SM, so the cost of a width is
+    `waves(width) * cost(width)` with `waves = ceil(tiles / SMs)`: a wide output keeps the 256-wide UMMA
+    tile, a shape with few tiles trades it for a narrower one to fill more SMs.
+    """
+    del K, a_dtype, b_dtype, out_dtype
+    tiles_m = -(-M // 128)
+    best = None
+    for width in (256, 128, 64):
+        tiles = tiles_m * -(-N // width)
+        cost = -(-tiles // _SM_COUNT) * _TILE_COST[width]
+        if best is None or cost < best[0] - 1e-9:
+            best = (cost, width)
+    return _TILE_OF_WIDTH[best[1]]
+
+
+def _launch(a, b_prepacked, scale, bias, out, tile) -> None:
+    torch.ops.feather_ops.scaled_mm.default(a, b_prepacked, scale, bias, out, *tile[:5], bool(tile[5]))
+
+
+@custom_op("feather_ops::scaled_mm_auto", mutates_args=("out",))
+def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Tensor | None, bias: torch.Tensor | None, out: torch.Tensor) -> None:
+    """Tile choice + launch as one opaque node, so a compiled caller does not specialize on the heuristic."""
+    _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(a.shape[0], b_prepacked.shape[1], a.shape[1]))
+
+
+def scaled_mm_hip(a, b_prepacked, scale, bias, out_dtype, tile=None):
+    """`(a @ W) * scale + bias` against the prepacked fp8 weight. `tile` pins a row of `SCALED_MM_TILES`."""
+    out = torch.empty((a.shape[0], b_prepacked.shape[1]), device=a.device, dtype=out_dtype)
+    if tile is None:
+        _scaled_mm_auto(a, b_prepacked, scale, bias, out)
+    else:
+        _launch(a, b_prepacked, scale, bias, out, tile)
+    return out
+
+
+
+def prepack_b_for_scaled_mm(b: torch.Tensor) -> torch.Tensor:
+    """`[K, N]` fp8 -> `[K_pad/16, N, 16]` with K zero padded to a multiple of 128: the sixteen consecutive k
+    of one column become one 16-byte cell (the reference's layout, `feather_ops/scaled_mm.py:137-150`)."""
+    k, n = b.shape
+    k_pad = (k + 127) // 128 * 128
+    cells = b.new_zeros((k_pad // 16, 16, n)) if k_pad != k else None
+    if cells is None:
+        cells = b.reshape(k // 16, 16, n)
+    else:
+        cells.reshape(k_pad, n)[:k] = b
+    return cells.transpose(1, 2).contiguous()
+
+
+def tile_shape(tile) -> tuple[int, int, int]:
+    """`(block_m, block_n, chunk_k)` the tuple names in the public vocabulary."""
+    return gemm_block_sizes(tile)
+
+
+def umma_tile(tile):
+    """The sm_100a tile the tuple runs on."""
+    return SCALED_MM_UMMA[tuple(tile)]

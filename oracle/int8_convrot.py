@@ -34,8 +34,10 @@ def quantize_rowwise_int8(x: torch.Tensor, scale=None):
     (reference feather_ops/int8_convrot.py:265-282)."""
     if scale is None:
         scale = (x.abs().amax(dim=-1).float() / 127.0).clamp(min=1e-30)
+    elif isinstance(scale, torch.Tensor):
+        scale = scale.reshape(-1).to(torch.float32)
     else:
-        scale = torch.as_tensor(scale, dtype=torch.float32).reshape(-1)
+        scale = torch.tensor(scale, dtype=torch.float32)
     q = torch.clamp(torch.round(x.float() / scale.reshape(-1, *([1] * (x.ndim - 1)))), -127.0, 127.0)
     return q.to(torch.int8), scale
 

@@ -1,0 +1,64 @@
+"""Calls into libfeather_ops_b200.so through ctypes with raw device pointers, as a foreign host would."""
+
+import torch
+
+from feather_ops_b200 import _lib
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def scaled_mm(a, b_prepacked, scale, bias, out_dtype, tile=(1, 8, 4, 8, 2, 0)):
+    m, k = a.shape
+    n = b_prepacked.shape[1]
+    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    ok = _lib.load().launch_scaled_mm(
+        _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), m, n, k, int(scale is not None), int(bias is not None),
+        b_prepacked.dtype == torch.float8_e5m2, a.dtype == torch.bfloat16, out_dtype == torch.bfloat16, *tile[:5], bool(tile[5]), _stream(),
+    )
+    assert ok, "launch_scaled_mm refused the call"
+    return c
+
+
+def convrot_quantize(x, rotate=True, col_scale=None):
+    m, k = x.shape
+    q = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    scale = torch.empty((m,), device=x.device, dtype=torch.float32)
+    ok = _lib.load().launch_convrot_quantize(_ptr(x), _ptr(col_scale), _ptr(q), _ptr(scale), m, k, int(x.dtype == torch.float16), rotate, _stream())
+    assert ok, "launch_convrot_quantize refused the call"
+    return q, scale
+
+
+def int8_scaled_mm(a, w_prepacked, a_scale, w_scale, bias, out_dtype, transposed_b, n_out, tile=(4, 4, 2, 4, 4)):
+    m, kc = a.shape
+    c = torch.empty((m, n_out), device=a.device, dtype=out_dtype)
+    weight_out = kc if transposed_b else n_out
+    inner = weight_out // 4
+    stride_kc, stride_out = (1, inner) if transposed_b else (inner, 1)
+    ok = _lib.load().launch_int8_scaled_mm(
+        _ptr(a), _ptr(w_prepacked), _ptr(a_scale), _ptr(w_scale), _ptr(bias), _ptr(c), m, n_out, kc, stride_kc, stride_out, transposed_b, *tile,
+        int(out_dtype == torch.bfloat16), _stream(),
+    )
+    assert ok, "launch_int8_scaled_mm refused the call"
+    return c
+
+
+def conv3x3(x, w_prepacked, bias, tile=(4, 4, 2, 4, 1)):
+    b, c_in, h, w = x.shape
+    c_out = w_prepacked.shape[1]
+    y = torch.empty((b, c_out, h, w), device=x.device, dtype=x.dtype)
+    rc = _lib.load().feather_conv3x3_launch(
+        _ptr(x), _ptr(w_prepacked), _ptr(bias), _ptr(y), b, c_in, c_out, h, w, int(bias is not None), *tile, int(x.dtype == torch.bfloat16), 0, _stream()
+    )
+    assert rc == 0, f"feather_conv3x3_launch returned {rc}"
+    return y
+
+
+def assert_clean(symbol):
+    """No bounded device wait ran out (also synchronizes)."""
+    assert _lib.read_status(symbol) == (0, 0)

@@ -1,0 +1,45 @@
+"""The C-ABI library loads without a GPU and exports every function `include/*.h` declares."""
+
+import ctypes
+import pathlib
+import re
+
+from feather_ops_b200 import _lib
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+
+
+def declared_functions() -> list[str]:
+    names = []
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names += re.findall(r"^\s*(?:bool|int|void)\s+(\w+)\s*\(", text, flags=re.M)
+    return names
+
+
+def test_header_declares_the_reference_launchers():
+    names = declared_functions()
+    for required in ("launch_scaled_mm", "launch_int8_scaled_mm", "launch_convrot_quantize", "feather_conv3x3_launch"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_functions():
+        assert isinstance(getattr(lib, name), ctypes._CFuncPtr), name
+
+
+def test_ctypes_prototypes_cover_the_header():
+    assert set(declared_functions()) <= set(_lib.PROTOTYPES)
+
+
+def test_launchers_reject_bad_arguments_without_touching_a_device(lib):
+    # unknown tile tuple, bad divisibility: refused before any CUDA call
+    assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 32, 32, 0, 0, True, True, True, 9, 9, 9, 9, 9, False, None)
+    assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 40, 32, 0, 0, True, True, True, 1, 8, 4, 8, 2, False, None)
+    assert not lib.launch_int8_scaled_mm(None, None, None, None, None, None, 16, 32, 32, 8, 1, False, 7, 7, 7, 7, 7, 1, None)
+    assert not lib.launch_convrot_quantize(None, None, None, None, 4, 300, 0, True, None)
+    assert lib.feather_conv3x3_launch(None, None, None, None, 1, 8, 8, 8, 8, 0, 9, 9, 9, 9, 1, 1, 0, None) == 1
+    assert lib.feather_conv3x3_launch(None, None, None, None, 1, 8, 8, 8, 9, 0, 4, 4, 2, 2, 2, 1, 0, None) == 1  # two rows, odd W
+    # empty problems are accepted and launch nothing
+    assert lib.launch_scaled_mm(None, None, None, None, None, 0, 32, 32, 0, 0, True, True, True, 1, 8, 4, 8, 2, False, None)
+    assert lib.launch_convrot_quantize(None, None, None, None, 0, 256, 0, True, None)

@@ -1,0 +1,189 @@
+"""The int8 ConvRot path on the GPU: quantizer codes bit-exact against the CPU restatement of the reference
+kernel's arithmetic, GEMM against the fp64 oracle with the reference's tolerance (tests/test_int8_convrot.py
+there: max-rel < 0.02 with a 1e-3 floor), compositions bit-exact against their parts."""
+
+import pytest
+import torch
+
+from oracle import int8_convrot as o8
+from tests import _cabi
+
+pytestmark = pytest.mark.gpu
+STATUS = "feather_int8_mm_status"
+
+
+def _max_rel(out, ref):
+    return ((out.float().cpu() - ref.float()).abs() / ref.float().abs().clamp(min=1e-3)).max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("shape", [(1, 256), (5, 512), (64, 1024), (33, 3072), (257, 4096), (4, 12288), (3, 33024), (2, 65536), (2, 248320)])
+def test_quantizer_codes_and_scales_are_bit_exact(cuda_device, shape, rotate, dtype):
+    m, k = shape
+    x = o8.make_activation(m, k, dtype, seed=m + k)
+    col = None if rotate else torch.rand(k, generator=torch.Generator().manual_seed(k)) + 0.5
+    q_ref, s_ref = o8.convrot_quantize(x, rotate, col)
+    q, s = _cabi.convrot_quantize(x.to(cuda_device), rotate, None if col is None else col.to(cuda_device))
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(s.cpu(), s_ref)
+
+
+def test_quantizer_against_the_reference_recipe(cuda_device, golden):
+    # the matmul rotation + row-wise quantize recipe, with the reference's own bounds
+    for case in golden["activation"]:
+        q, s = _cabi.convrot_quantize(case["x"].to(cuda_device), True)
+        q, s = q.cpu(), s.cpu()
+        assert (q != case["q_recipe"]).float().mean().item() < 2e-3
+        assert (q.int() - case["q_recipe"].int()).abs().max().item() <= 1
+        assert ((s - case["scale_recipe"]).abs() / case["scale_recipe"]).max().item() < 1e-2
+        assert q.abs().max().item() == 127  # the row maximum maps to +-127
+
+
+def test_quantizer_edge_cases(cuda_device):
+    import feather_ops_b200 as fo
+
+    zeros = torch.zeros((3, 512), device=cuda_device, dtype=torch.bfloat16)
+    q, s = fo.quantize_convrot_activation(zeros)
+    assert q.abs().max().item() == 0 and torch.equal(s.cpu(), torch.full((3,), 1e-30 * 0.0625))
+    with pytest.raises(RuntimeError, match="multiple of the ConvRot group size"):
+        fo.quantize_convrot_activation(torch.zeros((2, 300), device=cuda_device, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="x must be float16 or bfloat16"):
+        fo.quantize_convrot_activation(torch.zeros((2, 256), device=cuda_device, dtype=torch.float32))
+    q, s = fo.quantize_convrot_activation(torch.zeros((0, 256), device=cuda_device, dtype=torch.float16))
+    assert q.shape == (0, 256) and s.shape == (0,)
+    # full-size benchmark activation: 4096 x 3072 with outlier channels
+    x = o8.make_activation(4096, 3072, torch.bfloat16)
+    q_ref, s_ref = o8.convrot_quantize(x, True)
+    q, s = fo.quantize_convrot_activation(x.to(cuda_device))
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu(), s_ref)
+
+
+SHAPES = [(1, 64, 128), (17, 96, 64), (128, 128, 128), (67, 272, 304), (300, 516, 1040), (512, 1024, 2048), (4112, 1152, 1152)]
+
+
+def _gemm_case(m, n, k, transposed, out_dtype, seed):
+    gen = torch.Generator().manual_seed(seed)
+    w = torch.randint(-127, 128, (n, k), generator=gen, dtype=torch.int8)
+    kc, n_out = (n, k) if transposed else (k, n)
+    a = torch.randint(-127, 128, (m, kc), generator=gen, dtype=torch.int8)
+    a_scale = torch.rand(m, generator=gen) * 0.01 + 0.001
+    w_scale = None if transposed else torch.rand(n, generator=gen) * 0.01 + 0.001
+    bias = None if transposed else torch.randn(n, generator=gen).to(out_dtype)
+    return w, a, a_scale, w_scale, bias, n_out
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_against_the_fp64_oracle(cuda_device, shape, transposed, out_dtype):
+    m, n, k = shape
+    if (n if transposed else k) % 16:
+        pytest.skip("the contraction axis must be a multiple of 16")
+    w, a, a_scale, w_scale, bias, n_out = _gemm_case(m, n, k, transposed, out_dtype, seed=m + n)
+    ref = o8.int8_scaled_mm(a, w, a_scale, w_scale, bias, out_dtype, transposed)
+    dev = lambda t: None if t is None else t.to(cuda_device)  # noqa: E731
+    out = _cabi.int8_scaled_mm(dev(a), dev(o8.prepack_int8_weight(w)), dev(a_scale), dev(w_scale), dev(bias), out_dtype, transposed, n_out)
+    _cabi.assert_clean(STATUS)
+    assert _max_rel(out, ref) < 0.02
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_every_tile_in_both_directions(cuda_device, transposed):
+    from feather_ops_b200.tiles import INT8_TILES
+
+    m, n, k = (67, 272, 304)
+    w, a, a_scale, w_scale, bias, n_out = _gemm_case(m, n, k, transposed, torch.bfloat16, seed=7)
+    ref = o8.int8_scaled_mm(a, w, a_scale, w_scale, bias, torch.bfloat16, transposed)
+    dev = lambda t: None if t is None else t.to(cuda_device)  # noqa: E731
+    args = (dev(a), dev(o8.prepack_int8_weight(w)), dev(a_scale), dev(w_scale), dev(bias))
+    for tile in INT8_TILES:
+        out = _cabi.int8_scaled_mm(*args, torch.bfloat16, transposed, n_out, tile)
+        _cabi.assert_clean(STATUS)
+        assert _max_rel(out, ref) < 0.02
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_int32_accumulators_are_exact(cuda_device, transposed):
+    # unit scales and codes small enough that every accumulator is an integer below 2048: exact in fp16
+    gen = torch.Generator().manual_seed(2)
+    n, k, m = (256, 128, 130) if transposed else (128, 256, 130)
+    w = torch.randint(-3, 4, (n, k), generator=gen, dtype=torch.int8)
+    a = torch.randint(-3, 4, (m, n if transposed else k), generator=gen, dtype=torch.int8)
+    n_out = k if transposed else n
+    ones = torch.ones(max(m, n_out), device=cuda_device)
+    out = _cabi.int8_scaled_mm(a.to(cuda_device), o8.prepack_int8_weight(w).to(cuda_device), ones[:m].contiguous(),
+                               None if transposed else ones[:n_out].contiguous(), None, torch.float16, transposed, n_out)
+    acc = o8.int8_accumulators(a, w, transposed)
+    assert acc.abs().max().item() < 2048
+    assert torch.equal(out.cpu().float().long(), acc)
+
+
+def test_linear_and_dgrad_equal_their_compositions(cuda_device):
+    import feather_ops_b200 as fo
+    from feather_ops_b200 import int8_convrot as ic
+
+    gen = torch.Generator().manual_seed(4)
+    m, n, k = 200, 768, 512
+    x = torch.randn((2, m // 2, k), generator=gen).to(torch.bfloat16).to(cuda_device)
+    w = (torch.randn((n, k), generator=gen) * 0.02).to(torch.bfloat16).to(cuda_device)
+    bias = torch.randn(n, generator=gen).to(torch.bfloat16).to(cuda_device)
+    wq, ws = fo.quantize_convrot_weight(w)
+    packed = fo.prepack_int8_weight(wq)
+    assert torch.equal(fo.unpack_int8_weight(packed), wq)
+
+    y = fo.convrot_int8_linear(x, wq, ws, bias)
+    q, s = fo.quantize_convrot_activation(x.reshape(-1, k))
+    assert torch.equal(y, fo.int8_scaled_mm(q, packed, s, ws, bias).reshape(2, m // 2, n))
+    assert torch.equal(y, fo.convrot_int8_linear(x, packed, ws, bias, weight_packed=True))
+    # end to end against the unquantized product (reference bound: rel < 2e-2)
+    ref = x.float().reshape(-1, k) @ w.float().T + bias.float()
+    assert ((y.float().reshape(-1, n) - ref).norm() / ref.norm()).item() < 2e-2
+
+    g = torch.randn((m, n), generator=gen).to(torch.bfloat16).to(cuda_device)
+    dx = fo.convrot_int8_dgrad(g, wq, ws)
+    gq, gs = fo.quantize_convrot_activation(g, False, col_scale=ws)
+    composed = ic.rotate(fo.int8_scaled_mm(gq, packed, gs, None, None, torch.bfloat16, True), ic.build_hadamard(256, device=cuda_device, dtype=torch.bfloat16))
+    assert torch.equal(dx, composed)
+    ref_dx = g.float() @ w.float()
+    assert ((dx.float() - ref_dx).norm() / ref_dx.norm()).item() < 3e-2
+    _cabi.assert_clean(STATUS)
+
+
+def test_operator_errors(cuda_device):
+    import feather_ops_b200  # noqa: F401
+
+    op = torch.ops.feather_ops.int8_scaled_mm.default
+    a = torch.zeros((8, 64), device=cuda_device, dtype=torch.int8)
+    w = torch.zeros(64 * 32, device=cuda_device, dtype=torch.int8)
+    s = torch.ones(8, device=cuda_device)
+    c = torch.zeros((8, 32), device=cuda_device, dtype=torch.bfloat16)
+    tile = (4, 4, 2, 4, 4)
+    op(a, w, s, None, None, c, False, *tile)
+    with pytest.raises(RuntimeError, match="Unsupported config"):
+        op(a, w, s, None, None, c, False, 5, 5, 5, 5, 5)
+    with pytest.raises(RuntimeError, match="a must be int8"):
+        op(a.to(torch.uint8), w, s, None, None, c, False, *tile)
+    with pytest.raises(RuntimeError, match="weight_in \\* weight_out bytes"):
+        op(a, w[:100], s, None, None, c, False, *tile)
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        op(a[:, :40].contiguous(), torch.zeros(40 * 32, device=cuda_device, dtype=torch.int8), s, None, None, c, False, *tile)
+    with pytest.raises(RuntimeError, match="a_scale must have M elements"):
+        op(a, w, s[:4], None, None, c, False, *tile)
+
+
+def test_benchmark_shape_by_properties(cuda_device):
+    # 4096 x 3072 x 3072: quantize -> GEMM with the offline weight recipe; row sample against the fp64 oracle
+    import feather_ops_b200 as fo
+
+    x = o8.make_activation(4096, 3072, torch.bfloat16)
+    w = o8.make_weight(3072, 3072, torch.bfloat16)
+    wq, ws = o8.quantize_convrot_weight(w)
+    q_ref, s_ref = o8.convrot_quantize(x, True)
+    y = fo.convrot_int8_linear(x.to(cuda_device), wq.to(cuda_device), ws.to(cuda_device))
+    _cabi.assert_clean(STATUS)
+    rows = torch.randperm(4096, generator=torch.Generator().manual_seed(1))[:64]
+    ref = o8.int8_scaled_mm(q_ref[rows], wq, s_ref[rows], ws, None, torch.bfloat16)
+    assert _max_rel(y[rows.to(cuda_device)], ref) < 0.02
+    full = x.float()[rows] @ w.float().T
+    assert ((y[rows.to(cuda_device)].float().cpu() - full).norm() / full.norm()).item() < 2e-2

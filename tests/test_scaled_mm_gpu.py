@@ -1,0 +1,172 @@
+"""scaled_mm on the GPU against the CPU oracle, through the C ABI and through the torch operator.
+
+Shapes, dtype combinations and tolerances are the reference's (tests/test_scaled_mm_hip.py:8-32 there):
+Frobenius rel <= 0.01 and max-abs <= 2 (fp16) / 16 (bf16) against its naive path. Against the
+fp32-accumulate restatement the bound used here is much tighter (rel <= 1e-3): the only differences are
+the accumulation order and one-ulp output roundings.
+"""
+
+import pytest
+import torch
+
+from oracle import scaled_mm as osm
+from tests import _cabi
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 128, 128), (17, 96, 64), (128, 128, 128), (256, 256, 256), (512, 1024, 5120), (4111, 512, 256), (4112, 1152, 1152),
+          (4304, 4304, 1152), (5376, 512, 3072), (2048, 1024, 5120)]
+TAIL_SHAPE = (67, 272, 304)
+DTYPES = [(torch.float8_e5m2, torch.float16), (torch.float8_e5m2, torch.bfloat16), (torch.float8_e4m3fn, torch.bfloat16)]
+ATOL = {torch.float16: 2.0, torch.bfloat16: 16.0}
+STATUS = "feather_scaled_mm_status"
+
+
+def _compare(out, ref, out_dtype, rtol):
+    diff = (out.float().cpu() - ref.float()).abs()
+    rel = (diff.norm() / ref.float().norm().clamp(min=1e-6)).item()
+    assert rel <= rtol, f"rel={rel:.3g}"
+    assert diff.max().item() <= ATOL[out_dtype], f"max_abs={diff.max().item():.3g}"
+
+
+@pytest.mark.parametrize("a_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("b_dtype,out_dtype", DTYPES)
+@pytest.mark.parametrize("shape", SHAPES)
+def test_shapes_through_the_c_abi(cuda_device, shape, b_dtype, out_dtype, a_dtype):
+    m, n, k = shape
+    a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype)
+    out = _cabi.scaled_mm(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), bias.to(cuda_device), out_dtype)
+    _cabi.assert_clean(STATUS)
+    _compare(out, osm.scaled_mm_f32(a, packed, scale, bias, out_dtype, b_prepacked=True), out_dtype, 1e-3)
+    if m <= 512:  # the reference's own oracle, with the reference's tolerance
+        _compare(out, osm.scaled_mm_naive(a, packed, scale, bias, out_dtype, b_prepacked=True), out_dtype, 0.01)
+
+
+def test_every_tile_on_a_shape_with_a_tail_in_every_axis(cuda_device):
+    from feather_ops_b200.tiles import SCALED_MM_TILES
+
+    m, n, k = TAIL_SHAPE
+    a, packed, _, bias = osm.make_inputs(m, n, k, torch.float16, torch.float8_e5m2, torch.bfloat16)
+    scale = torch.tensor(0.75)
+    ref = osm.scaled_mm_f32(a, packed, scale, bias, torch.bfloat16, b_prepacked=True)
+    dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+    for tile in SCALED_MM_TILES:
+        out = _cabi.scaled_mm(*dev, torch.bfloat16, tile)
+        _cabi.assert_clean(STATUS)
+        _compare(out, ref, torch.bfloat16, 1e-3)
+
+
+def test_python_api_heuristic_optional_arguments_and_views(cuda_device):
+    import feather_ops_b200 as fo
+    from feather_ops_b200.scaled_mm import prepack_b_for_scaled_mm
+
+    for (m, n, k), scale_on, bias_on in (((96, 128, 64), False, False), ((4112, 1152, 1152), True, False), ((300, 2048, 512), True, True)):
+        a, packed, scale, bias = osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, with_scale=scale_on, with_bias=bias_on)
+        b = osm.unpack_b(packed, k)
+        packed_gpu = prepack_b_for_scaled_mm(b.to(cuda_device))
+        assert torch.equal(packed_gpu.cpu().view(torch.uint8), packed.view(torch.uint8))
+        out = fo.scaled_mm_hip(a.to(cuda_device), packed_gpu, None if scale is None else scale.to(cuda_device), None if bias is None else bias.to(cuda_device), torch.bfloat16)
+        _cabi.assert_clean(STATUS)
+        _compare(out, osm.scaled_mm_f32(a, packed, scale, bias, torch.bfloat16, b_prepacked=True), torch.bfloat16, 1e-3)
+    # a bias that is a 2-byte-aligned view takes the scalar load path
+    a, packed, scale, _ = osm.make_inputs(40, 64, 128, torch.float16, torch.float8_e5m2, torch.float16)
+    storage = torch.randn(65).to(torch.float16).to(cuda_device)
+    out = fo.scaled_mm_hip(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), storage[1:], torch.float16)
+    _compare(out, osm.scaled_mm_f32(a, packed, scale, storage[1:].cpu(), torch.float16, b_prepacked=True), torch.float16, 1e-3)
+    # an empty batch launches nothing
+    empty = fo.scaled_mm_hip(torch.zeros((0, 128), device=cuda_device, dtype=torch.float16), packed.to(cuda_device), None, None, torch.float16)
+    assert empty.shape == (0, 64)
+
+
+def test_golden_vectors_of_the_reference_naive_path(cuda_device, golden):
+    for case in golden["scaled_mm"]:
+        b_dtype = torch.float8_e5m2 if case["b_dtype"].endswith("e5m2") else torch.float8_e4m3fn
+        packed = case["b_prepacked"].view(b_dtype).to(cuda_device)
+        out = _cabi.scaled_mm(case["a"].to(cuda_device), packed, case["scale"].to(cuda_device), case["bias"].to(cuda_device), case["y"].dtype)
+        _compare(out, case["y"], case["y"].dtype, 0.01)
+
+
+def test_every_fp8_code_decodes_exactly(cuda_device):
+    # identity activations pick single weight entries: out[i, n] = up(B[i, n]) for all 256 codes of both formats
+    for b_dtype in (torch.float8_e5m2, torch.float8_e4m3fn):
+        codes = torch.arange(256, dtype=torch.uint8).repeat(16, 1)[:, :256].contiguous()  # [16, 256]: row i, column n -> code n
+        b = codes.view(b_dtype)
+        for a_dtype in (torch.float16, torch.bfloat16):
+            a = torch.eye(16, dtype=a_dtype)
+            out = _cabi.scaled_mm(a.to(cuda_device), osm.prepack_b(b).to(cuda_device), None, None, torch.float16 if a_dtype == torch.float16 else torch.bfloat16)
+            expect = b.to(torch.float32)
+            got = out.float().cpu()
+            finite = torch.isfinite(expect)
+            assert torch.equal(got[finite], expect[finite])  # every finite fp8 value is exact in fp16 and in bf16
+            assert not torch.isfinite(got[~finite]).any()  # inf and NaN codes stay non-finite (0 * inf in the other rows)
+
+
+def test_operator_errors(cuda_device):
+    import feather_ops_b200  # noqa: F401
+
+    op = torch.ops.feather_ops.scaled_mm.default
+    tile = (1, 8, 4, 8, 2, False)
+    a = torch.zeros((8, 64), device=cuda_device, dtype=torch.float16)
+    b = torch.zeros((8, 32, 16), device=cuda_device, dtype=torch.float8_e5m2)
+    c = torch.zeros((8, 32), device=cuda_device, dtype=torch.float16)
+    op(a, b, None, None, c, *tile)
+    with pytest.raises(RuntimeError, match="Unsupported config"):
+        op(a, b, None, None, c, 3, 3, 3, 3, 3, False)
+    with pytest.raises(RuntimeError, match="K must be divisible by 16"):
+        op(a[:, :40].contiguous(), b, None, None, c, *tile)
+    with pytest.raises(RuntimeError, match=r"a.stride\(0\) must equal K"):
+        op(a[:, :32], b, None, None, c, *tile)
+    with pytest.raises(RuntimeError, match="a must be float16 or bfloat16"):
+        op(a.float(), b, None, None, c, *tile)
+    with pytest.raises(RuntimeError, match="b_prepacked must be float8"):
+        op(a, b.view(torch.uint8), None, None, c, *tile)
+    with pytest.raises(RuntimeError, match="bias must have the same dtype as c"):
+        op(a, b, None, torch.zeros(32, device=cuda_device, dtype=torch.bfloat16), c, *tile)
+    with pytest.raises(RuntimeError, match="scale must have one element"):
+        op(a, b, torch.zeros(2, device=cuda_device), None, c, *tile)
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        op(a, b[:4].contiguous(), None, None, c, *tile)
+    with pytest.raises(RuntimeError, match=r"c.shape\[1\] must equal N"):
+        op(a, b, None, None, torch.zeros((8, 16), device=cuda_device, dtype=torch.float16), *tile)
+
+
+def test_compiled_caller_sees_one_opaque_node(cuda_device):
+    import feather_ops_b200 as fo
+
+    a, packed, scale, bias = osm.make_inputs(512, 1024, 512, torch.bfloat16, torch.float8_e5m2, torch.bfloat16)
+    args = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+
+    def run(a, b, s, bias):
+        return fo.scaled_mm_hip(a, b, s, bias, torch.bfloat16)
+
+    eager = run(*args)
+    traced = torch.compile(run, fullgraph=True, backend="aot_eager")(*args)
+    assert torch.equal(traced, eager)
+
+
+@pytest.mark.parametrize("n,k", [(12288, 3072), (3072, 12288), (9216, 3072)])
+def test_benchmark_shapes_by_properties(cuda_device, n, k):
+    # M = 4096 on the benchmark distribution (per-tensor scale = absmax / 57344). The full product is too
+    # large for the CPU oracle in a test, so: a row sample against the oracle, row independence (a row's
+    # result does not depend on which tile or launch it is in) and exact scaling by a power of two.
+    m = 4096
+    a, packed, scale, _ = osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, weight_std=0.02, with_bias=False)
+    a_gpu, packed_gpu, scale_gpu = a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device)
+    out = _cabi.scaled_mm(a_gpu, packed_gpu, scale_gpu, None, torch.bfloat16)
+    _cabi.assert_clean(STATUS)
+    assert torch.isfinite(out).all()
+    rows = torch.randperm(m, generator=torch.Generator().manual_seed(1))[:48]
+    ref = osm.scaled_mm_f32(a[rows], packed, scale, None, torch.bfloat16, b_prepacked=True)
+    _compare(out[rows.to(cuda_device)], ref, torch.bfloat16, 1e-3)
+    sub = _cabi.scaled_mm(a_gpu[1000:1130].contiguous(), packed_gpu, scale_gpu, None, torch.bfloat16)
+    assert torch.equal(sub, out[1000:1130])
+    doubled = _cabi.scaled_mm(a_gpu, packed_gpu, (scale_gpu * 2).contiguous(), None, torch.bfloat16)
+    assert torch.equal(doubled.float(), out.float() * 2)
+
+
+def test_reference_cpu_case_fp16(cuda_device):
+    # 256 x 4096 x 4096 fp16 on the benchmark distribution, whole output against the fp32 oracle
+    a, packed, scale, _ = osm.make_inputs(256, 4096, 4096, torch.float16, torch.float8_e5m2, torch.float16, weight_std=0.02, with_bias=False)
+    out = _cabi.scaled_mm(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), None, torch.float16)
+    _cabi.assert_clean(STATUS)
+    _compare(out, osm.scaled_mm_f32(a, packed, scale, None, torch.float16, b_prepacked=True), torch.float16, 1e-3)
