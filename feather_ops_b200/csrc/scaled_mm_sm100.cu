@@ -11,7 +11,8 @@
 //   * one persistent CTA per SM walks 128 x BN output tiles (m fastest so concurrently running CTAs share
 //     a weight panel in L2);
 //   * warp 0 is the TMA producer: per 64-wide k block it brings a 128 x 64 activation tile (128-byte
-//     swizzle, zero fill past M and K) and the raw fp8 cells [4][BN][16] into a ring of load slots;
+//     swizzle, zero fill past M and K) and the raw fp8 cells (boxes of 4 slabs x up to 128 cells, 2 KB
+//     contiguous per box row) into a ring of load slots;
 //   * eight upcast warps turn the raw cells into a K-major, 128-byte swizzled fp16 operand tile
 //     (e5m2 -> fp16 is a byte placement, e4m3 -> fp16 one cvt per pair; both exact for every code)
 //     in a second, shorter ring, fence it for the async proxy and hand it to the MMA warp;
@@ -40,7 +41,7 @@ constexpr int kBlockK = 64;            // one 128-byte swizzle span of 16-bit el
 constexpr int kSlabsPerBlock = kBlockK / 16;
 constexpr int kLoadStages = 4;
 constexpr int kOperandStages = 2;
-constexpr int kUpcastWarps = 8;
+constexpr int kUpcastWarps = 16;
 constexpr int kEpilogueWarps = 4;
 constexpr int kFirstEpilogueWarp = 2;
 constexpr int kFirstUpcastWarp = kFirstEpilogueWarp + kEpilogueWarps;
@@ -65,6 +66,9 @@ struct Params {
 template <int BN>
 struct Smem {
     static constexpr int kRawBytes = kSlabsPerBlock * BN * 16;
+    static constexpr int kBoxCells = BN < 128 ? BN : 128;          // 16-byte cells per TMA box row
+    static constexpr int kBoxes = BN / kBoxCells;                   // weight boxes per slot
+    static constexpr int kBoxBytes = kSlabsPerBlock * kBoxCells * 16;
     static constexpr int kOperandBytes = BN * 128;
     static constexpr int kAOff = 0;
     static constexpr int kOperandOff = kAOff + kLoadStages * kATileBytes;
@@ -193,7 +197,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!ok) break;
                     mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
                     tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
-                    tma_load_3d(smem + L::kRawOff + slot.idx * L::kRawBytes, &map_b, &load_full[slot.idx], 0, n0, kb * kSlabsPerBlock);
+#pragma unroll
+                    for (int box = 0; box < L::kBoxes; ++box) {
+                        tma_load_2d(smem + L::kRawOff + slot.idx * L::kRawBytes + box * L::kBoxBytes, &map_b, &load_full[slot.idx],
+                                    (n0 + box * L::kBoxCells) * 2, kb * kSlabsPerBlock);
+                    }
                     slot.advance(kLoadStages);
                 }
             }
@@ -295,12 +303,11 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else {
         // ------------------------------------------------------------------ upcast warps
+        // Work unit = one 16-byte cell (row n, slab j): unit u = t + i * threads, row = u % BN, slab = u / BN.
         const int t = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
-        constexpr int kRowGroups = (kUpcastWarps * 32) / BN;            // threads sharing one row
-        constexpr int kSlabsPerThread = kSlabsPerBlock / kRowGroups;
-        static_assert(kRowGroups >= 1 && kSlabsPerThread >= 1, "tile too narrow for the upcast warp layout");
-        const int row = t % BN;
-        const int first_slab = (t / BN) * kSlabsPerThread;
+        constexpr int kUpcastThreads = kUpcastWarps * 32;
+        constexpr int kUnits = BN * kSlabsPerBlock;
+        constexpr int kUnitsPerThread = (kUnits + kUpcastThreads - 1) / kUpcastThreads;
         Ring slot, operand;
         bool ok = true;
         for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
@@ -310,26 +317,34 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!ok) break;
                 const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
                 uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
-                uint4 cells[kSlabsPerThread];
+                uint4 cells[kUnitsPerThread];
 #pragma unroll
-                for (int j = 0; j < kSlabsPerThread; ++j) {
-                    cells[j] = *reinterpret_cast<const uint4*>(raw + ((first_slab + j) * BN + row) * 16);
+                for (int i = 0; i < kUnitsPerThread; ++i) {
+                    const int u = t + i * kUpcastThreads;
+                    if (kUnits % kUpcastThreads == 0 || u < kUnits) {
+                        const int row = u % BN;
+                        const int slab = u / BN;
+                        cells[i] = *reinterpret_cast<const uint4*>(raw + (row / L::kBoxCells) * L::kBoxBytes + (slab * L::kBoxCells + row % L::kBoxCells) * 16);
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < kSlabsPerThread; ++j) {
-                    const uint32_t w[4] = {cells[j].x, cells[j].y, cells[j].z, cells[j].w};
+                for (int i = 0; i < kUnitsPerThread; ++i) {
+                    const int u = t + i * kUpcastThreads;
+                    if (kUnits % kUpcastThreads != 0 && u >= kUnits) continue;
+                    const int row = u % BN;
+                    const int slab = u / BN;
+                    const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
                     uint32_t h[8];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        fp8x4_to_f16x4<kE5M2>(w[i], h[2 * i], h[2 * i + 1]);
+                    for (int q = 0; q < 4; ++q) {
+                        fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
                         if constexpr (kOperandBf16) {
-                            h[2 * i] = f16x2_to_bf16x2(h[2 * i]);
-                            h[2 * i + 1] = f16x2_to_bf16x2(h[2 * i + 1]);
+                            h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
+                            h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
                         }
                     }
-                    const int chunk = 2 * (first_slab + j);
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, chunk)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, chunk + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -391,11 +406,13 @@ bool launch_instance(const LaunchArgs& args) {
         }
     }
     {
+        // One slab row of the prepack is N contiguous 16-byte cells. Described as 8-byte elements so that a
+        // box row is up to 2048 contiguous bytes (128 cells) instead of one 16-byte cell per box row.
         const uint64_t k16_rows = static_cast<uint64_t>((args.K + 127) / 128) * 8;  // the prepack pads K to 128
-        const uint64_t dims[3] = {16, static_cast<uint64_t>(args.N), k16_rows};
-        const uint64_t strides[2] = {16, static_cast<uint64_t>(args.N) * 16};
-        const uint32_t box[3] = {16, BN, kSlabsPerBlock};
-        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.N) * 2, k16_rows};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.N) * 16};
+        const uint32_t box[2] = {static_cast<uint32_t>(L::kBoxCells * 2), kSlabsPerBlock};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
     }
 
     Params p{};
