@@ -317,7 +317,7 @@ def run_library(args):
                 "frac": achieved / peak,
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                 "peak_source": peak_source,
-                "kernel": "feather::smm::scaled_mm_kernel<256, e5m2, bf16 operands, bf16 out>",
+                "kernel": "feather::smm::scaled_mm_pair_kernel<e5m2, bf16 operands, bf16 out> (CTA pairs, 256x256 tiles)",
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "algorithmic_bytes": ALGORITHMIC_BYTES,
             },

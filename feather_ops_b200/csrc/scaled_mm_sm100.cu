@@ -33,6 +33,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 namespace feather {
 namespace smm {
 
@@ -372,6 +374,268 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair version (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile. CTA r of the
+// pair loads activation rows [128 r, 128 r + 128) and weight columns [128 r, 128 r + 128) of the tile,
+// converts only that half of the weight tile, and receives accumulator rows [128 r, 128 r + 128) x 256
+// columns in its own tensor memory. The UMMA (M = 256, N = 256, K = 16) is issued by CTA 0 and reads both
+// CTAs' shared memory, so per SM the converted-operand traffic and the conversion work are half of the
+// one-CTA kernel's for the same number of flops. Barriers that CTA 0's MMA thread waits on live in CTA 0
+// and are arrived on remotely by CTA 1's warps; barriers that release slots or publish an accumulator are
+// signalled in both CTAs by two commits.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kPairLoadStages = 6;     // measured: 6/3 = 1.30 PFLOP/s, 5/4 = 1.28, 4/3 = 1.22, 6/2 and 7/2 = 1.15
+constexpr int kPairOperandStages = 3;
+constexpr int kPairHalfN = 128;
+constexpr int kPairN = 2 * kPairHalfN;
+
+struct PairSmem {
+    static constexpr int kRawBytes = kSlabsPerBlock * kPairHalfN * 16;   // 8 KB
+    static constexpr int kOperandBytes = kPairHalfN * 128;               // 16 KB
+    static constexpr int kAOff = 0;
+    static constexpr int kOperandOff = kAOff + kPairLoadStages * kATileBytes;
+    static constexpr int kRawOff = kOperandOff + kPairOperandStages * kOperandBytes;
+    static constexpr int kBarOff = kRawOff + kPairLoadStages * kRawBytes;
+    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 4;
+    static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    using L = PairSmem;
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint64_t* const load_full = bars;
+    uint64_t* const load_empty = load_full + kPairLoadStages;
+    uint64_t* const operand_full = load_empty + kPairLoadStages;      // used in CTA 0 only
+    uint64_t* const operand_empty = operand_full + kPairOperandStages;
+    uint64_t* const tmem_full = operand_empty + kPairOperandStages;
+    uint64_t* const tmem_empty = tmem_full + 2;                        // used in CTA 0 only
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const uint32_t cta = cluster_cta_rank();
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kPairLoadStages; ++s) {
+            mbar_init(&load_full[s], 1);
+            mbar_init(&load_empty[s], 1);
+        }
+        for (int s = 0; s < kPairOperandStages; ++s) {
+            mbar_init(&operand_full[s], 2 * kUpcastWarps);
+            mbar_init(&operand_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * kPairN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers are initialised before anything is signalled across CTAs
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int tiles_n = (p.N + kPairN - 1) / kPairN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int first_tile = static_cast<int>(blockIdx.x) / 2;
+    const int tile_step = static_cast<int>(gridDim.x) / 2;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (this CTA's halves)
+        if (elect_one()) {
+            Ring slot;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+                const int n0 = (tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
+                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
+                    tma_load_2d(smem + L::kRawOff + slot.idx * L::kRawBytes, &map_b, &load_full[slot.idx], n0 * 2, kb * kSlabsPerBlock);
+                    slot.advance(kPairLoadStages);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (CTA 0 of the pair)
+        if (cta == 0 && elect_one()) {
+            Ring slot, operand, acc;
+            bool ok = true;
+            // every barrier the UMMA completion has to reach, in this CTA and at the same offset in the peer
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                ok = guard.wait(&tmem_empty[acc.idx], acc.phase ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc.idx * kPairN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 1) &&
+                         guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
+                    const uint32_t b_addr = smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        umma_f16_pair(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
+                                      (kb | k) != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (uint32_t dst = 0; dst < 2; ++dst) {
+                        umma_commit_pair(map_to_cta(smem_u32(&load_empty[slot.idx]), dst));
+                        umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
+                    }
+                    slot.advance(kPairLoadStages);
+                    operand.advance(kPairOperandStages);
+                }
+                if (!ok) break;
+#pragma unroll
+                for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc.idx]), dst));
+                acc.advance(2);
+            }
+        }
+    } else if (warp < kFirstUpcastWarp) {
+        // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
+        const int quarter = warp % 4;
+        const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+        Ring acc;
+        bool ok = true;
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+            const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+            const int n0 = (tile / tiles_m) * kPairN;
+            ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+#pragma unroll 1
+            for (int c = 0; c < kPairN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_wait_ld();
+                if (c == kPairN / 32 - 1) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), 0));
+                }
+                const int col0 = n0 + c * 32;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int col = col0 + g * 8;
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        o[i] = pack_out<kOutBf16>(__uint_as_float(v[g * 8 + 2 * i]) * scale, __uint_as_float(v[g * 8 + 2 * i + 1]) * scale);
+                    }
+                    if (p.bias != nullptr && col < p.N) {
+                        uint32_t bw[4];
+                        if (p.bias_vec) {
+                            const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                            bw[0] = b4.x;
+                            bw[1] = b4.y;
+                            bw[2] = b4.z;
+                            bw[3] = b4.w;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                bw[i] = static_cast<uint32_t>(__ldg(p.bias + col + 2 * i)) | (static_cast<uint32_t>(__ldg(p.bias + col + 2 * i + 1)) << 16);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 x = unpack_out<kOutBf16>(o[i]);
+                            const float2 b = unpack_out<kOutBf16>(bw[i]);
+                            o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
+                        }
+                    }
+                    if (row < p.M && col < p.N) {
+                        *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            acc.advance(2);
+        }
+    } else {
+        // ------------------------------------------------------------------ upcast warps (this CTA's weight half)
+        // One 16-byte cell per thread and slot: cell u = (slab u / 128, row u % 128).
+        const int t = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
+        constexpr int kUpcastThreads = kUpcastWarps * 32;
+        constexpr int kUnits = kPairHalfN * kSlabsPerBlock;
+        constexpr int kUnitsPerThread = (kUnits + kUpcastThreads - 1) / kUpcastThreads;
+        static_assert(kUnits % kUpcastThreads == 0, "the weight half tile must split evenly over the upcast threads");
+        Ring slot, operand;
+        bool ok = true;
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                     guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                if (!ok) break;
+                const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                uint4 cells[kUnitsPerThread];
+#pragma unroll
+                for (int i = 0; i < kUnitsPerThread; ++i) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kUpcastThreads) * 16);
+#pragma unroll
+                for (int i = 0; i < kUnitsPerThread; ++i) {
+                    const int u = t + i * kUpcastThreads;
+                    const int row = u % kPairHalfN;
+                    const int slab = u / kPairHalfN;
+                    const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
+                    uint32_t h[8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
+                        if constexpr (kOperandBf16) {
+                            h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
+                            h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
+                slot.advance(kPairLoadStages);
+                operand.advance(kPairOperandStages);
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+    }
+    cluster_sync_all();  // neither CTA frees tensor memory while the pair's UMMAs may still write to it
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2 * kPairN);
+    }
+}
+
 struct LaunchArgs {
     const uint16_t* a;
     const uint8_t* b;
@@ -434,6 +698,102 @@ bool launch_instance(const LaunchArgs& args) {
     return cudaGetLastError() == cudaSuccess;
 }
 
+// FEATHER_SCALED_MM_PAIR=0 keeps the one-CTA kernel for every shape (A/B measurements).
+inline bool pair_kernel_enabled() {
+    static const bool enabled = [] {
+        const char* v = getenv("FEATHER_SCALED_MM_PAIR");
+        return v == nullptr || v[0] != '0';
+    }();
+    return enabled;
+}
+
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+bool launch_pair_instance(const LaunchArgs& args) {
+    using L = PairSmem;
+    auto* kernel = &scaled_mm_pair_kernel<kE5M2, kOperandBf16, kOutBf16>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+    CUtensorMap map_a, map_b;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.K) * 2};
+        const uint32_t box[2] = {kBlockK, kBlockM};
+        if (!encode_map(&map_a, args.a_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.a, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B)) {
+            return false;
+        }
+    }
+    {
+        const uint64_t k16_rows = static_cast<uint64_t>((args.K + 127) / 128) * 8;
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.N) * 2, k16_rows};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.N) * 16};
+        const uint32_t box[2] = {kPairHalfN * 2, kSlabsPerBlock};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    }
+    Params p{};
+    p.scale = args.scale;
+    p.bias = args.bias;
+    p.c = args.c;
+    p.M = static_cast<int>(args.M);
+    p.N = static_cast<int>(args.N);
+    p.K = static_cast<int>(args.K);
+    p.tiles_m = static_cast<int>((args.M + 2 * kBlockM - 1) / (2 * kBlockM));
+    p.tiles_n = static_cast<int>((args.N + kPairN - 1) / kPairN);
+    p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
+    p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    // A persistent grid must not exceed what can be resident at once: CTA pairs need both SMs of a TPC, and
+    // parts with an odd number of enabled SMs in some TPCs hold fewer pairs than sm_count / 2.
+    static int resident_pairs[64] = {};
+    if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = L::kDynamic;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = device_info().sm_count / 2;
+        }
+        resident_pairs[dev] = clusters;
+        if (getenv("FEATHER_DEBUG") != nullptr) fprintf(stderr, "feather: %d CTA pairs resident per launch\n", clusters);
+    }
+    const int pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : device_info().sm_count / 2;
+    const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
+    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+bool launch_pair(const LaunchArgs& args) {
+    const bool operand_bf16 = args.a_bf16;
+#define FEATHER_SMM_PAIR_CASE(E5, OB, OUT)                                 \
+    if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
+        return launch_pair_instance<E5, OB, OUT>(args);                     \
+    }
+    FEATHER_SMM_PAIR_CASE(true, false, true)
+    FEATHER_SMM_PAIR_CASE(true, false, false)
+    FEATHER_SMM_PAIR_CASE(false, false, true)
+    FEATHER_SMM_PAIR_CASE(false, false, false)
+    FEATHER_SMM_PAIR_CASE(true, true, true)
+    FEATHER_SMM_PAIR_CASE(true, true, false)
+    FEATHER_SMM_PAIR_CASE(false, true, true)
+    FEATHER_SMM_PAIR_CASE(false, true, false)
+#undef FEATHER_SMM_PAIR_CASE
+    return false;
+}
+
 template <int BN>
 bool launch_for_block_n(const LaunchArgs& args) {
     const bool operand_bf16 = args.a_bf16;  // the weights are decoded to the activation's format
@@ -472,7 +832,11 @@ extern "C" bool launch_scaled_mm(const uint16_t* a, const uint8_t* b_prepacked, 
     if (M == 0) return true;
     const smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
                                use_fp8_e5m2, a_bf16, output_bf16, stream};
-    if (block_n >= 256) return smm::launch_for_block_n<256>(args);
+    if (block_n >= 256) {
+        // a pair tile is 256 rows tall: worth it as soon as there is more than one 128-row tile
+        if (M > smm::kBlockM && smm::pair_kernel_enabled()) return smm::launch_pair(args);
+        return smm::launch_for_block_n<256>(args);
+    }
     if (block_n >= 128) return smm::launch_for_block_n<128>(args);
     return smm::launch_for_block_n<64>(args);
 }
