@@ -408,6 +408,308 @@ __global__ void __launch_bounds__(kThreads, 1) int8_mm_kernel(const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair version (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile. CTA r loads
+// activation rows [128 r, +128) by TMA and re-lays out weight rows (output columns) [128 r, +128) of the
+// tile; the UMMA (M = 256, N = 256, K = 32) is issued by CTA 0 and reads both CTAs' shared memory, so each
+// SM moves half of the weight tile per UMMA. The re-layout goes through registers: a thread owns four
+// operand rows x one 16-byte chunk, loads the four 16-byte micro-tiles that hold them (the loads of the
+// next three k blocks are in flight while one is stored, in register sets with static roles), picks
+// dwords (forward) or transposes 4x4 bytes (backward), and stores with eight lanes covering one full
+// 128-byte swizzled row, which is conflict free.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kPairAStages = 6;
+constexpr int kPairOperandStages = 5;
+constexpr int kPairHalfN = 128;
+constexpr int kPairN = 2 * kPairHalfN;
+constexpr int kPairRelayoutWarps = 8;
+constexpr int kPairThreads = 32 * (kFirstRelayoutWarp + kPairRelayoutWarps);
+
+struct PairSmem {
+    static constexpr int kOperandBytes = kPairHalfN * 128;  // 16 KB
+    static constexpr int kAOff = 0;
+    static constexpr int kOperandOff = kAOff + kPairAStages * kATileBytes;
+    static constexpr int kBarOff = kOperandOff + kPairOperandStages * kOperandBytes;
+    static constexpr int kNumBars = 2 * kPairAStages + 2 * kPairOperandStages + 4;
+    static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <bool kTransposedB, bool kOutBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
+    using L = PairSmem;
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint64_t* const a_full = bars;                                   // local: TMA bytes of this CTA's rows
+    uint64_t* const a_empty = a_full + kPairAStages;                 // signalled in both CTAs by CTA 0's commits
+    uint64_t* const operand_full = a_empty + kPairAStages;           // CTA 0 only: both CTAs' warps arrive here
+    uint64_t* const operand_empty = operand_full + kPairOperandStages;
+    uint64_t* const tmem_full = operand_empty + kPairOperandStages;
+    uint64_t* const tmem_empty = tmem_full + 2;                      // CTA 0 only
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const uint32_t cta = cluster_cta_rank();
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kPairAStages; ++s) {
+            mbar_init(&a_full[s], 1);
+            mbar_init(&a_empty[s], 1);
+        }
+        for (int s = 0; s < kPairOperandStages; ++s) {
+            // the operand slot is complete when both CTAs' re-layout warps AND both CTAs' activation tiles are in:
+            // the re-layout warps wait for their CTA's activation tile before they arrive
+            mbar_init(&operand_full[s], 2 * kPairRelayoutWarps);
+            mbar_init(&operand_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_a);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * kPairN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int tiles_n = (p.N_out + kPairN - 1) / kPairN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int first_tile = static_cast<int>(blockIdx.x) / 2;
+    const int tile_step = static_cast<int>(gridDim.x) / 2;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (this CTA's activation rows)
+        if (elect_one()) {
+            Ring slot;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&a_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&a_full[slot.idx], kATileBytes);
+                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &a_full[slot.idx], kb * kBlockK, m0);
+                    slot.advance(kPairAStages);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (CTA 0 of the pair)
+        if (cta == 0 && elect_one()) {
+            Ring slot, operand, acc;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                ok = guard.wait(&tmem_empty[acc.idx], acc.phase ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc.idx * kPairN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&a_full[slot.idx], slot.phase, kSiteLoadFull) &&
+                         guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
+                    const uint32_t b_addr = smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 32; ++k) {
+                        umma_i8_pair(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
+                                     (kb | k) != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (uint32_t dst = 0; dst < 2; ++dst) {
+                        umma_commit_pair(map_to_cta(smem_u32(&a_empty[slot.idx]), dst));
+                        umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
+                    }
+                    slot.advance(kPairAStages);
+                    operand.advance(kPairOperandStages);
+                }
+                if (!ok) break;
+#pragma unroll
+                for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc.idx]), dst));
+                acc.advance(2);
+            }
+        }
+    } else if (warp < kFirstRelayoutWarp) {
+        // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
+        const int quarter = warp % 4;
+        const bool wide_rows = (p.N_out % 8) == 0;
+        Ring acc;
+        bool ok = true;
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+            const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+            const int n0 = (tile / tiles_m) * kPairN;
+            ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = m0 + quarter * 32 + lane;
+            const float row_scale = row < p.M ? __ldg(p.a_scale + row) : 0.0f;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N_out;
+#pragma unroll 1
+            for (int c = 0; c < kPairN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_wait_ld();
+                if (c == kPairN / 32 - 1) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), 0));
+                }
+                const int col0 = n0 + c * 32;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int col = col0 + g * 4;
+                    if (col >= p.N_out) continue;
+                    float f[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float value = static_cast<float>(static_cast<int32_t>(v[g * 4 + i])) * row_scale;
+                        if constexpr (!kTransposedB) {
+                            if (p.b_scale != nullptr) value *= __ldg(p.b_scale + col + i);
+                            if (p.bias != nullptr) value += out_bits_to_float<kOutBf16>(__ldg(p.bias + col + i));
+                        }
+                        f[i] = value;
+                    }
+                    v[g * 4] = pack_out<kOutBf16>(f[0], f[1]);
+                    v[g * 4 + 1] = pack_out<kOutBf16>(f[2], f[3]);
+                }
+                if (row < p.M) {
+                    if (wide_rows) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (col0 + g * 8 < p.N_out) {
+                                *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = make_uint4(v[g * 8], v[g * 8 + 1], v[g * 8 + 4], v[g * 8 + 5]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            if (col0 + g * 4 < p.N_out) {
+                                *reinterpret_cast<uint2*>(c_row + col0 + g * 4) = make_uint2(v[g * 4], v[g * 4 + 1]);
+                            }
+                        }
+                    }
+                }
+            }
+            acc.advance(2);
+        }
+    } else {
+        // ------------------------------------------------------------------ weight re-layout warps (this CTA's 128 operand rows)
+        // thread = (row group g: operand rows 4 g .. 4 g + 3, chunk c: contraction bytes 16 c .. 16 c + 15)
+        // A quarter warp covers 4 chunks x 2 row groups: its eight 16-byte stores land in eight different
+        // bank groups (rows 4 apart flip bit 2 of the swizzle phase), and a warp's loads cover whole 128-byte
+        // lines of the prepack (8 consecutive micro-tiles of 4 contraction steps).
+        const int rw = warp - kFirstRelayoutWarp;
+        const int chunk = (lane & 3) + 4 * (rw & 1);
+        const int group = (lane >> 2) + 8 * (rw >> 1);  // 0..31
+        const uint4* const tiles = reinterpret_cast<const uint4*>(p.b);
+        const int k4_total = p.K / 4;
+        const int out4_total = p.N_out / 4;
+
+        auto fetch = [&](int tile, int kb, uint4 (&m)[4]) {
+            const int out4 = ((tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN) / 4 + group;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int kc4 = kb * (kBlockK / 4) + chunk * 4 + j;
+                const bool live = out4 < out4_total && kc4 < k4_total;
+                m[j] = live ? __ldg(tiles + static_cast<int64_t>(kc4) * p.stride_kc + static_cast<int64_t>(out4) * p.stride_out) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+
+        // Register pipeline: kPrefetch register sets, used round robin with static indices (the loop over the
+        // sets is fully unrolled, no set is ever copied: a copy would wait for the load it copies). Set d holds
+        // the micro-tiles of k block `it` with it % kPrefetch == d and is refilled for k block it + kPrefetch
+        // right after it has been stored, so kPrefetch - 1 k blocks of loads are always in flight.
+        constexpr int kPrefetch = 4;  // measured: 2, 4 and 6 sets are within 5 % of each other
+        Ring slot, operand;
+        bool ok = true;
+        int fetch_tile = first_tile;  // cursor of the load stream
+        int fetch_kb = 0;
+        int store_tile = first_tile;  // cursor of the store stream
+        int store_kb = 0;
+        uint4 pre[kPrefetch][4];
+#pragma unroll
+        for (int d = 0; d < kPrefetch; ++d) {
+            if (fetch_tile < num_tiles) fetch(fetch_tile, fetch_kb, pre[d]);
+            if (++fetch_kb == num_kb) {
+                fetch_kb = 0;
+                fetch_tile += tile_step;
+            }
+        }
+        while (ok && store_tile < num_tiles) {
+#pragma unroll
+            for (int d = 0; d < kPrefetch; ++d) {
+                if (!ok || store_tile >= num_tiles) break;
+                ok = guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                if (!ok) break;
+                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                uint32_t rows[4][4];  // rows[j][r]: contraction bytes 4 j .. 4 j + 3 of operand row 4 group + r
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t in[4] = {pre[d][j].x, pre[d][j].y, pre[d][j].z, pre[d][j].w};
+                    if constexpr (kTransposedB) {
+                        transpose4x4(in, rows[j]);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) rows[j][r] = in[r];
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(group * 4 + r, chunk)) = make_uint4(rows[0][r], rows[1][r], rows[2][r], rows[3][r]);
+                }
+                // refill this set for the k block kPrefetch ahead
+                if (fetch_tile < num_tiles) fetch(fetch_tile, fetch_kb, pre[d]);
+                if (++fetch_kb == num_kb) {
+                    fetch_kb = 0;
+                    fetch_tile += tile_step;
+                }
+                fence_proxy_async_smem();
+                // the activation tile of this k block must have landed in this CTA before the slot is published
+                ok = guard.wait(&a_full[slot.idx], slot.phase, kSiteLoadFull, 2);
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
+                slot.advance(kPairAStages);
+                operand.advance(kPairOperandStages);
+                if (++store_kb == num_kb) {
+                    store_kb = 0;
+                    store_tile += tile_step;
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+    }
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2 * kPairN);
+    }
+}
+
 struct LaunchArgs {
     const int8_t* a;
     const uint8_t* b;
@@ -460,6 +762,71 @@ bool launch_instance(const LaunchArgs& args) {
     return cudaGetLastError() == cudaSuccess;
 }
 
+template <bool kTransposedB, bool kOutBf16>
+bool launch_pair_instance(const LaunchArgs& args) {
+    using L = PairSmem;
+    auto* kernel = &int8_mm_pair_kernel<kTransposedB, kOutBf16>;
+    static bool configured[64] = {};
+    static int resident_pairs[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
+        // a persistent grid must fit at once: pairs need both SMs of a TPC
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
+        config.blockDim = dim3(kPairThreads);
+        config.dynamicSmemBytes = L::kDynamic;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = device_info().sm_count / 2;
+        }
+        resident_pairs[dev] = clusters;
+        configured[dev] = true;
+    }
+    CUtensorMap map_a;
+    const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(args.K)};
+    const uint32_t box[2] = {kBlockK, kBlockM};
+    if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+
+    Params p{};
+    p.b = args.b;
+    p.a_scale = args.a_scale;
+    p.b_scale = args.b_scale;
+    p.bias = args.bias;
+    p.c = args.c;
+    p.M = static_cast<int>(args.M);
+    p.N_out = static_cast<int>(args.N_out);
+    p.K = static_cast<int>(args.K);
+    p.stride_kc = args.stride_kc;
+    p.stride_out = args.stride_out;
+    p.tiles_m = static_cast<int>((args.M + 2 * kBlockM - 1) / (2 * kBlockM));
+    p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
+    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int pairs = resident_pairs[dev];
+    const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
+    kernel<<<grid, kPairThreads, L::kDynamic, args.stream>>>(map_a, p);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+bool launch_pair(const LaunchArgs& args) {
+    if (args.transposed_b) {
+        return args.out_bf16 ? launch_pair_instance<true, true>(args) : launch_pair_instance<true, false>(args);
+    }
+    return args.out_bf16 ? launch_pair_instance<false, true>(args) : launch_pair_instance<false, false>(args);
+}
+
 template <int BN>
 bool launch_for_block_n(const LaunchArgs& args) {
     if (args.transposed_b) {
@@ -487,7 +854,11 @@ extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const f
     if (M == 0) return true;
     const i8mm::LaunchArgs args{a, b, a_scale, b_scale, bias, c, M, N_out, K_contract, b_stride_kc, b_stride_out,
                                 transposed_b, output_dtype != 0, stream};
-    if (block_n >= 256) return i8mm::launch_for_block_n<256>(args);
+    if (block_n >= 256) {
+        // a pair tile is 256 rows tall: worth it as soon as there is more than one 128-row tile
+        if (M > i8mm::kBlockM) return i8mm::launch_pair(args);
+        return i8mm::launch_for_block_n<256>(args);
+    }
     if (block_n >= 128) return i8mm::launch_for_block_n<128>(args);
     return i8mm::launch_for_block_n<64>(args);
 }
