@@ -6,7 +6,6 @@
 // csrc/hip_kernel_int8.cu (:646-704 the radix-4 rotation, :779-865 the kernel, :869-924 the C ABI).
 // The arithmetic is reproduced operation for operation, because the int8 codes have to be reproducible:
 //
-//   * a group lives in one warp, eight consecutive values per lane (element = lane * 8 + i);
 //   * four radix-4 stages, one per base-4 digit of the element index, lowest digit first; with the four
 //     members of a butterfly in index order a0..a3, the member with digit d becomes
 //     ((a0 + a1) + a2) + a3 - 2 * a[3 - d], all in fp32;
@@ -15,11 +14,20 @@
 //     scale is divisor / 16 when rotating (the 1 / sqrt(256) normalization folded in), divisor otherwise;
 //   * without rotation an optional per-column multiplier is applied first and rounded to the input dtype.
 //
-// The pass is HBM bound (2 bytes in, 1 byte out per element): lanes load 16 bytes and store 8, a warp
-// keeps its groups in registers between the absmax and the quantize step (up to four groups, i.e. rows up
-// to 32768 wide with 32 warps), and wider rows recompute the groups from global memory, which is L2
-// resident by then. One CTA owns one or more whole rows, so the only reduction is a per-row maximum
-// across the CTA's warps.
+// Data movement is where this differs from the reference. There a group lives in one wave, eight values per
+// lane, and two of the four stages fetch their butterfly members with cross-lane shuffles (72 shuffles per
+// lane and group). On B200 that makes the pass shuffle bound (one warp shuffle per clock and SM) at about an
+// eighth of the HBM rate. Here a group lives in a half warp, sixteen consecutive values per lane, so two
+// digits are inside the lane: stages 0 and 1 run on registers, the 16 x 16 value matrix is transposed
+// through (bank-conflict-free, padded) shared memory, stages 2 and 3 run on registers again, and the
+// rounded 16-bit results are transposed back so that every lane ends up with the sixteen consecutive
+// outputs it stores as one 16-byte vector. No shuffle is used for the rotation.
+//
+// The pass is HBM bound (2 bytes in, 1 byte out per element). A warp keeps its groups as packed 16-bit
+// values in registers between the absmax and the quantize step (up to four rounds of two groups, i.e. rows
+// up to 32768 wide with 16 warps per row); wider rows recompute the groups from global memory, which is L2
+// resident by then. One CTA owns one or more whole rows, so the only reduction is a per-row maximum across
+// the CTA's warps.
 #include "feather_host.h"
 
 #include <cuda_bf16.h>
@@ -29,9 +37,12 @@ namespace feather {
 namespace quant {
 
 constexpr int kGroup = 256;
-constexpr int kPerLane = 8;
-constexpr int kMaxWarpsPerRow = 32;
-constexpr int kCachedGroups = 4;
+constexpr int kPerLane = 16;          // consecutive values of one lane
+constexpr int kMaxWarpsPerRow = 16;   // a warp handles two groups per round
+constexpr int kCachedRounds = 4;
+constexpr int kMaxWarpsPerCta = 16;
+constexpr int kPadded = 17;           // row pitch (in words) of the transpose buffer
+constexpr int kRegionWords = 16 * kPadded;
 
 template <bool kFp16>
 __device__ __forceinline__ float to_float(uint16_t bits) {
@@ -42,14 +53,19 @@ __device__ __forceinline__ float to_float(uint16_t bits) {
     }
 }
 
+template <bool kFp16>
+__device__ __forceinline__ uint16_t to_bits(float v) {
+    if constexpr (kFp16) {
+        return __half_as_ushort(__float2half_rn(v));
+    } else {
+        return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    }
+}
+
 // Round to the input dtype (nearest even) and come back to fp32.
 template <bool kFp16>
 __device__ __forceinline__ float round_to_input(float v) {
-    if constexpr (kFp16) {
-        return __half2float(__float2half_rn(v));
-    } else {
-        return __bfloat162float(__float2bfloat16_rn(v));
-    }
+    return to_float<kFp16>(to_bits<kFp16>(v));
 }
 
 __device__ __forceinline__ float butterfly(float a0, float a1, float a2, float a3, int digit) {
@@ -57,154 +73,171 @@ __device__ __forceinline__ float butterfly(float a0, float a1, float a2, float a
     return (((a0 + a1) + a2) + a3) - 2.0f * mirrored;
 }
 
-// In-register group-256 regular Hadamard. `v[i]` is element `lane * 8 + i`.
-__device__ __forceinline__ void hadamard256(float (&v)[kPerLane], int lane) {
-    // digit 0 (stride 1): members are four consecutive registers
-    {
-        float r[kPerLane];
+// Two radix-4 stages over the sixteen values of a lane: first the low index digit (members are four
+// consecutive registers), then the high one (members are registers q, q + 4, q + 8, q + 12).
+__device__ __forceinline__ void two_stages(float (&v)[kPerLane]) {
+    float r[kPerLane];
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
-            const int b = i & 4;
-            r[i] = butterfly(v[b], v[b + 1], v[b + 2], v[b + 3], i & 3);
-        }
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) v[i] = r[i];
+    for (int i = 0; i < kPerLane; ++i) {
+        const int b = i & ~3;
+        r[i] = butterfly(v[b], v[b + 1], v[b + 2], v[b + 3], i & 3);
     }
-    // digit 1 (stride 4): registers {q, q + 4} of the even lane, then of the odd lane
-    {
-        float other[kPerLane];
 #pragma unroll
-        for (int i = 0; i < kPerLane; ++i) other[i] = __shfl_xor_sync(0xffffffffu, v[i], 1);
-        const bool odd = (lane & 1) != 0;
-        float r[kPerLane];
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
-            const int q = i & 3;
-            const float a0 = odd ? other[q] : v[q];
-            const float a1 = odd ? other[q + 4] : v[q + 4];
-            const float a2 = odd ? v[q] : other[q];
-            const float a3 = odd ? v[q + 4] : other[q + 4];
-            const int digit = (odd ? 2 : 0) + (i >> 2);
-            r[i] = butterfly(a0, a1, a2, a3, digit);
-        }
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) v[i] = r[i];
-    }
-    // digits 2 and 3 (strides 16 and 64): members sit in the same register of four different lanes
-#pragma unroll
-    for (int stage = 0; stage < 2; ++stage) {
-        const int lane_step = 2 << (2 * stage);
-        const int digit = (lane >> (1 + 2 * stage)) & 3;
-        float r[kPerLane];
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) {
-            const float a0 = __shfl_xor_sync(0xffffffffu, v[i], lane_step * digit);
-            const float a1 = __shfl_xor_sync(0xffffffffu, v[i], lane_step * (digit ^ 1));
-            const float a2 = __shfl_xor_sync(0xffffffffu, v[i], lane_step * (digit ^ 2));
-            const float a3 = __shfl_xor_sync(0xffffffffu, v[i], lane_step * (digit ^ 3));
-            r[i] = butterfly(a0, a1, a2, a3, digit);
-        }
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) v[i] = r[i];
+    for (int i = 0; i < kPerLane; ++i) {
+        const int q = i & 3;
+        v[i] = butterfly(r[q], r[q + 4], r[q + 8], r[q + 12], i >> 2);
     }
 }
 
-// Load one group's eight values of this lane, apply the column multiplier or the rotation, and round to
-// the input dtype. Returns the lane's maximum magnitude through `amax`.
+// Produce one group for one half warp: load this lane's sixteen consecutive values, apply the column
+// multiplier or the rotation, round to the input dtype. `packed` receives the lane's sixteen consecutive
+// results as 16-bit patterns, `amax` the running maximum magnitude. `region` is this half warp's transpose
+// buffer. Every lane of the warp must call this together (it synchronizes the warp); `live` says whether
+// the half warp has a group at all.
 template <bool kFp16>
-__device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, const float* __restrict__ col_scale, int base, int lane,
-                                        bool rotate, float (&v)[kPerLane], float& amax) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x_row + base));
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+__device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, const float* __restrict__ col_scale, int base, int l, bool live,
+                                        bool rotate, float* region, uint32_t (&packed)[8], float& amax) {
+    float v[kPerLane];
+    {
+        uint4 raw[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+        if (live) {
+            raw[0] = __ldg(reinterpret_cast<const uint4*>(x_row + base));
+            raw[1] = __ldg(reinterpret_cast<const uint4*>(x_row + base + 8));
+        }
+        const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) v[i] = to_float<kFp16>(static_cast<uint16_t>(w[i / 2] >> (16 * (i % 2))));
+    }
+    if (!rotate) {
+        if (col_scale != nullptr && live) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float4 s = __ldg(reinterpret_cast<const float4*>(col_scale + base + 4 * c));
+                v[4 * c] = round_to_input<kFp16>(v[4 * c] * s.x);
+                v[4 * c + 1] = round_to_input<kFp16>(v[4 * c + 1] * s.y);
+                v[4 * c + 2] = round_to_input<kFp16>(v[4 * c + 2] * s.z);
+                v[4 * c + 3] = round_to_input<kFp16>(v[4 * c + 3] * s.w);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint16_t lo = to_bits<kFp16>(v[2 * i]);
+            const uint16_t hi = to_bits<kFp16>(v[2 * i + 1]);
+            amax = fmaxf(amax, fmaxf(fabsf(to_float<kFp16>(lo)), fabsf(to_float<kFp16>(hi))));
+            packed[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+        }
+        return;
+    }
+    two_stages(v);  // digits 0 and 1: element index = l * 16 + i
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) region[l * kPadded + i] = v[i];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) v[i] = region[i * kPadded + l];  // now element index = i * 16 + l
+    __syncwarp();
+    two_stages(v);  // digits 2 and 3
+    uint16_t* const halves = reinterpret_cast<uint16_t*>(region);
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) {
-        v[i] = to_float<kFp16>(static_cast<uint16_t>(w[i / 2] >> (16 * (i % 2))));
+        const uint16_t bits = to_bits<kFp16>(v[i]);
+        amax = fmaxf(amax, fabsf(to_float<kFp16>(bits)));
+        halves[i * 16 + l] = bits;
     }
-    if (!rotate && col_scale != nullptr) {
-        const float4 s0 = __ldg(reinterpret_cast<const float4*>(col_scale + base));
-        const float4 s1 = __ldg(reinterpret_cast<const float4*>(col_scale + base + 4));
-        const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-        for (int i = 0; i < kPerLane; ++i) v[i] = round_to_input<kFp16>(v[i] * s[i]);
-    }
-    if (rotate) hadamard256(v, lane);
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-        v[i] = round_to_input<kFp16>(v[i]);
-        amax = fmaxf(amax, fabsf(v[i]));
-    }
+    __syncwarp();
+    const uint4 lo = *reinterpret_cast<const uint4*>(halves + l * 16);
+    const uint4 hi = *reinterpret_cast<const uint4*>(halves + l * 16 + 8);
+    __syncwarp();
+    packed[0] = lo.x;
+    packed[1] = lo.y;
+    packed[2] = lo.z;
+    packed[3] = lo.w;
+    packed[4] = hi.x;
+    packed[5] = hi.y;
+    packed[6] = hi.z;
+    packed[7] = hi.w;
 }
 
-__device__ __forceinline__ int code_of(float v, float inv_divisor) {
-    return static_cast<int>(fminf(fmaxf(rintf(v * inv_divisor), -127.0f), 127.0f));
+__device__ __forceinline__ uint32_t code_of(float v, float inv_divisor) {
+    return static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(rintf(v * inv_divisor), -127.0f), 127.0f))) & 0xffu;
 }
 
-__device__ __forceinline__ void store_codes(int8_t* __restrict__ q_row, int base, const float (&v)[kPerLane], float inv_divisor) {
-    uint32_t packed[2];
+template <bool kFp16>
+__device__ __forceinline__ void store_codes(int8_t* __restrict__ q_row, int base, const uint32_t (&packed)[8], float inv_divisor) {
+    uint32_t out[4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int w = 0; w < 4; ++w) {
         uint32_t word = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            word |= (static_cast<uint32_t>(code_of(v[4 * h + i], inv_divisor)) & 0xffu) << (8 * i);
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t pair = packed[2 * w + j];
+            word |= code_of(to_float<kFp16>(static_cast<uint16_t>(pair & 0xffffu)), inv_divisor) << (16 * j);
+            word |= code_of(to_float<kFp16>(static_cast<uint16_t>(pair >> 16)), inv_divisor) << (16 * j + 8);
         }
-        packed[h] = word;
+        out[w] = word;
     }
-    *reinterpret_cast<uint2*>(q_row + base) = make_uint2(packed[0], packed[1]);
+    *reinterpret_cast<uint4*>(q_row + base) = make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-// blockDim = (32, warps_per_row, rows_per_cta). `kCache`: every warp owns at most `kCachedGroups` groups of
-// its row and keeps them in registers across the row maximum.
+// blockDim = (32, warps_per_row, rows_per_cta). A warp handles the groups 2 * (warp + j * warps) + half of its
+// row in round j. `kCache`: at most kCachedRounds rounds, kept in registers across the row maximum.
 template <bool kFp16, bool kCache>
-__global__ void convrot_quantize_kernel(const uint16_t* __restrict__ x, const float* __restrict__ col_scale, int8_t* __restrict__ q,
-                                        float* __restrict__ row_scale, int64_t M, int K, int groups, bool rotate) {
-    __shared__ float warp_max[kMaxWarpsPerRow];  // rows_per_cta * warps_per_row <= 32 entries
+__global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_kernel(const uint16_t* __restrict__ x, const float* __restrict__ col_scale,
+                                                                               int8_t* __restrict__ q, float* __restrict__ row_scale, int64_t M, int K,
+                                                                               int groups, bool rotate) {
+    extern __shared__ __align__(16) float regions[];  // 2 * kRegionWords per warp of the CTA
+    __shared__ float warp_max[kMaxWarpsPerCta];
     const int lane = static_cast<int>(threadIdx.x);
+    const int half = lane >> 4;
+    const int l = lane & 15;
     const int warp = static_cast<int>(threadIdx.y);
     const int warps = static_cast<int>(blockDim.y);
     const int local_row = static_cast<int>(threadIdx.z);
+    const int cta_warp = local_row * warps + warp;
+    float* const region = regions + (cta_warp * 2 + half) * kRegionWords;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.z + local_row;
-    const bool live = row < M;
-    const uint16_t* const x_row = x + (live ? row : 0) * K;
-    int8_t* const q_row = q + (live ? row : 0) * K;
+    const bool row_live = row < M;
+    const uint16_t* const x_row = x + (row_live ? row : 0) * K;
+    int8_t* const q_row = q + (row_live ? row : 0) * K;
+    const int rounds = (groups + 2 * warps - 1) / (2 * warps);
 
-    float cached[kCache ? kCachedGroups : 1][kPerLane];
+    uint32_t cached[kCache ? kCachedRounds : 1][8];
     float amax = 0.0f;
-    if (live) {
-        if constexpr (kCache) {
+    if constexpr (kCache) {
 #pragma unroll
-            for (int j = 0; j < kCachedGroups; ++j) {
-                const int g = warp + j * warps;
-                if (g < groups) produce<kFp16>(x_row, col_scale, g * kGroup + lane * kPerLane, lane, rotate, cached[j], amax);
+        for (int j = 0; j < kCachedRounds; ++j) {
+            if (j < rounds) {
+                const int g = 2 * (warp + j * warps) + half;
+                produce<kFp16>(x_row, col_scale, g * kGroup + l * kPerLane, l, row_live && g < groups, rotate, region, cached[j], amax);
             }
-        } else {
-            for (int g = warp; g < groups; g += warps) {
-                produce<kFp16>(x_row, col_scale, g * kGroup + lane * kPerLane, lane, rotate, cached[0], amax);
-            }
+        }
+    } else {
+        for (int j = 0; j < rounds; ++j) {
+            const int g = 2 * (warp + j * warps) + half;
+            produce<kFp16>(x_row, col_scale, g * kGroup + l * kPerLane, l, row_live && g < groups, rotate, region, cached[0], amax);
         }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    if (lane == 0) warp_max[local_row * warps + warp] = amax;
+    if (lane == 0) warp_max[cta_warp] = amax;
     __syncthreads();
-    if (!live) return;
     float row_max = 0.0f;
     for (int w = 0; w < warps; ++w) row_max = fmaxf(row_max, warp_max[local_row * warps + w]);
     const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
-    if (warp == 0 && lane == 0) row_scale[row] = rotate ? divisor * 0.0625f : divisor;
+    if (row_live && warp == 0 && lane == 0) row_scale[row] = rotate ? divisor * 0.0625f : divisor;
     const float inv_divisor = 1.0f / divisor;
 
     if constexpr (kCache) {
 #pragma unroll
-        for (int j = 0; j < kCachedGroups; ++j) {
-            const int g = warp + j * warps;
-            if (g < groups) store_codes(q_row, g * kGroup + lane * kPerLane, cached[j], inv_divisor);
+        for (int j = 0; j < kCachedRounds; ++j) {
+            const int g = 2 * (warp + j * warps) + half;
+            if (j < rounds && row_live && g < groups) store_codes<kFp16>(q_row, g * kGroup + l * kPerLane, cached[j], inv_divisor);
         }
     } else {
-        for (int g = warp; g < groups; g += warps) {
+        for (int j = 0; j < rounds; ++j) {
+            const int g = 2 * (warp + j * warps) + half;
             float unused = 0.0f;
-            produce<kFp16>(x_row, col_scale, g * kGroup + lane * kPerLane, lane, rotate, cached[0], unused);
-            store_codes(q_row, g * kGroup + lane * kPerLane, cached[0], inv_divisor);
+            produce<kFp16>(x_row, col_scale, g * kGroup + l * kPerLane, l, row_live && g < groups, rotate, region, cached[0], unused);
+            if (row_live && g < groups) store_codes<kFp16>(q_row, g * kGroup + l * kPerLane, cached[0], inv_divisor);
         }
     }
 }
@@ -222,25 +255,28 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
     if (K <= 0 || K % kGroup != 0 || K > (1ll << 30) || M < 0) return false;
     if (M == 0) return true;
     const int groups = static_cast<int>(K / kGroup);
-    const int warps = groups < kMaxWarpsPerRow ? groups : kMaxWarpsPerRow;
+    const int pairs = (groups + 1) / 2;
+    const int warps = pairs < kMaxWarpsPerRow ? pairs : kMaxWarpsPerRow;
     // short rows share a CTA so that a CTA is at least eight warps
     int rows_per_cta = 8 / warps;
     if (rows_per_cta < 1) rows_per_cta = 1;
-    const bool cache = groups <= warps * kCachedGroups;
+    const bool cache = groups <= 2 * warps * kCachedRounds;
     const dim3 block(32, warps, rows_per_cta);
     const dim3 grid(static_cast<unsigned>((M + rows_per_cta - 1) / rows_per_cta));
     const uint16_t* const xp = static_cast<const uint16_t*>(x);
+    const int k = static_cast<int>(K);
+    const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kRegionWords * sizeof(float);
     if (input_fp16 != 0) {
         if (cache) {
-            convrot_quantize_kernel<true, true><<<grid, block, 0, stream>>>(xp, col_scale, q, row_scale, M, static_cast<int>(K), groups, rotate);
+            convrot_quantize_kernel<true, true><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
         } else {
-            convrot_quantize_kernel<true, false><<<grid, block, 0, stream>>>(xp, col_scale, q, row_scale, M, static_cast<int>(K), groups, rotate);
+            convrot_quantize_kernel<true, false><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
         }
     } else {
         if (cache) {
-            convrot_quantize_kernel<false, true><<<grid, block, 0, stream>>>(xp, col_scale, q, row_scale, M, static_cast<int>(K), groups, rotate);
+            convrot_quantize_kernel<false, true><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
         } else {
-            convrot_quantize_kernel<false, false><<<grid, block, 0, stream>>>(xp, col_scale, q, row_scale, M, static_cast<int>(K), groups, rotate);
+            convrot_quantize_kernel<false, false><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
         }
     }
     return cudaGetLastError() == cudaSuccess;
