@@ -104,6 +104,15 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1: the CPU legs take every core this process may run on."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
+
+
 def cpu_baseline(threads=None):
     """The reference's CPU path (`scaled_mm_naive`, restated in oracle/scaled_mm.py) on a bounded sample:
     the first CPU_SAMPLE_ROWS token rows of the benchmark batch against the full weight."""
@@ -111,6 +120,8 @@ def cpu_baseline(threads=None):
 
     if threads:
         torch.set_num_threads(threads)
+    else:
+        use_all_host_threads()
     a, packed, scale = make_inputs(0)
     a = a[:CPU_SAMPLE_ROWS].contiguous()
     osm.scaled_mm_naive(a, packed, scale, None, torch.bfloat16, b_prepacked=True)  # warm-up
@@ -136,6 +147,7 @@ def run_reference(args):
         return
     from oracle import scaled_mm as osm
 
+    use_all_host_threads()
     a, packed, scale = make_inputs(0)
     a = a[:CPU_SAMPLE_ROWS].contiguous()
     for _ in range(max(1, min(args.warmup, 2))):
