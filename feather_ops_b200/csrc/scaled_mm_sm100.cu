@@ -384,8 +384,13 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // and are arrived on remotely by CTA 1's warps; barriers that release slots or publish an accumulator are
 // signalled in both CTAs by two commits.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kPairLoadStages = 6;     // measured: 6/3 = 1.30 PFLOP/s, 5/4 = 1.28, 4/3 = 1.22, 6/2 and 7/2 = 1.15
-constexpr int kPairOperandStages = 3;
+// Both ring depths are multiples of the number of upcast teams: a team then always meets the same slots and
+// sees every phase of the barriers it waits on (a waiter that skipped phases could mistake an old phase of the
+// same parity for the one it needs).
+constexpr int kPairLoadStages = 6;
+constexpr int kPairOperandStages = 4;
+constexpr int kPairTeams = 2;   // upcast teams taking k blocks in turn (measured: 1 team 1.27, 2 or 4 teams 1.35 PFLOP/s)
+static_assert(kPairLoadStages % kPairTeams == 0 && kPairOperandStages % kPairTeams == 0, "ring depths must be multiples of the team count");
 constexpr int kPairHalfN = 128;
 constexpr int kPairN = 2 * kPairHalfN;
 
@@ -429,7 +434,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             mbar_init(&load_empty[s], 1);
         }
         for (int s = 0; s < kPairOperandStages; ++s) {
-            mbar_init(&operand_full[s], 2 * kUpcastWarps);
+            mbar_init(&operand_full[s], 2 * kUpcastWarps / kPairTeams);
             mbar_init(&operand_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -576,45 +581,53 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     } else {
         // ------------------------------------------------------------------ upcast warps (this CTA's weight half)
-        // One 16-byte cell per thread and slot: cell u = (slab u / 128, row u % 128).
-        const int t = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
-        constexpr int kUpcastThreads = kUpcastWarps * 32;
+        // The warps form kPairTeams teams that take the k blocks in turn, so a team has kPairTeams k-block times
+        // for its chain (wait, shared load, convert, shared store, proxy fence, arrive) and the chains of
+        // consecutive k blocks overlap. Within a team: cell u = (slab u / 128, row u % 128), u = t + i * team size.
+        constexpr int kTeamThreads = kUpcastWarps * 32 / kPairTeams;
+        const int upcast_thread = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
+        const int team = upcast_thread / kTeamThreads;
+        const int t = upcast_thread % kTeamThreads;
         constexpr int kUnits = kPairHalfN * kSlabsPerBlock;
-        constexpr int kUnitsPerThread = (kUnits + kUpcastThreads - 1) / kUpcastThreads;
-        static_assert(kUnits % kUpcastThreads == 0, "the weight half tile must split evenly over the upcast threads");
+        constexpr int kUnitsPerThread = kUnits / kTeamThreads;
+        static_assert(kUnits % kTeamThreads == 0, "the weight half tile must split evenly over a team");
         Ring slot, operand;
         bool ok = true;
+        uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
-                     guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
-                if (!ok) break;
-                const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
-                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
-                uint4 cells[kUnitsPerThread];
+                if (turn == static_cast<uint32_t>(team)) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                         guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                    if (!ok) break;
+                    const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                    uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                    uint4 cells[kUnitsPerThread];
 #pragma unroll
-                for (int i = 0; i < kUnitsPerThread; ++i) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kUpcastThreads) * 16);
+                    for (int i = 0; i < kUnitsPerThread; ++i) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kTeamThreads) * 16);
 #pragma unroll
-                for (int i = 0; i < kUnitsPerThread; ++i) {
-                    const int u = t + i * kUpcastThreads;
-                    const int row = u % kPairHalfN;
-                    const int slab = u / kPairHalfN;
-                    const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
-                    uint32_t h[8];
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        const int u = t + i * kTeamThreads;
+                        const int row = u % kPairHalfN;
+                        const int slab = u / kPairHalfN;
+                        const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
+                        uint32_t h[8];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
-                        if constexpr (kOperandBf16) {
-                            h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
-                            h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                        for (int q = 0; q < 4; ++q) {
+                            fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
+                            if constexpr (kOperandBf16) {
+                                h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
+                                h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                            }
                         }
+                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
+                turn = turn + 1 == kPairTeams ? 0 : turn + 1;
                 slot.advance(kPairLoadStages);
                 operand.advance(kPairOperandStages);
             }
@@ -633,6 +646,284 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, 2 * kPairN);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Skinny-M version (M <= 128, HBM bound on the weight): one CTA per (64-column tile, K split), two CTAs
+// resident per SM, so that a few hundred CTAs stream the weight concurrently. With `splits` > 1 every CTA
+// writes its fp32 partial tile to a scratch buffer [splits][M][N], takes a ticket from a per-tile counter,
+// and the CTA that draws the last ticket sums the partials in split order (deterministic), applies the
+// epilogue, writes C and puts the counter back to zero. With `splits` == 1 nothing is staged.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kSkinnyN = 64;
+constexpr int kSkinnyUpcastWarps = 8;   // 256 cells per k block, one per thread
+constexpr int kSkinnyThreads = 32 * (kFirstUpcastWarp + kSkinnyUpcastWarps);
+constexpr int kSkinnyRawBytes = kSlabsPerBlock * kSkinnyN * 16;   // 4 KB of fp8 cells per k block
+constexpr int kSkinnyOperandBytes = kSkinnyN * 128;               // 8 KB converted operand
+constexpr int kSkinnyMaxStages = 12;
+constexpr int kSkinnyTeams = 2;
+constexpr int kSkinnyOperandStages = 6;   // per k block there is almost no work: the barrier hand-offs have to overlap
+constexpr int kSkinnySmemBudget = 100 * 1024;                     // two CTAs per SM
+
+struct SkinnyParams {
+    Params base;
+    float* partials;      // [splits][M][N] fp32, only touched when splits > 1
+    uint32_t* counters;   // [tiles_n], zero before the launch and zero again after it
+    int splits;
+    int kb_per_split;
+    uint32_t a_slot_bytes;  // bytes of one activation box and slot: only ceil(M / 8) * 8 rows are fetched and kept
+    uint32_t load_stages;   // depth of the load ring: as many slots as fit beside a second CTA on the SM
+};
+
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+__global__ void __launch_bounds__(kSkinnyThreads, 2)
+scaled_mm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const SkinnyParams sp) {
+    constexpr int BN = kSkinnyN;
+    const Params& p = sp.base;
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    // [activation slots, packed at a_slot_bytes][operand slots][raw weight slots][barriers]. An activation slot only
+    // holds the rows that exist; the UMMA reads 128 rows from its start, i.e. on into the following slots and
+    // buffers (at least 16 KB follow the last slot), and what it finds there only reaches accumulator rows >= M.
+    const uint32_t stages = sp.load_stages;
+    uint8_t* const a_smem = smem;
+    uint8_t* const operand_smem = a_smem + stages * sp.a_slot_bytes;
+    uint8_t* const raw_smem = operand_smem + kSkinnyOperandStages * kSkinnyOperandBytes;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(raw_smem + stages * kSkinnyRawBytes);
+    uint64_t* const load_full = bars;
+    uint64_t* const load_empty = load_full + stages;
+    uint64_t* const operand_full = load_empty + stages;
+    uint64_t* const operand_empty = operand_full + kSkinnyOperandStages;
+    uint64_t* const tmem_full = operand_empty + kSkinnyOperandStages;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+    volatile uint32_t* const last_flag = tmem_slot + 2;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        *last_flag = 0u;
+        for (uint32_t s = 0; s < stages; ++s) {
+            mbar_init(&load_full[s], 1);
+            mbar_init(&load_empty[s], 1);
+        }
+        for (int s = 0; s < kSkinnyOperandStages; ++s) {
+            mbar_init(&operand_full[s], kSkinnyUpcastWarps / kSkinnyTeams);
+            mbar_init(&operand_empty[s], 1);
+        }
+        mbar_init(&tmem_full[0], 1);
+        mbar_init_fence();
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, BN);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tile = static_cast<int>(blockIdx.x) / sp.splits;   // splits of one tile are neighbours in the grid
+    const int split = static_cast<int>(blockIdx.x) % sp.splits;
+    const int n0 = tile * BN;
+    const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+    const int kb_begin = split * sp.kb_per_split;
+    const int kb_end = kb_begin + sp.kb_per_split < num_kb ? kb_begin + sp.kb_per_split : num_kb;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            Ring slot;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty)) break;
+                // The activation box only covers the rows that exist (rounded up to 8): rows of a 128-row box that lie
+                // past M are zero filled but still cross the L2 -> SM fabric. The UMMA reads 128 rows of the slot all
+                // the same; what the missing rows hold only reaches accumulator rows that are never stored.
+                mbar_arrive_expect_tx(&load_full[slot.idx], sp.a_slot_bytes + kSkinnyRawBytes);
+                tma_load_2d(a_smem + slot.idx * sp.a_slot_bytes, &map_a, &load_full[slot.idx], kb * kBlockK, 0);
+                tma_load_2d(raw_smem + slot.idx * kSkinnyRawBytes, &map_b, &load_full[slot.idx], n0 * 2, kb * kSlabsPerBlock);
+                slot.advance(stages);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            Ring slot, operand;
+            bool ok = true;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 1) &&
+                     guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(a_smem + slot.idx * sp.a_slot_bytes);
+                const uint32_t b_addr = smem_u32(operand_smem + operand.idx * kSkinnyOperandBytes);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; ++k) {
+                    umma_f16(tmem_base, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
+                             (kb > kb_begin || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&load_empty[slot.idx]);
+                umma_commit(&operand_empty[operand.idx]);
+                slot.advance(stages);
+                operand.advance(kSkinnyOperandStages);
+            }
+            if (ok) umma_commit(&tmem_full[0]);
+        }
+    } else if (warp < kFirstUpcastWarp) {
+        // ------------------------------------------------------------------ epilogue (+ split reduction)
+        const int quarter = warp % 4;
+        const int row = quarter * 32 + lane;
+        const bool row_live = row < p.M;
+        const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+        const bool ok = guard.wait(&tmem_full[0], 0u, kSiteTmemFull);
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+
+        // scale, round, bias, round, store: 32 consecutive columns of this thread's row
+        auto finish = [&](const float (&acc)[32], int col0) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int col = col0 + g * 8;
+                if (col >= p.N) continue;
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[i] = pack_out<kOutBf16>(acc[g * 8 + 2 * i] * scale, acc[g * 8 + 2 * i + 1] * scale);
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t bw = static_cast<uint32_t>(__ldg(p.bias + col + 2 * i)) | (static_cast<uint32_t>(__ldg(p.bias + col + 2 * i + 1)) << 16);
+                        const float2 x = unpack_out<kOutBf16>(o[i]);
+                        const float2 b = unpack_out<kOutBf16>(bw);
+                        o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
+                    }
+                }
+                *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        };
+
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(taddr + c * 32, v);
+                tmem_wait_ld();
+                float acc[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(v[i]);
+                if (!row_live) continue;
+                if (sp.splits == 1) {
+                    finish(acc, n0 + c * 32);
+                } else {
+                    float* const dst = sp.partials + (static_cast<int64_t>(split) * p.M + row) * p.N + n0 + c * 32;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        if (n0 + c * 32 + g * 4 < p.N) *reinterpret_cast<float4*>(dst + g * 4) = make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
+                    }
+                }
+            }
+        }
+        if (sp.splits > 1) {
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == kFirstEpilogueWarp && lane == 0) {
+                const uint32_t ticket = atomicAdd(sp.counters + tile, 1u);
+                *last_flag = (ticket == static_cast<uint32_t>(sp.splits - 1)) ? 1u : 0u;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag != 0u) {
+                __threadfence();
+                if (row_live) {
+#pragma unroll 1
+                    for (int c = 0; c < BN / 32; ++c) {
+                        float acc[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+                        for (int s = 0; s < sp.splits; ++s) {  // fixed order: the sum does not depend on which CTA finishes last
+                            const float* const src = sp.partials + (static_cast<int64_t>(s) * p.M + row) * p.N + n0 + c * 32;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                if (n0 + c * 32 + g * 4 < p.N) {
+                                    const float4 t4 = __ldcg(reinterpret_cast<const float4*>(src + g * 4));
+                                    acc[g * 4] += t4.x;
+                                    acc[g * 4 + 1] += t4.y;
+                                    acc[g * 4 + 2] += t4.z;
+                                    acc[g * 4 + 3] += t4.w;
+                                }
+                            }
+                        }
+                        finish(acc, n0 + c * 32);
+                    }
+                }
+                if (warp == kFirstEpilogueWarp && lane == 0) sp.counters[tile] = 0u;  // ready for the next launch
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ upcast warps
+        // Two teams of four warps take the k blocks in turn (a k block is 256 cells, two per thread of a team):
+        // there is almost no work per k block, so what has to overlap is the chain of barrier hand-offs. Both
+        // ring depths are even, so a team always meets the same slots and sees every phase of their barriers.
+        constexpr int kTeams = kSkinnyTeams;
+        constexpr int kTeamThreads = kSkinnyUpcastWarps * 32 / kTeams;
+        constexpr int kUnits = BN * kSlabsPerBlock;
+        constexpr int kUnitsPerThread = kUnits / kTeamThreads;
+        const int upcast_thread = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
+        const int team = upcast_thread / kTeamThreads;
+        const int t = upcast_thread % kTeamThreads;
+        Ring slot, operand;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (((kb - kb_begin) % kTeams) == team) {
+                if (!(guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                      guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty))) {
+                    break;
+                }
+                const uint8_t* const raw = raw_smem + slot.idx * kSkinnyRawBytes;
+                uint8_t* const dst = operand_smem + operand.idx * kSkinnyOperandBytes;
+                uint4 cells[kUnitsPerThread];
+#pragma unroll
+                for (int i = 0; i < kUnitsPerThread; ++i) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kTeamThreads) * 16);
+#pragma unroll
+                for (int i = 0; i < kUnitsPerThread; ++i) {
+                    const int u = t + i * kTeamThreads;
+                    const int row = u % BN;
+                    const int slab = u / BN;
+                    const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
+                    uint32_t h[8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
+                        if constexpr (kOperandBf16) {
+                            h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
+                            h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&operand_full[operand.idx]);
+            }
+            slot.advance(stages);
+            operand.advance(kSkinnyOperandStages);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, BN);
     }
 }
 
@@ -794,6 +1085,95 @@ bool launch_pair(const LaunchArgs& args) {
     return false;
 }
 
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
+    auto* kernel = &scaled_mm_skinny_kernel<kE5M2, kOperandBf16, kOutBf16>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBudget) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+    CUtensorMap map_a, map_b;
+    const uint32_t a_rows = static_cast<uint32_t>((args.M + 7) / 8 * 8);
+    const uint32_t a_slot_bytes = a_rows * kBlockK * 2;
+    // ring depth: what fits in the budget after the operand slots, the barriers and the alignment slack
+    const uint32_t fixed = kSkinnyOperandStages * kSkinnyOperandBytes + 1024 + 512;
+    uint32_t stages = (kSkinnySmemBudget - fixed) / (a_slot_bytes + kSkinnyRawBytes);
+    if (stages > kSkinnyMaxStages) stages = kSkinnyMaxStages;
+    stages -= stages % kSkinnyTeams;  // see kSkinnyTeams
+    if (stages < 2) return false;
+    const uint32_t smem_bytes = fixed + stages * (a_slot_bytes + kSkinnyRawBytes);
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.K) * 2};
+        const uint32_t box[2] = {kBlockK, a_rows};
+        if (!encode_map(&map_a, args.a_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.a, dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B)) {
+            return false;
+        }
+    }
+    {
+        const uint64_t k16_rows = static_cast<uint64_t>((args.K + 127) / 128) * 8;
+        const uint64_t dims[2] = {static_cast<uint64_t>(args.N) * 2, k16_rows};
+        const uint64_t strides[1] = {static_cast<uint64_t>(args.N) * 16};
+        const uint32_t box[2] = {kSkinnyN * 2, kSlabsPerBlock};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    }
+    SkinnyParams sp{};
+    sp.base.scale = args.scale;
+    sp.base.bias = args.bias;
+    sp.base.c = args.c;
+    sp.base.M = static_cast<int>(args.M);
+    sp.base.N = static_cast<int>(args.N);
+    sp.base.K = static_cast<int>(args.K);
+    sp.base.tiles_m = 1;
+    sp.base.tiles_n = static_cast<int>((args.N + kSkinnyN - 1) / kSkinnyN);
+    sp.base.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, kBlockM, kSkinnyN);
+    sp.base.bias_vec = 0;
+    const int num_kb = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
+    if (splits < 1) splits = 1;
+    if (splits > num_kb) splits = num_kb;
+    sp.kb_per_split = (num_kb + splits - 1) / splits;
+    sp.splits = (num_kb + sp.kb_per_split - 1) / sp.kb_per_split;  // no empty split
+    sp.partials = partials;
+    sp.counters = counters;
+    sp.a_slot_bytes = a_slot_bytes;
+    sp.load_stages = stages;
+    const int64_t grid = static_cast<int64_t>(sp.base.tiles_n) * sp.splits;
+    if (grid > (1 << 30)) return false;
+    kernel<<<static_cast<unsigned>(grid), kSkinnyThreads, smem_bytes, args.stream>>>(map_a, map_b, sp);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+bool launch_skinny(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
+    const bool operand_bf16 = args.a_bf16;
+#define FEATHER_SMM_SKINNY_CASE(E5, OB, OUT)                               \
+    if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
+        return launch_skinny_instance<E5, OB, OUT>(args, splits, partials, counters); \
+    }
+    FEATHER_SMM_SKINNY_CASE(true, false, true)
+    FEATHER_SMM_SKINNY_CASE(true, false, false)
+    FEATHER_SMM_SKINNY_CASE(false, false, true)
+    FEATHER_SMM_SKINNY_CASE(false, false, false)
+    FEATHER_SMM_SKINNY_CASE(true, true, true)
+    FEATHER_SMM_SKINNY_CASE(true, true, false)
+    FEATHER_SMM_SKINNY_CASE(false, true, true)
+    FEATHER_SMM_SKINNY_CASE(false, true, false)
+#undef FEATHER_SMM_SKINNY_CASE
+    return false;
+}
+
+// Number of K splits that `launch_skinny` will actually use for a request of `splits`.
+inline int effective_splits(int64_t K, int splits) {
+    const int num_kb = static_cast<int>((K + kBlockK - 1) / kBlockK);
+    if (splits < 1) splits = 1;
+    if (splits > num_kb) splits = num_kb;
+    const int per = (num_kb + splits - 1) / splits;
+    return (num_kb + per - 1) / per;
+}
+
 template <int BN>
 bool launch_for_block_n(const LaunchArgs& args) {
     const bool operand_bf16 = args.a_bf16;  // the weights are decoded to the activation's format
@@ -838,7 +1218,35 @@ extern "C" bool launch_scaled_mm(const uint16_t* a, const uint8_t* b_prepacked, 
         return smm::launch_for_block_n<256>(args);
     }
     if (block_n >= 128) return smm::launch_for_block_n<128>(args);
+    // narrow tiles with at most one row tile: one CTA per 64-column tile, two CTAs per SM
+    if (M <= smm::kBlockM) return smm::launch_skinny(args, 1, nullptr, nullptr);
     return smm::launch_for_block_n<64>(args);
+}
+
+// Split-K variant for skinny problems (M <= 128), no counterpart in the reference's C ABI (its README calls
+// split-K "no notable speedup" on gfx11; on B200 a 1..16-row product is bound by how many CTAs stream the
+// weight). `partials` is scratch for `feather_scaled_mm_splitk_partial_floats(M, N, K, splits)` floats,
+// `counters` holds ceil(N / 64) uint32 that must be zero before the first launch and are left zero by every
+// launch. Launches that share the scratch must not overlap on the device. The result is deterministic:
+// partial sums are added in split order.
+extern "C" bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
+                                        int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
+                                        bool output_bf16, int splits, float* partials, uint32_t* counters, cudaStream_t stream) {
+    using namespace feather;
+    if (M < 0 || M > smm::kBlockM || N <= 0 || K <= 0 || N % 16 != 0 || K % 16 != 0) return false;
+    if (N > (1 << 30) || K > (1 << 30)) return false;
+    if (M == 0) return true;
+    if (smm::effective_splits(K, splits) > 1 && (partials == nullptr || counters == nullptr)) return false;
+    const smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
+                               use_fp8_e5m2, a_bf16, output_bf16, stream};
+    return smm::launch_skinny(args, splits, partials, counters);
+}
+
+// Floats of `partials` scratch that `launch_scaled_mm_splitk` needs (0 when the request collapses to one split).
+extern "C" int64_t feather_scaled_mm_splitk_partial_floats(int64_t M, int64_t N, int64_t K, int splits) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int effective = feather::smm::effective_splits(K, splits);
+    return effective > 1 ? static_cast<int64_t>(effective) * M * N : 0;
 }
 
 // Reads (and clears) the status record the kernel's bounded waits report into: out[0] = wait site

@@ -100,6 +100,57 @@ void scaled_mm(const Tensor& a, const Tensor& b_prepacked, const std::optional<T
     STD_TORCH_CHECK(launched, "Unsupported config");
 }
 
+// Split-K scaled_mm for skinny problems. Same tensor contract as `scaled_mm`, plus caller-provided scratch:
+// `partials` (float32, at least feather_scaled_mm_splitk_partial_floats elements) and `counters` (int32,
+// ceil(N / 64) zeros). The Python wrapper allocates both with torch, so they are stream ordered.
+void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::optional<Tensor>& scale, const std::optional<Tensor>& bias, Tensor& c,
+                      Tensor& partials, Tensor& counters, int64_t splits) {
+    STD_TORCH_CHECK(a.is_cuda() && b_prepacked.is_cuda() && c.is_cuda() && partials.is_cuda() && counters.is_cuda(), "tensors must be CUDA tensors");
+    const auto device = a.get_device_index();
+    STD_TORCH_CHECK(b_prepacked.get_device_index() == device && c.get_device_index() == device && partials.get_device_index() == device &&
+                        counters.get_device_index() == device,
+                    "all tensors must be on the same device as a");
+    STD_TORCH_CHECK(is_half_or_bf16(a.scalar_type()), "a must be float16 or bfloat16");
+    STD_TORCH_CHECK(is_half_or_bf16(c.scalar_type()), "c must be float16 or bfloat16");
+    const auto b_type = b_prepacked.scalar_type();
+    STD_TORCH_CHECK(b_type == ScalarType::Float8_e4m3fn || b_type == ScalarType::Float8_e5m2, "b_prepacked must be float8_e4m3fn or float8_e5m2");
+    STD_TORCH_CHECK(a.dim() == 2 && c.dim() == 2, "a and c must be 2D");
+    STD_TORCH_CHECK(b_prepacked.dim() == 3 && b_prepacked.size(2) == 16, "b_prepacked must be 3D (K/16, N, 16)");
+    const int64_t M = a.size(0);
+    const int64_t K = a.size(1);
+    const int64_t N = b_prepacked.size(1);
+    STD_TORCH_CHECK(M <= 128, "the split-K path is for M <= 128");
+    STD_TORCH_CHECK(K % 16 == 0, "K must be divisible by 16");
+    STD_TORCH_CHECK(N % 16 == 0, "N must be divisible by 16");
+    STD_TORCH_CHECK(b_prepacked.size(0) >= K / 16 && b_prepacked.size(0) % 8 == 0, "b_prepacked.shape[0] must cover K padded to 128");
+    STD_TORCH_CHECK(c.size(0) == M && c.size(1) == N, "c must be [M, N]");
+    STD_TORCH_CHECK(a.is_contiguous() && b_prepacked.is_contiguous() && c.is_contiguous(), "a, b_prepacked and c must be contiguous");
+    STD_TORCH_CHECK(partials.scalar_type() == ScalarType::Float && partials.is_contiguous(), "partials must be contiguous float32");
+    STD_TORCH_CHECK(counters.scalar_type() == ScalarType::Int && counters.is_contiguous(), "counters must be contiguous int32");
+    STD_TORCH_CHECK(partials.numel() >= feather_scaled_mm_splitk_partial_floats(M, N, K, static_cast<int>(splits)), "partials is too small");
+    STD_TORCH_CHECK(counters.numel() >= (N + 63) / 64, "counters must have ceil(N / 64) elements");
+    if (scale.has_value()) {
+        STD_TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == ScalarType::Float && scale->numel() == 1, "scale must be one float32 on the device");
+    }
+    if (bias.has_value()) {
+        STD_TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == c.scalar_type() && bias->numel() == N && bias->is_contiguous(),
+                        "bias must be N contiguous elements of c's dtype");
+    }
+    STD_TORCH_CHECK(aligned16(a.const_data_ptr()) && aligned16(b_prepacked.const_data_ptr()) && aligned16(c.mutable_data_ptr()) &&
+                        aligned16(partials.mutable_data_ptr()),
+                    "data pointers must be 16-byte aligned");
+    torch::stable::accelerator::DeviceGuard guard(device);
+    const feather_stream_t stream = current_stream(device);
+    const bool launched = launch_scaled_mm_splitk(
+        static_cast<const uint16_t*>(a.const_data_ptr()), static_cast<const uint8_t*>(b_prepacked.const_data_ptr()),
+        scale.has_value() ? static_cast<const float*>(scale->const_data_ptr()) : nullptr,
+        bias.has_value() ? static_cast<const uint16_t*>(bias->const_data_ptr()) : nullptr, static_cast<uint16_t*>(c.mutable_data_ptr()), M, N, K,
+        scale.has_value() ? 1 : 0, bias.has_value() ? 1 : 0, b_type == ScalarType::Float8_e5m2, a.scalar_type() == ScalarType::BFloat16,
+        c.scalar_type() == ScalarType::BFloat16, static_cast<int>(splits), static_cast<float*>(partials.mutable_data_ptr()),
+        static_cast<uint32_t*>(counters.mutable_data_ptr()), stream);
+    STD_TORCH_CHECK(launched, "scaled_mm_splitk: unsupported problem");
+}
+
 void int8_scaled_mm(const Tensor& a, const Tensor& b_prepacked, const Tensor& a_scale, const std::optional<Tensor>& b_scale,
                     const std::optional<Tensor>& bias, Tensor& c, bool transposed_b, int64_t block_warps_m, int64_t block_warps_n,
                     int64_t unroll_k, int64_t repeat_m, int64_t repeat_n) {
@@ -257,6 +308,9 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
         "scaled_mm(Tensor a, Tensor b_prepacked, Tensor? scale, Tensor? bias, Tensor(a!) c, int block_warps_m, int block_warps_n, "
         "int unroll_k, int repeat_m, int repeat_n, bool prefetch) -> ()");
     m.def(
+        "scaled_mm_splitk(Tensor a, Tensor b_prepacked, Tensor? scale, Tensor? bias, Tensor(a!) c, Tensor(b!) partials, Tensor(c!) counters, "
+        "int splits) -> ()");
+    m.def(
         "int8_scaled_mm(Tensor a, Tensor b_prepacked, Tensor a_scale, Tensor? b_scale, Tensor? bias, Tensor(a!) c, bool transposed_b, "
         "int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n) -> ()");
     m.def("convrot_quantize(Tensor x, Tensor? col_scale, Tensor(a!) q, Tensor(b!) row_scale, bool rotate) -> ()");
@@ -267,6 +321,7 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
 
 STABLE_TORCH_LIBRARY_IMPL(feather_ops, CUDA, m) {
     m.impl("scaled_mm", TORCH_BOX(&scaled_mm));
+    m.impl("scaled_mm_splitk", TORCH_BOX(&scaled_mm_splitk));
     m.impl("int8_scaled_mm", TORCH_BOX(&int8_scaled_mm));
     m.impl("convrot_quantize", TORCH_BOX(&convrot_quantize));
     m.impl("conv2d_3x3", TORCH_BOX(&conv2d_3x3));

@@ -43,6 +43,22 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
     return _TILE_OF_WIDTH[best[1]]
 
 
+_SKINNY_MAX_M = 128      # one row tile: the weight stream is the cost, a 64-wide tile per CTA, two CTAs per SM
+_SPLIT_MAX_M = 32        # below this the fp32 partials are small against the weight and K is split as well
+_RESIDENT_SKINNY_CTAS = 2 * _SM_COUNT
+
+
+def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
+    """How many K splits the skinny path uses (1 = none). A split costs a round trip of fp32 partials and more
+    CTA start-ups, so K is only split when the 64-wide column tiles alone cannot fill the resident CTAs (two per
+    SM), at most four ways and never below eight 64-wide k blocks per split."""
+    if M > _SPLIT_MAX_M:
+        return 1
+    tiles = -(-N // 64)
+    k_blocks = -(-K // 64)
+    return max(1, min(4, _RESIDENT_SKINNY_CTAS // tiles, k_blocks // 8))
+
+
 def _launch(a, b_prepacked, scale, bias, out, tile) -> None:
     torch.ops.feather_ops.scaled_mm.default(a, b_prepacked, scale, bias, out, *tile[:5], bool(tile[5]))
 
@@ -50,7 +66,16 @@ def _launch(a, b_prepacked, scale, bias, out, tile) -> None:
 @custom_op("feather_ops::scaled_mm_auto", mutates_args=("out",))
 def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Tensor | None, bias: torch.Tensor | None, out: torch.Tensor) -> None:
     """Tile choice + launch as one opaque node, so a compiled caller does not specialize on the heuristic."""
-    _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(a.shape[0], b_prepacked.shape[1], a.shape[1]))
+    m, k = a.shape
+    n = b_prepacked.shape[1]
+    if 0 < m <= _SKINNY_MAX_M:
+        splits = select_scaled_mm_splits(m, n, k)
+        floats = splits * m * n if splits > 1 else 1
+        partials = torch.empty(floats, device=a.device, dtype=torch.float32)
+        counters = torch.zeros(-(-n // 64), device=a.device, dtype=torch.int32)
+        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, counters, splits)
+        return
+    _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(m, n, k))
 
 
 def scaled_mm_hip(a, b_prepacked, scale, bias, out_dtype, tile=None):

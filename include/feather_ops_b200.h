@@ -31,6 +31,19 @@ bool launch_scaled_mm(const uint16_t* a, const uint8_t* b_prepacked, const float
                       int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n, bool prefetch,
                       feather_stream_t stream);
 
+/* Split-K variant of scaled_mm for skinny problems (M <= 128): one CTA per (64-column tile, K split) streams the
+ * weight, fp32 partial tiles go to `partials`, the CTA that finishes a tile last sums them in split order and writes c.
+ * partials: scratch of feather_scaled_mm_splitk_partial_floats(M, N, K, splits) floats (may be NULL when that is 0).
+ * counters: ceil(N / 64) uint32, zero before the first launch; every launch leaves them zero. Launches sharing the
+ * scratch must not overlap on the device. No counterpart in the reference's C ABI (its kernels have no split-K). */
+bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c, int64_t M,
+                             int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16, bool output_bf16, int splits,
+                             float* partials, uint32_t* counters, feather_stream_t stream);
+
+/* Number of floats of `partials` scratch launch_scaled_mm_splitk needs (0 when the request collapses to one split).
+ * No counterpart in the reference. */
+int64_t feather_scaled_mm_splitk_partial_floats(int64_t M, int64_t N, int64_t K, int splits);
+
 /* Diagnostic: reads and clears the record that the scaled_mm kernel's bounded device waits report into.
  * out[0] = 0 when every wait completed, else the wait site; out[1] = block index. Synchronizes the device.
  * Returns 0 on success. No counterpart in the reference (its kernels have no device-side waits). */

@@ -13,7 +13,7 @@ def declared_functions() -> list[str]:
     names = []
     for header in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
-        names += re.findall(r"^\s*(?:bool|int|void)\s+(\w+)\s*\(", text, flags=re.M)
+        names += re.findall(r"^\s*(?:bool|int|int64_t|void)\s+(\w+)\s*\(", text, flags=re.M)
     return names
 
 

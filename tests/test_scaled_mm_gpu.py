@@ -170,3 +170,34 @@ def test_reference_cpu_case_fp16(cuda_device):
     out = _cabi.scaled_mm(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), None, torch.float16)
     _cabi.assert_clean(STATUS)
     _compare(out, osm.scaled_mm_f32(a, packed, scale, None, torch.float16, b_prepacked=True), torch.float16, 1e-3)
+
+
+@pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16)])
+@pytest.mark.parametrize("shape", [(1, 128, 128), (1, 12288, 3072), (16, 12288, 3072), (17, 272, 1040), (33, 96, 4096), (128, 3072, 1024)])
+def test_skinny_split_k_through_the_c_abi(cuda_device, shape, a_dtype, b_dtype, out_dtype):
+    m, n, k = shape
+    a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype, seed=m + k)
+    ref = osm.scaled_mm_f32(a, packed, scale, bias, out_dtype, b_prepacked=True)
+    dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+    partials = counters = None
+    for splits in (1, 2, 3, 4, 4):
+        out, partials_used, counters_used = _cabi.scaled_mm_splitk(*dev, out_dtype, splits, partials if splits == 4 else None, counters if splits == 4 else None)
+        _cabi.assert_clean(STATUS)
+        _compare(out, ref, out_dtype, 1e-3)
+        assert int(counters_used.abs().sum().item()) == 0  # every launch leaves its tickets at zero
+        if splits == 4:
+            if partials is not None:
+                assert torch.equal(out, previous)  # same scratch reused, split order fixed: bit identical
+            partials, counters, previous = partials_used, counters_used, out
+
+
+def test_skinny_shapes_through_the_python_api(cuda_device):
+    import feather_ops_b200 as fo
+    from feather_ops_b200.scaled_mm import select_scaled_mm_splits
+
+    assert select_scaled_mm_splits(1, 3072, 12288) > 1 and select_scaled_mm_splits(64, 3072, 12288) == 1
+    for m, n, k in ((1, 12288, 3072), (16, 3072, 12288), (100, 12288, 3072), (128, 3072, 1024)):
+        a, packed, scale, bias = osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, weight_std=0.02, with_bias=False)
+        out = fo.scaled_mm_hip(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), None, torch.bfloat16)
+        _cabi.assert_clean(STATUS)
+        _compare(out, osm.scaled_mm_f32(a, packed, scale, None, torch.bfloat16, b_prepacked=True), torch.bfloat16, 1e-3)
