@@ -26,6 +26,10 @@ PROTOTYPES = {
         [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _c_int, _c_int, _c_bool, _c_bool, _c_bool, _c_int, _ptr, _ptr, _ptr],
     ),
     "feather_scaled_mm_splitk_partial_floats": (_i64, [_i64, _i64, _i64, _c_int]),
+    "launch_scaled_mm_splitk_static": (
+        _c_int,
+        [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _c_int, _c_int, _c_bool, _c_bool, _c_bool, _c_int, _ptr, ctypes.c_char_p, ctypes.c_size_t],
+    ),
     "feather_scaled_mm_status": (_c_int, [_ptr]),
     "launch_convrot_quantize": (_c_bool, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _c_int, _c_bool, _ptr]),
     "launch_int8_scaled_mm": (

@@ -33,7 +33,9 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 namespace feather {
 namespace smm {
@@ -1247,6 +1249,113 @@ extern "C" int64_t feather_scaled_mm_splitk_partial_floats(int64_t M, int64_t N,
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     const int effective = feather::smm::effective_splits(K, splits);
     return effective > 1 ? static_cast<int64_t>(effective) * M * N : 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Split-K scaled_mm without any allocation: the scratch lives in this library's own device memory.
+//
+// Who needs this: hosts that bind the C ABI directly and have nothing to allocate device memory with once
+// they are running. Examples are a serving loop that has handed all free device memory to its own arena at
+// start-up (so a later cudaMalloc fails or, worse, stalls the device while the driver reshuffles), a
+// foreign-language plugin (C, Go, Rust through FFI) that owns its input and output buffers but has no
+// device allocator of its own, and code running inside a callback where the runtime forbids allocation
+// calls. They still pass inputs and outputs; only the fp32 partials and the per-tile tickets come from here.
+//
+// The scratch is one file-scope __device__ array (4 MiB of partials + 1 KiB of tickets, held by every GPU
+// that loads the library, from load until exit). That bounds the problems this entry point accepts:
+// M <= 16, N <= 16384 and at most 4 splits; anything larger is refused with an error code and message.
+// On the host the array's name is only a handle, not a device address: the address is looked up once per
+// device with cudaGetSymbolAddress (with that device current), by the first call made on that device. That
+// first call therefore does a little extra runtime work and should be made before any stream capture begins.
+// Every call uses the same array and finds the previous call's partials in it; the tickets, which must start
+// at zero, are cleared on the caller's stream before each launch. Two calls that run on the device at the
+// same time (different streams, different host threads) would race on the scratch: serialize them.
+// ---------------------------------------------------------------------------------------------------------
+namespace feather {
+namespace smm {
+
+constexpr int64_t kStaticMaxM = 16;
+constexpr int64_t kStaticMaxN = 16384;
+constexpr int kStaticMaxSplits = 4;
+constexpr size_t kStaticPartialBytes = static_cast<size_t>(kStaticMaxSplits) * kStaticMaxM * kStaticMaxN * sizeof(float);  // 4 MiB
+constexpr size_t kStaticCounterBytes = (kStaticMaxN / kSkinnyN) * sizeof(uint32_t);                                         // 1 KiB
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticPartialBytes + kStaticCounterBytes];
+
+// Device address of the scratch on the current device, looked up on first use. Returns nullptr on failure.
+static unsigned char* static_scratch_address(cudaError_t* error) {
+    static std::mutex lock;
+    static unsigned char* address[64] = {};
+    int dev = 0;
+    *error = cudaGetDevice(&dev);
+    if (*error != cudaSuccess || dev < 0 || dev >= 64) {
+        if (*error == cudaSuccess) *error = cudaErrorInvalidDevice;
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> hold(lock);
+    if (address[dev] == nullptr) {
+        void* found = nullptr;
+        *error = cudaGetSymbolAddress(&found, g_static_scratch);
+        if (*error != cudaSuccess) return nullptr;
+        address[dev] = static_cast<unsigned char*>(found);
+    }
+    return address[dev];
+}
+
+static void write_message(char* out, size_t capacity, const char* text) {
+    if (out != nullptr && capacity > 0) snprintf(out, capacity, "%s", text);
+}
+
+}  // namespace smm
+}  // namespace feather
+
+// Same computation and arguments as launch_scaled_mm_splitk, minus the two scratch pointers. Returns 0 when
+// the kernel was enqueued; 1 for arguments launch_scaled_mm_splitk would refuse too; 2 when the problem is
+// larger than the built-in scratch (M > 16, N > 16384 or more than 4 effective splits); 3 when a CUDA call
+// failed. `error_message` (may be NULL) receives a description for every nonzero return. Calls no
+// allocating routine. Calls that overlap on the device race on the shared scratch.
+extern "C" int launch_scaled_mm_splitk_static(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias,
+                                              uint16_t* c, int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2,
+                                              bool a_bf16, bool output_bf16, int splits, cudaStream_t stream, char* error_message,
+                                              size_t error_capacity) {
+    using namespace feather;
+    if (M < 0 || N <= 0 || K <= 0 || N % 16 != 0 || K % 16 != 0 || K > (1 << 30)) {
+        smm::write_message(error_message, error_capacity, "scaled_mm_splitk_static: M must be >= 0, N and K positive multiples of 16");
+        return 1;
+    }
+    const int effective = smm::effective_splits(K, splits);
+    if (M > smm::kStaticMaxM || N > smm::kStaticMaxN || effective > smm::kStaticMaxSplits) {
+        char text[200];
+        snprintf(text, sizeof(text),
+                 "scaled_mm_splitk_static: M=%lld N=%lld splits=%d exceeds the built-in scratch (M <= %lld, N <= %lld, splits <= %d); "
+                 "use launch_scaled_mm_splitk with caller scratch",
+                 static_cast<long long>(M), static_cast<long long>(N), effective, static_cast<long long>(smm::kStaticMaxM),
+                 static_cast<long long>(smm::kStaticMaxN), smm::kStaticMaxSplits);
+        smm::write_message(error_message, error_capacity, text);
+        return 2;
+    }
+    if (M == 0) return 0;
+    cudaError_t error = cudaSuccess;
+    unsigned char* const scratch = smm::static_scratch_address(&error);
+    if (scratch == nullptr) {
+        smm::write_message(error_message, error_capacity, cudaGetErrorString(error));
+        return 3;
+    }
+    float* const partials = reinterpret_cast<float*>(scratch);
+    uint32_t* const counters = reinterpret_cast<uint32_t*>(scratch + smm::kStaticPartialBytes);
+    // the tickets must start at zero whatever an earlier (possibly interrupted) call left behind
+    error = cudaMemsetAsync(counters, 0, smm::kStaticCounterBytes, stream);
+    if (error != cudaSuccess) {
+        smm::write_message(error_message, error_capacity, cudaGetErrorString(error));
+        return 3;
+    }
+    const smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
+                               use_fp8_e5m2, a_bf16, output_bf16, stream};
+    if (!smm::launch_skinny(args, splits, partials, counters)) {
+        smm::write_message(error_message, error_capacity, "scaled_mm_splitk_static: the kernel launch failed");
+        return 3;
+    }
+    return 0;
 }
 
 // Reads (and clears) the status record the kernel's bounded waits report into: out[0] = wait site

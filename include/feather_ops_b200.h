@@ -13,6 +13,7 @@
 #define FEATHER_OPS_B200_H_
 
 #include <stdbool.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -43,6 +44,17 @@ bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prepacked, cons
 /* Number of floats of `partials` scratch launch_scaled_mm_splitk needs (0 when the request collapses to one split).
  * No counterpart in the reference. */
 int64_t feather_scaled_mm_splitk_partial_floats(int64_t M, int64_t N, int64_t K, int splits);
+
+/* launch_scaled_mm_splitk for hosts that cannot allocate device memory (a serving loop that gave all free memory to its
+ * own arena, an FFI plugin without a device allocator, a callback in which allocation calls are forbidden): the partials
+ * and tickets live in a 4 MiB + 1 KiB __device__ array inside the library, so no scratch is passed and nothing is
+ * allocated. Limits: M <= 16, N <= 16384, at most 4 effective splits. Returns 0 = enqueued, 1 = invalid arguments,
+ * 2 = larger than the built-in scratch, 3 = a CUDA call failed; error_message (may be NULL) receives the reason.
+ * The first call on a device looks the array's address up (make it before any stream capture). All calls share
+ * the array, so calls that overlap on the device race. This entry point has no counterpart in the reference. */
+int launch_scaled_mm_splitk_static(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
+                                   int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
+                                   bool output_bf16, int splits, feather_stream_t stream, char* error_message, size_t error_capacity);
 
 /* Diagnostic: reads and clears the record that the scaled_mm kernel's bounded device waits report into.
  * out[0] = 0 when every wait completed, else the wait site; out[1] = block index. Synchronizes the device.
