@@ -1,6 +1,7 @@
-// Thin torch extension over the C ABI: registers the four `torch.ops.feather_ops.*` operators with the
+// Thin torch extension over the C ABI: registers the `torch.ops.feather_ops.*` operators: four with the
 // schemas of the reference (csrc/hip_kernel.cu:825-846, csrc/hip_kernel_int8.cu:564-586 and :972-980,
-// csrc/hip_conv2d_3x3.cu:672-692), validates tensors with the reference's messages, takes the current
+// csrc/hip_conv2d_3x3.cu:672-692) and `scaled_mm_splitk` (the skinny-M launcher over caller scratch, no
+// counterpart in the reference). It validates tensors with the reference's messages, takes the current
 // CUDA stream of the input's device and forwards raw pointers to libfeather_ops_b200.so. Built against
 // torch's stable ABI, so it does not depend on libtorch_python. Nothing here computes or allocates.
 #include <Python.h>
