@@ -1,6 +1,9 @@
 """Per-operator measurements of the BASELINE configurations (everything except the headline step of bench.py).
 
-    python -m feather_ops_b200.benchmarks [scaled_mm] [msweep] [int8] [conv]      # default: all
+    python -m feather_ops_b200.benchmarks [scaled_mm] [msweep] [int8] [conv] [--profile]     # default: all groups
+
+`--profile` is for runs under a profiler: every case makes three plain launches (no CUDA graph, no timing), so a
+capture of one kernel stays a handful of launches; the printed times are then null.
 
 Protocol (after the reference's bench/protocol.py): warm-up, then rounds of back-to-back launches inside
 one CUDA-event pair, median over the rounds. The launches of a round are replayed from a CUDA graph so that
@@ -22,8 +25,16 @@ INT8_NOMINAL_TOPS = 4500.0
 BF16_NOMINAL_TFLOPS = 2250.0
 
 
+PROFILE_MODE = False
+
+
 def time_graph(launch, sets: int, rounds: int = 5, launches_per_round: int = 20) -> float:
     """Median microseconds per launch. `launch(i)` enqueues one launch on buffer set `i % sets`."""
+    if PROFILE_MODE:
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        return float("nan")
     for i in range(max(3, sets)):
         launch(i)
     torch.cuda.synchronize()
@@ -49,6 +60,7 @@ def sets_for(bytes_per_set: int, cold: bool) -> int:
 
 
 def emit(**fields) -> None:
+    fields = {k: (None if isinstance(v, float) and v != v else v) for k, v in fields.items()}
     print(json.dumps(fields), flush=True)
 
 
@@ -165,6 +177,8 @@ def main(argv):
         raise SystemExit("the benchmarks need a CUDA device: the kernels have no CPU fallback")
     import feather_ops_b200  # noqa: F401
 
+    global PROFILE_MODE
+    PROFILE_MODE = "--profile" in argv
     device = torch.device("cuda")
     groups = {"scaled_mm": bench_scaled_mm, "msweep": bench_msweep, "int8": bench_int8, "conv": bench_conv}
     chosen = [a for a in argv if a in groups] or list(groups)

@@ -410,44 +410,59 @@ __global__ void __launch_bounds__(kThreads, 1) int8_mm_kernel(const __grid_const
 
 // ---------------------------------------------------------------------------------------------------------
 // CTA-pair version (tcgen05 cta_group::2): a cluster of two CTAs owns a 256 x 256 output tile. CTA r loads
-// activation rows [128 r, +128) by TMA and re-lays out weight rows (output columns) [128 r, +128) of the
-// tile; the UMMA (M = 256, N = 256, K = 32) is issued by CTA 0 and reads both CTAs' shared memory, so each
-// SM moves half of the weight tile per UMMA. The re-layout goes through registers: a thread owns four
-// operand rows x one 16-byte chunk, loads the four 16-byte micro-tiles that hold them (the loads of the
-// next three k blocks are in flight while one is stored, in register sets with static roles), picks
-// dwords (forward) or transposes 4x4 bytes (backward), and stores with eight lanes covering one full
-// 128-byte swizzled row, which is conflict free.
+// activation rows [128 r, +128) and the raw micro-tiles of weight rows (output columns) [128 r, +128) of the
+// tile by TMA; the UMMA (M = 256, N = 256, K = 32) is issued by CTA 0 and reads both CTAs' shared memory.
+//
+// Raw weight slab of one k block: 32 x 32 micro-tiles of 16 bytes, fetched as four boxes of 32 rows x 128
+// bytes with the 128-byte swizzle. In global memory a slab row is one step of the slower micro-tile axis
+// (forward: the contraction, backward: the output axis), so the same box shape serves both directions.
+// The re-layout warps go shared -> registers -> shared: unit (group g = four operand rows, chunk c = 16
+// contraction bytes) reads the four micro-tiles (contraction step 4 c + j, output step g), picks dwords
+// (forward) or transposes 4x4 bytes (backward) and writes four 16-byte chunks of the swizzled K-major
+// operand. The eight lanes of a quarter warp take g % 8 = l and c = l ^ t: both their 16-byte loads and
+// their 16-byte stores then fall into eight different bank groups (the swizzle phases of the rows they touch
+// differ in bit 2 exactly when l is odd), so neither side has bank conflicts. Global loads that feed
+// registers directly (the previous version) ran at one k block per L2 latency whatever the prefetch depth.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kPairAStages = 6;
-constexpr int kPairOperandStages = 5;
+// Ring depths are multiples of the team count: a team always meets the same slots and sees every phase of the
+// barriers it waits on.
+constexpr int kPairLoadStages = 4;
+constexpr int kPairOperandStages = 4;
+constexpr int kPairTeams = 2;
+static_assert(kPairLoadStages % kPairTeams == 0 && kPairOperandStages % kPairTeams == 0, "ring depths must be multiples of the team count");
 constexpr int kPairHalfN = 128;
 constexpr int kPairN = 2 * kPairHalfN;
 constexpr int kPairRelayoutWarps = 8;
 constexpr int kPairThreads = 32 * (kFirstRelayoutWarp + kPairRelayoutWarps);
+constexpr int kRawBoxBytes = 32 * 128;
 
 struct PairSmem {
+    static constexpr int kRawBytes = 4 * kRawBoxBytes;       // 16 KB: 32 x 32 micro-tiles
     static constexpr int kOperandBytes = kPairHalfN * 128;  // 16 KB
     static constexpr int kAOff = 0;
-    static constexpr int kOperandOff = kAOff + kPairAStages * kATileBytes;
-    static constexpr int kBarOff = kOperandOff + kPairOperandStages * kOperandBytes;
-    static constexpr int kNumBars = 2 * kPairAStages + 2 * kPairOperandStages + 4;
+    static constexpr int kRawOff = kAOff + kPairLoadStages * kATileBytes;
+    static constexpr int kOperandOff = kRawOff + kPairLoadStages * kRawBytes;
+    static constexpr int kColumnOff = kOperandOff + kPairOperandStages * kOperandBytes;  // 2 x (256 scales + 256 biases), fp32
+    static constexpr int kBarOff = kColumnOff + 2 * 2 * kPairN * 4;
+    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 6;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
 
 template <bool kTransposedB, bool kOutBf16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
-int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
+int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
     using L = PairSmem;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-    uint64_t* const a_full = bars;                                   // local: TMA bytes of this CTA's rows
-    uint64_t* const a_empty = a_full + kPairAStages;                 // signalled in both CTAs by CTA 0's commits
-    uint64_t* const operand_full = a_empty + kPairAStages;           // CTA 0 only: both CTAs' warps arrive here
+    uint64_t* const load_full = bars;                                // local: TMA bytes of this CTA's halves
+    uint64_t* const load_empty = load_full + kPairLoadStages;        // signalled in both CTAs by CTA 0's commits
+    uint64_t* const operand_full = load_empty + kPairLoadStages;     // CTA 0 only: both CTAs' warps arrive here
     uint64_t* const operand_empty = operand_full + kPairOperandStages;
     uint64_t* const tmem_full = operand_empty + kPairOperandStages;
     uint64_t* const tmem_empty = tmem_full + 2;                      // CTA 0 only
+    uint64_t* const columns_full = tmem_empty + 2;                   // local: the tile's column scales and biases are staged
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
@@ -458,22 +473,24 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
 
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
-        for (int s = 0; s < kPairAStages; ++s) {
-            mbar_init(&a_full[s], 1);
-            mbar_init(&a_empty[s], 1);
+        for (int s = 0; s < kPairLoadStages; ++s) {
+            mbar_init(&load_full[s], 1);
+            mbar_init(&load_empty[s], 1);
         }
         for (int s = 0; s < kPairOperandStages; ++s) {
-            // the operand slot is complete when both CTAs' re-layout warps AND both CTAs' activation tiles are in:
-            // the re-layout warps wait for their CTA's activation tile before they arrive
-            mbar_init(&operand_full[s], 2 * kPairRelayoutWarps);
+            // complete when the team's warps of both CTAs have written their halves; a warp arrives only after
+            // its CTA's load (activation tile included) has landed, so the MMA thread needs no other wait
+            mbar_init(&operand_full[s], 2 * kPairRelayoutWarps / kPairTeams);
             mbar_init(&operand_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
+            mbar_init(&columns_full[s], kEpilogueWarps);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, 2 * kPairN);
@@ -493,18 +510,25 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
     const int tile_step = static_cast<int>(gridDim.x) / 2;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (this CTA's activation rows)
+        // ------------------------------------------------------------------ TMA producer (this CTA's halves)
         if (elect_one()) {
             Ring slot;
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
                 const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+                const int n0 = (tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = guard.wait(&a_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
+                    ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&a_full[slot.idx], kATileBytes);
-                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &a_full[slot.idx], kb * kBlockK, m0);
-                    slot.advance(kPairAStages);
+                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
+                    tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
+                    // map_b: x = byte offset along the faster micro-tile axis, y = step of the slower one
+                    const int x0 = kTransposedB ? kb * (kBlockK * 4) : n0 * 4;
+                    const int y0 = kTransposedB ? n0 / 4 : kb * (kBlockK / 4);
+                    uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+#pragma unroll
+                    for (int box = 0; box < 4; ++box) tma_load_2d(raw + box * kRawBoxBytes, &map_b, &load_full[slot.idx], x0 + box * 128, y0);
+                    slot.advance(kPairLoadStages);
                 }
             }
         }
@@ -519,8 +543,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc.idx * kPairN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = guard.wait(&a_full[slot.idx], slot.phase, kSiteLoadFull) &&
-                         guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
+                    ok = guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
@@ -532,10 +555,10 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
                     }
 #pragma unroll
                     for (uint32_t dst = 0; dst < 2; ++dst) {
-                        umma_commit_pair(map_to_cta(smem_u32(&a_empty[slot.idx]), dst));
+                        umma_commit_pair(map_to_cta(smem_u32(&load_empty[slot.idx]), dst));
                         umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
                     }
-                    slot.advance(kPairAStages);
+                    slot.advance(kPairLoadStages);
                     operand.advance(kPairOperandStages);
                 }
                 if (!ok) break;
@@ -546,13 +569,34 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
         }
     } else if (warp < kFirstRelayoutWarp) {
         // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
+        // The column scales and biases of a tile are staged in shared memory once (each epilogue warp writes
+        // a quarter, one barrier arrival per warp) instead of being fetched per element. Two buffers, used
+        // alternately like the accumulators: a warp refills a buffer only after every warp has arrived for the
+        // tile in between, i.e. has finished reading it.
         const int quarter = warp % 4;
         const bool wide_rows = (p.N_out % 8) == 0;
+        const bool has_scale = !kTransposedB && p.b_scale != nullptr;
+        const bool has_bias = !kTransposedB && p.bias != nullptr;
         Ring acc;
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
             const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
             const int n0 = (tile / tiles_m) * kPairN;
+            float* const col_scale = reinterpret_cast<float*>(smem + L::kColumnOff) + acc.idx * 2 * kPairN;
+            float* const col_bias = col_scale + kPairN;
+            if (has_scale || has_bias) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int c = quarter * 64 + i * 32 + lane;
+                    const int col = n0 + c;
+                    col_scale[c] = has_scale && col < p.N_out ? __ldg(p.b_scale + col) : 1.0f;
+                    col_bias[c] = has_bias && col < p.N_out ? out_bits_to_float<kOutBf16>(__ldg(p.bias + col)) : 0.0f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&columns_full[acc.idx]);
+                ok = guard.wait(&columns_full[acc.idx], acc.phase, kSiteTmemFull, 3);
+                if (!ok) break;
+            }
             ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
             if (!ok) break;
             tc_fence_after_sync();
@@ -573,17 +617,22 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
                 const int col0 = n0 + c * 32;
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    const int col = col0 + g * 4;
-                    if (col >= p.N_out) continue;
                     float f[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        float value = static_cast<float>(static_cast<int32_t>(v[g * 4 + i])) * row_scale;
-                        if constexpr (!kTransposedB) {
-                            if (p.b_scale != nullptr) value *= __ldg(p.b_scale + col + i);
-                            if (p.bias != nullptr) value += out_bits_to_float<kOutBf16>(__ldg(p.bias + col + i));
-                        }
-                        f[i] = value;
+                    for (int i = 0; i < 4; ++i) f[i] = static_cast<float>(static_cast<int32_t>(v[g * 4 + i])) * row_scale;
+                    if (has_scale) {
+                        const float4 s4 = *reinterpret_cast<const float4*>(col_scale + c * 32 + g * 4);
+                        f[0] *= s4.x;
+                        f[1] *= s4.y;
+                        f[2] *= s4.z;
+                        f[3] *= s4.w;
+                    }
+                    if (has_bias) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(col_bias + c * 32 + g * 4);
+                        f[0] += b4.x;
+                        f[1] += b4.y;
+                        f[2] += b4.z;
+                        f[3] += b4.w;
                     }
                     v[g * 4] = pack_out<kOutBf16>(f[0], f[1]);
                     v[g * 4 + 1] = pack_out<kOutBf16>(f[2], f[3]);
@@ -610,87 +659,70 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const Params p) {
         }
     } else {
         // ------------------------------------------------------------------ weight re-layout warps (this CTA's 128 operand rows)
-        // thread = (row group g: operand rows 4 g .. 4 g + 3, chunk c: contraction bytes 16 c .. 16 c + 15)
-        // A quarter warp covers 4 chunks x 2 row groups: its eight 16-byte stores land in eight different
-        // bank groups (rows 4 apart flip bit 2 of the swizzle phase), and a warp's loads cover whole 128-byte
-        // lines of the prepack (8 consecutive micro-tiles of 4 contraction steps).
-        const int rw = warp - kFirstRelayoutWarp;
-        const int chunk = (lane & 3) + 4 * (rw & 1);
-        const int group = (lane >> 2) + 8 * (rw >> 1);  // 0..31
-        const uint4* const tiles = reinterpret_cast<const uint4*>(p.b);
-        const int k4_total = p.K / 4;
-        const int out4_total = p.N_out / 4;
-
-        auto fetch = [&](int tile, int kb, uint4 (&m)[4]) {
-            const int out4 = ((tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN) / 4 + group;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int kc4 = kb * (kBlockK / 4) + chunk * 4 + j;
-                const bool live = out4 < out4_total && kc4 < k4_total;
-                m[j] = live ? __ldg(tiles + static_cast<int64_t>(kc4) * p.stride_kc + static_cast<int64_t>(out4) * p.stride_out) : make_uint4(0u, 0u, 0u, 0u);
-            }
-        };
-
-        // Register pipeline: kPrefetch register sets, used round robin with static indices (the loop over the
-        // sets is fully unrolled, no set is ever copied: a copy would wait for the load it copies). Set d holds
-        // the micro-tiles of k block `it` with it % kPrefetch == d and is refilled for k block it + kPrefetch
-        // right after it has been stored, so kPrefetch - 1 k blocks of loads are always in flight.
-        constexpr int kPrefetch = 4;  // measured: 2, 4 and 6 sets are within 5 % of each other
+        constexpr int kTeamThreads = kPairRelayoutWarps * 32 / kPairTeams;
+        constexpr int kUnitsPerThread = 256 / kTeamThreads;  // 32 groups x 8 chunks per k block
+        const int relayout_thread = static_cast<int>(threadIdx.x) - kFirstRelayoutWarp * 32;
+        const int team = relayout_thread / kTeamThreads;
+        const int t = relayout_thread % kTeamThreads;
+        const uint32_t l = static_cast<uint32_t>(t) & 7u;
         Ring slot, operand;
         bool ok = true;
-        int fetch_tile = first_tile;  // cursor of the load stream
-        int fetch_kb = 0;
-        int store_tile = first_tile;  // cursor of the store stream
-        int store_kb = 0;
-        uint4 pre[kPrefetch][4];
+        uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (turn == static_cast<uint32_t>(team)) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                         guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                    if (!ok) break;
+                    const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                    uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                    uint4 m[kUnitsPerThread][4];
 #pragma unroll
-        for (int d = 0; d < kPrefetch; ++d) {
-            if (fetch_tile < num_tiles) fetch(fetch_tile, fetch_kb, pre[d]);
-            if (++fetch_kb == num_kb) {
-                fetch_kb = 0;
-                fetch_tile += tile_step;
-            }
-        }
-        while (ok && store_tile < num_tiles) {
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        const uint32_t set = static_cast<uint32_t>(t + i * kTeamThreads) >> 3;  // 0..31
+                        const uint32_t group = 8u * (set & 3u) + l;
+                        const uint32_t chunk = l ^ (set >> 2);
 #pragma unroll
-            for (int d = 0; d < kPrefetch; ++d) {
-                if (!ok || store_tile >= num_tiles) break;
-                ok = guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
-                if (!ok) break;
-                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
-                uint32_t rows[4][4];  // rows[j][r]: contraction bytes 4 j .. 4 j + 3 of operand row 4 group + r
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t in[4] = {pre[d][j].x, pre[d][j].y, pre[d][j].z, pre[d][j].w};
-                    if constexpr (kTransposedB) {
-                        transpose4x4(in, rows[j]);
-                    } else {
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) rows[j][r] = in[r];
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            uint32_t offset;
+                            if constexpr (kTransposedB) {
+                                // slab row = output step, micro-tile column = contraction step 4 chunk + j
+                                offset = (chunk >> 1) * kRawBoxBytes + sw128_offset(group, 4u * (chunk & 1u) + j);
+                            } else {
+                                // slab row = contraction step 4 chunk + j, micro-tile column = output step
+                                offset = (group >> 3) * kRawBoxBytes + sw128_offset(4u * chunk + j, group & 7u);
+                            }
+                            m[i][j] = *reinterpret_cast<const uint4*>(raw + offset);
+                        }
                     }
-                }
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(group * 4 + r, chunk)) = make_uint4(rows[0][r], rows[1][r], rows[2][r], rows[3][r]);
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        const uint32_t set = static_cast<uint32_t>(t + i * kTeamThreads) >> 3;
+                        const uint32_t group = 8u * (set & 3u) + l;
+                        const uint32_t chunk = l ^ (set >> 2);
+                        uint32_t rows[4][4];  // rows[j][r]: contraction bytes 4 j .. 4 j + 3 of operand row 4 group + r
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t in[4] = {m[i][j].x, m[i][j].y, m[i][j].z, m[i][j].w};
+                            if constexpr (kTransposedB) {
+                                transpose4x4(in, rows[j]);
+                            } else {
+#pragma unroll
+                                for (int r = 0; r < 4; ++r) rows[j][r] = in[r];
+                            }
+                        }
+#pragma unroll
+                        for (uint32_t r = 0; r < 4; ++r) {
+                            *reinterpret_cast<uint4*>(dst + sw128_offset(group * 4u + r, chunk)) = make_uint4(rows[0][r], rows[1][r], rows[2][r], rows[3][r]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
                 }
-                // refill this set for the k block kPrefetch ahead
-                if (fetch_tile < num_tiles) fetch(fetch_tile, fetch_kb, pre[d]);
-                if (++fetch_kb == num_kb) {
-                    fetch_kb = 0;
-                    fetch_tile += tile_step;
-                }
-                fence_proxy_async_smem();
-                // the activation tile of this k block must have landed in this CTA before the slot is published
-                ok = guard.wait(&a_full[slot.idx], slot.phase, kSiteLoadFull, 2);
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
-                slot.advance(kPairAStages);
+                turn = turn + 1 == kPairTeams ? 0 : turn + 1;
+                slot.advance(kPairLoadStages);
                 operand.advance(kPairOperandStages);
-                if (++store_kb == num_kb) {
-                    store_kb = 0;
-                    store_tile += tile_step;
-                }
             }
         }
     }
@@ -798,6 +830,16 @@ bool launch_pair_instance(const LaunchArgs& args) {
     const uint64_t strides[1] = {static_cast<uint64_t>(args.K)};
     const uint32_t box[2] = {kBlockK, kBlockM};
     if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    // weight as a 2-D byte array: x runs along the micro-tile axis with stride 1 (forward: output steps,
+    // backward: contraction steps), y along the other one
+    CUtensorMap map_b;
+    const uint64_t fast_tiles = static_cast<uint64_t>((kTransposedB ? args.K : args.N_out) / 4);
+    const uint64_t slow_tiles = static_cast<uint64_t>((kTransposedB ? args.N_out : args.K) / 4);
+    const uint64_t slow_stride = static_cast<uint64_t>(kTransposedB ? args.stride_out : args.stride_kc);
+    const uint64_t b_dims[2] = {fast_tiles * 16, slow_tiles};
+    const uint64_t b_strides[1] = {slow_stride * 16};
+    const uint32_t b_box[2] = {128, 32};
+    if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
 
     Params p{};
     p.b = args.b;
@@ -816,8 +858,17 @@ bool launch_pair_instance(const LaunchArgs& args) {
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int pairs = resident_pairs[dev];
     const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
-    kernel<<<grid, kPairThreads, L::kDynamic, args.stream>>>(map_a, p);
+    kernel<<<grid, kPairThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
+}
+
+// The pair kernel fetches the weight by TMA: the micro-tile axis that its boxes run along must be contiguous,
+// the other stride must fit a tensor map, and the base must be 16-byte aligned.
+bool pair_eligible(const LaunchArgs& args) {
+    const int64_t fast = args.transposed_b ? args.stride_kc : args.stride_out;
+    const int64_t slow = args.transposed_b ? args.stride_out : args.stride_kc;
+    const int64_t fast_tiles = (args.transposed_b ? args.K : args.N_out) / 4;
+    return fast == 1 && slow >= fast_tiles && slow < (int64_t{1} << 34) && (reinterpret_cast<uintptr_t>(args.b) & 15u) == 0;
 }
 
 bool launch_pair(const LaunchArgs& args) {
@@ -856,7 +907,7 @@ extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const f
                                 transposed_b, output_dtype != 0, stream};
     if (block_n >= 256) {
         // a pair tile is 256 rows tall: worth it as soon as there is more than one 128-row tile
-        if (M > i8mm::kBlockM) return i8mm::launch_pair(args);
+        if (M > i8mm::kBlockM && i8mm::pair_eligible(args)) return i8mm::launch_pair(args);
         return i8mm::launch_for_block_n<256>(args);
     }
     if (block_n >= 128) return i8mm::launch_for_block_n<128>(args);
