@@ -8,7 +8,7 @@
 //
 // One persistent CTA per SM walks tiles of 128 output channels x (rows x BN) pixels, one launch for the
 // whole batch. Per 16-channel group (one pipeline slot):
-//   * warp 0 (TMA): the group's 18 weight rows x 128 channels land as [18][128][16 B], which already is
+//   * warp 0 (TMA): the group's 18 weight rows x 128 channels (2 KB contiguous each) land as [18][128][16 B], which already is
 //     the no-swizzle K-major UMMA layout (8-channel core matrices 128 B apart, K-adjacent ones 2 KB apart).
 //     Output channels past C_out are zero filled by the TMA unit.
 //   * sixteen gather warps in two alternating teams: read the (rows + 2) x (BN + 2) halo tile of the
@@ -27,6 +27,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <cstdlib>
 
 namespace feather {
 namespace conv {
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
                     ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes);
-                    tma_load_3d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], 0, tc.m0, g * kWeightRows);
+                    tma_load_2d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], tc.m0 * 2, g * kWeightRows);
                 }
             }
         }
@@ -179,13 +181,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
                     tc_fence_after_sync();
                     const uint32_t w_addr = smem_u32(weight_smem + s * kWeightStageBytes);
                     const uint32_t x_addr = smem_u32(act_smem + s * p.act_stage_bytes);
-#pragma unroll 1
+                    // the start address sits in the low bits of a descriptor in 16-byte units: a tap is an addition
+                    const uint64_t desc_w0 = make_smem_desc(w_addr, kBlockM * 16, 128, kSwizzleNone);
+                    const uint64_t desc_x0 = make_smem_desc(x_addr, plane_bytes, 128, kSwizzleNone);
+#pragma unroll
                     for (int tap = 0; tap < 9; ++tap) {
                         const int kh = tap / 3;
                         const int kw = tap % 3;
-                        const uint64_t desc_w = make_smem_desc(w_addr + tap * 2 * (kBlockM * 16), kBlockM * 16, 128, kSwizzleNone);
+                        const uint64_t desc_w = desc_w0 + static_cast<uint64_t>(tap * 2 * kBlockM);
                         for (int r = 0; r < p.rows; ++r) {
-                            const uint64_t desc_x = make_smem_desc(x_addr + ((r + kh) * halo_cols + kw) * 16, plane_bytes, 128, kSwizzleNone);
+                            const uint64_t desc_x = desc_x0 + static_cast<uint64_t>((r + kh) * halo_cols + kw);
                             umma_f16(tmem_d + r * p.bn, desc_w, desc_x, p.idesc, (g | tap) != 0 ? 1u : 0u);
                         }
                     }
@@ -266,48 +271,58 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
         for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
             const TileCoord tc = tile_coord(p, tile);
             const uint16_t* const x_img = p.x + static_cast<int64_t>(tc.b) * p.C_in * hw;
+            // The item geometry depends on the tile only: decode it once, so that the per-group work is loads,
+            // byte permutes and stores. `kind`: 0 = nothing (past the item list or outside the image, where the
+            // zeros are stored without loading), 1 = single pixel, 2 = pixel pair.
+            int64_t src_off[kMaxItems];   // element offset of channel (plane * 8) of group 0 at the item's first pixel
+            int dst_off[kMaxItems];       // byte offset inside the stage; < 0: no item
+            uint32_t kinds = 0;            // 4 bits per item: kind | in_image << 2 | plane << 3
+#pragma unroll
+            for (int j = 0; j < kMaxItems; ++j) {
+                const int item = t + j * kTeamThreads;
+                src_off[j] = 0;
+                dst_off[j] = -1;
+                if (item < items) {
+                    const int plane = item / (halo_rows * per_row);
+                    const int rem = item % (halo_rows * per_row);
+                    const int hr = rem / per_row;
+                    const int e = rem % per_row;
+                    int hc;       // first halo column of the item
+                    bool pair;
+                    if (p.pairs) {
+                        pair = e < p.bn / 2;
+                        hc = pair ? 1 + 2 * e : (e == p.bn / 2 ? 0 : p.bn + 1);
+                    } else {
+                        pair = false;
+                        hc = e;
+                    }
+                    const int h = tc.h0 - 1 + hr;
+                    const int w = tc.w0 - 1 + hc;
+                    const bool in_image = h >= 0 && h < p.H && w >= 0 && w < p.W;
+                    src_off[j] = static_cast<int64_t>(plane) * 8 * hw + static_cast<int64_t>(in_image ? h : 0) * p.W + (in_image ? w : 0);
+                    dst_off[j] = plane * plane_bytes + (hr * halo_cols + hc) * 16;
+                    kinds |= ((pair ? 2u : 1u) | (in_image ? 4u : 0u) | (plane ? 8u : 0u)) << (4 * j);
+                }
+            }
             for (int g = 0; g < p.groups; ++g, ++it) {
                 if (static_cast<int>(it & 1u) != team) continue;
                 const uint32_t s = it % kStages;
                 const uint32_t phase = (it / kStages) & 1u;
+                const uint16_t* const x_group = x_img + static_cast<int64_t>(g) * 16 * hw;
+                const bool second_plane_live = g * 16 + 8 < p.C_in;  // C_in is a multiple of 8: a plane is whole or absent
                 // issue every load of this thread's items first, so they are all in flight together
                 uint32_t v[kMaxItems][8];
-                int dst_off[kMaxItems];
-                int kind[kMaxItems];  // 0 = nothing, 1 = single pixel, 2 = pixel pair
 #pragma unroll
                 for (int j = 0; j < kMaxItems; ++j) {
-                    const int item = t + j * kTeamThreads;
-                    kind[j] = 0;
-                    dst_off[j] = 0;
-                    if (item < items) {
-                        const int plane = item / (halo_rows * per_row);
-                        const int rem = item % (halo_rows * per_row);
-                        const int hr = rem / per_row;
-                        const int e = rem % per_row;
-                        int hc;       // first halo column of the item
-                        bool pair;
-                        if (p.pairs) {
-                            pair = e < p.bn / 2;
-                            hc = pair ? 1 + 2 * e : (e == p.bn / 2 ? 0 : p.bn + 1);
-                        } else {
-                            pair = false;
-                            hc = e;
-                        }
-                        const int h = tc.h0 - 1 + hr;
-                        const int w = tc.w0 - 1 + hc;
-                        const bool in_image = h >= 0 && h < p.H && w >= 0 && w < p.W;
-                        const int c_first = g * 16 + plane * 8;
-                        const uint16_t* const src = x_img + static_cast<int64_t>(c_first) * hw + static_cast<int64_t>(in_image ? h : 0) * p.W + (in_image ? w : 0);
-                        kind[j] = pair ? 2 : 1;
-                        dst_off[j] = plane * plane_bytes + (hr * halo_cols + hc) * 16;
+                    const uint32_t k = (kinds >> (4 * j)) & 15u;
+                    const bool live = (k & 4u) != 0 && ((k & 8u) == 0 || second_plane_live);
+                    const uint16_t* const src = x_group + src_off[j];
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const bool live = in_image && c_first + c < p.C_in;
-                            if (pair) {
-                                v[j][c] = live ? __ldg(reinterpret_cast<const uint32_t*>(src + c * hw)) : 0u;
-                            } else {
-                                v[j][c] = live ? static_cast<uint32_t>(__ldg(src + c * hw)) : 0u;
-                            }
+                    for (int c = 0; c < 8; ++c) {
+                        if ((k & 2u) != 0) {
+                            v[j][c] = live ? __ldg(reinterpret_cast<const uint32_t*>(src + c * hw)) : 0u;
+                        } else {
+                            v[j][c] = live ? static_cast<uint32_t>(__ldg(src + c * hw)) : 0u;
                         }
                     }
                 }
@@ -316,12 +331,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
                 uint8_t* const dst = act_smem + s * p.act_stage_bytes;
 #pragma unroll
                 for (int j = 0; j < kMaxItems; ++j) {
-                    if (kind[j] == 0) continue;
+                    if (dst_off[j] < 0) continue;
                     // low halves = this pixel (the only one of a single), high halves = the pair's second pixel
                     const uint4 first = make_uint4(__byte_perm(v[j][0], v[j][1], 0x5410u), __byte_perm(v[j][2], v[j][3], 0x5410u),
                                                    __byte_perm(v[j][4], v[j][5], 0x5410u), __byte_perm(v[j][6], v[j][7], 0x5410u));
                     *reinterpret_cast<uint4*>(dst + dst_off[j]) = first;
-                    if (kind[j] == 2) {
+                    if (((kinds >> (4 * j)) & 2u) != 0) {
                         const uint4 second = make_uint4(__byte_perm(v[j][0], v[j][1], 0x7632u), __byte_perm(v[j][2], v[j][3], 0x7632u),
                                                         __byte_perm(v[j][4], v[j][5], 0x7632u), __byte_perm(v[j][6], v[j][7], 0x7632u));
                         *reinterpret_cast<uint4*>(dst + dst_off[j] + 16) = second;
@@ -347,6 +362,368 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 2 * kAccColumns);
     }
+}
+
+// The prepacked weight as a 2-D array of 8-byte words: x = 2 words per output channel (its eight input
+// channels of one row), y = prepack row. A box of 256 words x 18 rows is the group's tile for 128 output
+// channels, every box row one contiguous 2 KB run. (Described as [8 elements][C_out][rows] with 16-byte box
+// rows, the copy engine fetched a 32-byte sector and spent one row slot per output channel: twice the L2
+// traffic and most of the time of a group.)
+inline bool encode_weight_map(CUtensorMap* map, const void* wp, int C_out, int groups) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(C_out) * 2, static_cast<uint64_t>(groups) * kWeightRows};
+    const uint64_t strides[1] = {static_cast<uint64_t>(C_out) * 16};
+    const uint32_t box[2] = {2 * kBlockM, kWeightRows};
+    return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_INT64, 2, wp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair version (tcgen05 cta_group::2) for C_out > 128: a cluster of two CTAs owns 256 output channels x
+// two output rows x 128 pixels. CTA r loads the weights of output channels [128 r, +128) and gathers the
+// halo tile (3 rows x 130 columns) of output row h0 + r; the UMMA (M = 256, N = 256, K = 16) is issued by
+// CTA 0, takes the 128 pixels of each CTA as one half of its N extent and leaves 128 channels x 256 pixels in
+// each CTA's tensor memory (columns 0..127: row h0, 128..255: row h0 + 1). Against the one-CTA kernel with the
+// same tile, every SM gathers 3 halo rows instead of 4 per 256 pixels, the UMMA reads half as much shared
+// memory per flop (the measured limiter of the one-CTA kernel), and the 256-wide UMMA spends a smaller share
+// of its time loading the weight operand (162 clocks per 128 x 256 x 16 against 2 x 98 for two 128-wide ones).
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kPairStages = 4;
+constexpr int kPairBN = 128;                       // pixels per CTA (one output row segment)
+constexpr int kPairHaloCols = kPairBN + 2;
+constexpr int kPairHaloRows = 3;
+constexpr int kPairPlaneBytes = kPairHaloRows * kPairHaloCols * 16;
+constexpr int kPairActStageBytes = (2 * kPairPlaneBytes + 127) / 128 * 128;
+constexpr int kPairItems = 2;                      // gather items per thread per slot (396 items, 256 threads per team)
+constexpr int kPairSmemBytes = kPairStages * (kWeightStageBytes + kPairActStageBytes) + (3 * kPairStages + 4) * 8 + 16 + 1024;
+
+template <bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* const weight_smem = smem;
+    uint8_t* const act_smem = smem + kPairStages * kWeightStageBytes;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(act_smem + kPairStages * kPairActStageBytes);
+    uint64_t* const weight_full = bars;                        // local: this CTA's weight rows have landed
+    uint64_t* const act_full = weight_full + kPairStages;      // CTA 0 only: both CTAs' gather warps arrive here
+    uint64_t* const stage_empty = act_full + kPairStages;      // signalled in both CTAs by CTA 0's commits
+    uint64_t* const tmem_full = stage_empty + kPairStages;
+    uint64_t* const tmem_empty = tmem_full + 2;                // CTA 0 only
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* const abort_flag = tmem_slot + 1;
+
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const uint32_t cta = cluster_cta_rank();
+    const WaitGuard guard{abort_flag, g_status};
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0u;
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(&weight_full[s], 1);
+            // a gather warp arrives only after its own CTA's weights have landed, so this one barrier tells the
+            // MMA thread that both CTAs' operands of the slot are complete
+            mbar_init(&act_full[s], 2 * kTeamWarps);
+            mbar_init(&stage_empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&tmem_full[s], 1);
+            mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
+        }
+        mbar_init_fence();
+        tma_prefetch_desc(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, 2 * kAccColumns);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // tiles: output-channel pairs fastest, then pixel segments, then row pairs, then images
+    const int tiles_m = (p.C_out + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int tiles_w = (p.W + kPairBN - 1) / kPairBN;
+    const int tiles_h = (p.H + 1) / 2;
+    const int num_tiles = p.B * tiles_m * tiles_h * tiles_w;
+    const int first_tile = static_cast<int>(blockIdx.x) / 2;
+    const int tile_step = static_cast<int>(gridDim.x) / 2;
+    auto coord = [&](int tile) {
+        TileCoord t;
+        t.m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+        tile /= tiles_m;
+        t.w0 = (tile % tiles_w) * kPairBN;
+        tile /= tiles_w;
+        t.h0 = (tile % tiles_h) * 2;
+        t.b = tile / tiles_h;
+        return t;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (this CTA's weight rows)
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                const TileCoord tc = coord(tile);
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    const uint32_t s = it % kPairStages;
+                    const uint32_t phase = (it / kPairStages) & 1u;
+                    ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteLoadEmpty);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes);
+                    tma_load_2d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], tc.m0 * 2, g * kWeightRows);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (CTA 0 of the pair)
+        if (cta == 0 && elect_one()) {
+            uint32_t it = 0;
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++acc_it) {
+                const uint32_t acc = acc_it & 1u;
+                ok = guard.wait(&tmem_empty[acc], ((acc_it >> 1) & 1u) ^ 1u, kSiteTmemEmpty);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc * kAccColumns;
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    const uint32_t s = it % kPairStages;
+                    const uint32_t phase = (it / kPairStages) & 1u;
+                    ok = guard.wait(&act_full[s], phase, kSiteOperandFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t desc_w0 = make_smem_desc(smem_u32(weight_smem + s * kWeightStageBytes), kBlockM * 16, 128, kSwizzleNone);
+                    const uint64_t desc_x0 = make_smem_desc(smem_u32(act_smem + s * kPairActStageBytes), kPairPlaneBytes, 128, kSwizzleNone);
+#pragma unroll
+                    for (int tap = 0; tap < 9; ++tap) {
+                        const int kh = tap / 3;
+                        const int kw = tap % 3;
+                        umma_f16_pair(tmem_d, desc_w0 + static_cast<uint64_t>(tap * 2 * kBlockM),
+                                      desc_x0 + static_cast<uint64_t>(kh * kPairHaloCols + kw), p.idesc, (g | tap) != 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&stage_empty[s]), dst));
+                }
+                if (!ok) break;
+#pragma unroll
+                for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc]), dst));
+            }
+        }
+    } else if (warp < kFirstGatherWarp) {
+        // ------------------------------------------------------------------ epilogue (this CTA's 128 channels, both rows)
+        const int quarter = warp % 4;
+        const bool vector_rows = (p.W % 8) == 0;
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step, ++acc_it) {
+            const TileCoord tc = coord(tile);
+            const uint32_t acc = acc_it & 1u;
+            ok = guard.wait(&tmem_full[acc], (acc_it >> 1) & 1u, kSiteTmemFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int co = tc.m0 + quarter * 32 + lane;
+            const bool co_live = co < p.C_out;
+            const float bias = (p.bias != nullptr && co_live) ? bits_to_float<kBf16>(__ldg(p.bias + co)) : 0.0f;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccColumns;
+            constexpr int kChunks = kPairBN / 32;
+#pragma unroll 1
+            for (int r = 0; r < 2; ++r) {
+                const int h = tc.h0 + r;
+                uint16_t* const y_row = p.y + ((static_cast<int64_t>(tc.b) * p.C_out + (co_live ? co : 0)) * p.H + (h < p.H ? h : 0)) * p.W;
+#pragma unroll 1
+                for (int c = 0; c < kChunks; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + r * kPairBN + c * 32, v);
+                    tmem_wait_ld();
+                    if (r == 1 && c == kChunks - 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+                    }
+                    if (!co_live || h >= p.H) continue;
+                    const int w_first = tc.w0 + c * 32;
+                    if (vector_rows) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (w_first + g * 8 < p.W) {
+                                uint32_t o[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    o[i] = pack_out<kBf16>(__uint_as_float(v[g * 8 + 2 * i]) + bias, __uint_as_float(v[g * 8 + 2 * i + 1]) + bias);
+                                }
+                                *reinterpret_cast<uint4*>(y_row + w_first + g * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (w_first + i < p.W) {
+                                const uint32_t o = pack_out<kBf16>(__uint_as_float(v[i]) + bias, 0.0f);
+                                y_row[w_first + i] = static_cast<uint16_t>(o & 0xffffu);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ activation gather warps (output row h0 + cta)
+        // W is even here (the launcher checks): per (plane, halo row) the halo columns 1..128 as 64 aligned pixel
+        // pairs, then the edge columns 0 and 129 as single pixels.
+        const int team = (warp - kFirstGatherWarp) / kTeamWarps;
+        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kTeamWarps) * 32;
+        constexpr int kTeamThreads = kTeamWarps * 32;
+        constexpr int kPerRow = kPairBN / 2 + 2;
+        constexpr int kItems = 2 * kPairHaloRows * kPerRow;
+        static_assert(kItems <= kPairItems * kTeamThreads, "the halo tile must fit the per-thread item count");
+        const int64_t hw = static_cast<int64_t>(p.H) * p.W;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+            const TileCoord tc = coord(tile);
+            const uint16_t* const x_img = p.x + static_cast<int64_t>(tc.b) * p.C_in * hw;
+            int64_t src_off[kPairItems];
+            int dst_off[kPairItems];
+            uint32_t kinds = 0;  // 4 bits per item: kind (1 single, 2 pair) | in_image << 2 | plane << 3
+#pragma unroll
+            for (int j = 0; j < kPairItems; ++j) {
+                const int item = t + j * kTeamThreads;
+                src_off[j] = 0;
+                dst_off[j] = -1;
+                if (item < kItems) {
+                    const int plane = item / (kPairHaloRows * kPerRow);
+                    const int rem = item % (kPairHaloRows * kPerRow);
+                    const int hr = rem / kPerRow;
+                    const int e = rem % kPerRow;
+                    const bool pair = e < kPairBN / 2;
+                    const int hc = pair ? 1 + 2 * e : (e == kPairBN / 2 ? 0 : kPairBN + 1);
+                    const int h = tc.h0 + static_cast<int>(cta) - 1 + hr;
+                    const int w = tc.w0 - 1 + hc;
+                    const bool in_image = h >= 0 && h < p.H && w >= 0 && w < p.W;
+                    src_off[j] = static_cast<int64_t>(plane) * 8 * hw + static_cast<int64_t>(in_image ? h : 0) * p.W + (in_image ? w : 0);
+                    dst_off[j] = plane * kPairPlaneBytes + (hr * kPairHaloCols + hc) * 16;
+                    kinds |= ((pair ? 2u : 1u) | (in_image ? 4u : 0u) | (plane ? 8u : 0u)) << (4 * j);
+                }
+            }
+            for (int g = 0; g < p.groups; ++g, ++it) {
+                if (static_cast<int>(it & 1u) != team) continue;
+                const uint32_t s = it % kPairStages;
+                const uint32_t phase = (it / kPairStages) & 1u;
+                const uint16_t* const x_group = x_img + static_cast<int64_t>(g) * 16 * hw;
+                const bool second_plane_live = g * 16 + 8 < p.C_in;
+                uint32_t v[kPairItems][8];
+#pragma unroll
+                for (int j = 0; j < kPairItems; ++j) {
+                    const uint32_t k = (kinds >> (4 * j)) & 15u;
+                    const bool live = (k & 4u) != 0 && ((k & 8u) == 0 || second_plane_live);
+                    const uint16_t* const src = x_group + src_off[j];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        if ((k & 2u) != 0) {
+                            v[j][c] = live ? __ldg(reinterpret_cast<const uint32_t*>(src + c * hw)) : 0u;
+                        } else {
+                            v[j][c] = live ? static_cast<uint32_t>(__ldg(src + c * hw)) : 0u;
+                        }
+                    }
+                }
+                ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteOperandEmpty);
+                if (!ok) break;
+                uint8_t* const dst = act_smem + s * kPairActStageBytes;
+#pragma unroll
+                for (int j = 0; j < kPairItems; ++j) {
+                    if (dst_off[j] < 0) continue;
+                    const uint4 first = make_uint4(__byte_perm(v[j][0], v[j][1], 0x5410u), __byte_perm(v[j][2], v[j][3], 0x5410u),
+                                                   __byte_perm(v[j][4], v[j][5], 0x5410u), __byte_perm(v[j][6], v[j][7], 0x5410u));
+                    *reinterpret_cast<uint4*>(dst + dst_off[j]) = first;
+                    if (((kinds >> (4 * j)) & 2u) != 0) {
+                        const uint4 second = make_uint4(__byte_perm(v[j][0], v[j][1], 0x7632u), __byte_perm(v[j][2], v[j][3], 0x7632u),
+                                                        __byte_perm(v[j][4], v[j][5], 0x7632u), __byte_perm(v[j][6], v[j][7], 0x7632u));
+                        *reinterpret_cast<uint4*>(dst + dst_off[j] + 16) = second;
+                    }
+                }
+                fence_proxy_async_smem();
+                // this CTA's weight rows of the slot must have landed before the slot is published to the MMA thread
+                ok = guard.wait(&weight_full[s], phase, kSiteLoadFull, 2);
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&act_full[s]), 0));
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (guard.aborted()) {
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+    }
+    cluster_sync_all();  // neither CTA frees tensor memory while the pair's UMMAs may still write to it
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 2 * kAccColumns);
+    }
+}
+
+template <bool kBf16>
+int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W, cudaStream_t stream) {
+    auto* kernel = &conv3x3_pair_kernel<kBf16>;
+    Params p{};
+    p.x = static_cast<const uint16_t*>(x);
+    p.bias = static_cast<const uint16_t*>(bias);
+    p.y = static_cast<uint16_t*>(y);
+    p.B = B;
+    p.C_in = C_in;
+    p.C_out = C_out;
+    p.H = H;
+    p.W = W;
+    p.groups = (C_in + 15) / 16;
+    p.bn = kPairBN;
+    p.rows = 2;
+    p.idesc = make_idesc(kAccF32, kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, 2 * kPairBN);
+    p.pairs = 1;
+
+    static bool configured[64] = {};
+    static int resident_pairs[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 1;
+        // a persistent grid must be resident at once: a pair needs both SMs of a TPC
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = kPairSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = device_info().sm_count / 2;
+        }
+        resident_pairs[dev] = clusters;
+        configured[dev] = true;
+    }
+
+    CUtensorMap map_w;
+    if (!encode_weight_map(&map_w, wp, C_out, p.groups)) return 1;
+    const int64_t tiles_m = (C_out + 2 * kBlockM - 1) / (2 * kBlockM);
+    const int64_t num_tiles = static_cast<int64_t>(B) * tiles_m * ((H + 1) / 2) * ((W + kPairBN - 1) / kPairBN);
+    if (num_tiles > (1ll << 30)) return 1;
+    const int pairs = resident_pairs[dev];
+    const int grid = 2 * static_cast<int>(num_tiles < pairs ? num_tiles : pairs);
+    kernel<<<grid, kThreads, kPairSmemBytes, stream>>>(map_w, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
 template <bool kBf16>
@@ -384,13 +761,7 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
     }
 
     CUtensorMap map_w;
-    const uint64_t dims[3] = {8, static_cast<uint64_t>(C_out), static_cast<uint64_t>(p.groups) * kWeightRows};
-    const uint64_t strides[2] = {16, static_cast<uint64_t>(C_out) * 16};
-    const uint32_t box[3] = {8, kBlockM, kWeightRows};
-    if (!encode_map(&map_w, kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, wp, dims, strides, box,
-                    CU_TENSOR_MAP_SWIZZLE_NONE)) {
-        return 1;
-    }
+    if (!encode_weight_map(&map_w, wp, C_out, p.groups)) return 1;
     const int64_t num_tiles = static_cast<int64_t>(B) * p.tiles_m * p.tiles_h * p.tiles_w;
     if (num_tiles > (1ll << 30)) return 1;
     const int sms = device_info().sm_count;
@@ -424,6 +795,12 @@ extern "C" int feather_conv3x3_launch(const void* x, const void* wp, const void*
     if ((W & 1) != 0 && bn == 256) bn = 128;  // odd widths gather pixel by pixel: keep the item count per thread bounded
     const cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
     const void* const bias_ptr = has_bias ? bias : nullptr;
+    // two rows of 128 pixels and more than one 128-channel tile: the CTA-pair kernel computes the same tile
+    // shape (same accumulation order) with two SMs sharing the pixels
+    if (rows == 2 && bn == 128 && C_out > conv::kBlockM && std::getenv("FEATHER_CONV_PAIR_OFF") == nullptr) {
+        return is_bf16 != 0 ? conv::launch_pair<true>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, stream)
+                            : conv::launch_pair<false>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, stream);
+    }
     return is_bf16 != 0 ? conv::launch<true>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, bn, rows, stream)
                         : conv::launch<false>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, bn, rows, stream);
 }

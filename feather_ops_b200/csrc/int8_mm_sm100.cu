@@ -426,9 +426,18 @@ __global__ void __launch_bounds__(kThreads, 1) int8_mm_kernel(const __grid_const
 // ---------------------------------------------------------------------------------------------------------
 // Ring depths are multiples of the team count: a team always meets the same slots and sees every phase of the
 // barriers it waits on.
-constexpr int kPairLoadStages = 4;
-constexpr int kPairOperandStages = 4;
-constexpr int kPairTeams = 2;
+#ifndef FEATHER_I8_LOAD_STAGES
+#define FEATHER_I8_LOAD_STAGES 4
+#endif
+#ifndef FEATHER_I8_OPERAND_STAGES
+#define FEATHER_I8_OPERAND_STAGES 4
+#endif
+#ifndef FEATHER_I8_TEAMS
+#define FEATHER_I8_TEAMS 2
+#endif
+constexpr int kPairLoadStages = FEATHER_I8_LOAD_STAGES;
+constexpr int kPairOperandStages = FEATHER_I8_OPERAND_STAGES;
+constexpr int kPairTeams = FEATHER_I8_TEAMS;
 static_assert(kPairLoadStages % kPairTeams == 0 && kPairOperandStages % kPairTeams == 0, "ring depths must be multiples of the team count");
 constexpr int kPairHalfN = 128;
 constexpr int kPairN = 2 * kPairHalfN;
