@@ -146,6 +146,24 @@ def bench_int8(device):
     emit(case="cfg3 convrot_int8_linear (quantize + GEMM) 4096x3072x3072", op="convrot_int8_linear", us=round(us, 2),
          tops=round(2 * m * n * k / us / 1e6, 1))
 
+    # a large square GEMM: many waves of tiles, so the steady state of the kernel shows
+    m = n = k = 8192
+    a8 = torch.randint(-127, 128, (m, k), device=device, dtype=torch.int8)
+    w8 = torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8)
+    packed8 = ic.prepack_int8_weight(w8).reshape(-1)
+    a_scale = torch.rand((m,), device=device) + 0.5
+    w_scale = torch.rand((n,), device=device) + 0.5
+    out8 = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in range(2)]
+    tile = ic.select_int8_config(m, n, k, False)
+
+    def big(i):
+        torch.ops.feather_ops.int8_scaled_mm.default(a8, packed8, a_scale, w_scale, None, out8[i % 2], False, *tile)
+
+    us = time_graph(big, 2)
+    tops = 2 * m * n * k / us / 1e6
+    emit(case="int8_scaled_mm 8192x8192x8192 (steady state)", op="int8_scaled_mm", tile=list(tile), us=round(us, 2), tops=round(tops, 1),
+         frac_of_nominal_int8=round(tops / INT8_NOMINAL_TOPS, 3))
+
 
 def bench_conv(device):
     from . import conv2d as fc
