@@ -62,36 +62,51 @@ __device__ __forceinline__ uint16_t to_bits(float v) {
     }
 }
 
+// Two values rounded to the input dtype (nearest even), packed low | high << 16. One instruction on the FMA
+// pipe; the one-value conversions go through the quarter-rate conversion unit.
+template <bool kFp16>
+__device__ __forceinline__ uint32_t to_bits2(float lo, float hi) {
+    if constexpr (kFp16) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&b);
+    }
+}
+
 // Round to the input dtype (nearest even) and come back to fp32.
 template <bool kFp16>
 __device__ __forceinline__ float round_to_input(float v) {
     return to_float<kFp16>(to_bits<kFp16>(v));
 }
 
-__device__ __forceinline__ float butterfly(float a0, float a1, float a2, float a3, int digit) {
-    const float mirrored = digit == 0 ? a3 : digit == 1 ? a2 : digit == 2 ? a1 : a0;
-    return (((a0 + a1) + a2) + a3) - 2.0f * mirrored;
+// One radix-4 butterfly in place: member d becomes ((a0 + a1) + a2) + a3 - 2 * a[3 - d]. The sum is formed once,
+// in the reference's order; 2 * a is exact, so the fused multiply-add rounds exactly like the subtraction.
+__device__ __forceinline__ void butterfly4(float& a0, float& a1, float& a2, float& a3) {
+    const float sum = ((a0 + a1) + a2) + a3;
+    const float r0 = fmaf(-2.0f, a3, sum);
+    const float r1 = fmaf(-2.0f, a2, sum);
+    const float r2 = fmaf(-2.0f, a1, sum);
+    const float r3 = fmaf(-2.0f, a0, sum);
+    a0 = r0;
+    a1 = r1;
+    a2 = r2;
+    a3 = r3;
 }
 
 // Two radix-4 stages over the sixteen values of a lane: first the low index digit (members are four
 // consecutive registers), then the high one (members are registers q, q + 4, q + 8, q + 12).
 __device__ __forceinline__ void two_stages(float (&v)[kPerLane]) {
-    float r[kPerLane];
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-        const int b = i & ~3;
-        r[i] = butterfly(v[b], v[b + 1], v[b + 2], v[b + 3], i & 3);
-    }
+    for (int b = 0; b < kPerLane; b += 4) butterfly4(v[b], v[b + 1], v[b + 2], v[b + 3]);
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-        const int q = i & 3;
-        v[i] = butterfly(r[q], r[q + 4], r[q + 8], r[q + 12], i >> 2);
-    }
+    for (int q = 0; q < 4; ++q) butterfly4(v[q], v[q + 4], v[q + 8], v[q + 12]);
 }
 
 // Produce one group for one half warp: load this lane's sixteen consecutive values, apply the column
 // multiplier or the rotation, round to the input dtype. `packed` receives the lane's sixteen consecutive
-// results as 16-bit patterns, `amax` the running maximum magnitude. `region` is this half warp's transpose
+// results as 16-bit patterns, `amax` the running maximum magnitude before that rounding. `region` is this half warp's transpose
 // buffer. Every lane of the warp must call this together (it synchronizes the warp); `live` says whether
 // the half warp has a group at all.
 template <bool kFp16>
@@ -121,10 +136,8 @@ __device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, cons
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const uint16_t lo = to_bits<kFp16>(v[2 * i]);
-            const uint16_t hi = to_bits<kFp16>(v[2 * i + 1]);
-            amax = fmaxf(amax, fmaxf(fabsf(to_float<kFp16>(lo)), fabsf(to_float<kFp16>(hi))));
-            packed[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+            packed[i] = to_bits2<kFp16>(v[2 * i], v[2 * i + 1]);
         }
         return;
     }
@@ -138,10 +151,11 @@ __device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, cons
     two_stages(v);  // digits 2 and 3
     uint16_t* const halves = reinterpret_cast<uint16_t*>(region);
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-        const uint16_t bits = to_bits<kFp16>(v[i]);
-        amax = fmaxf(amax, fabsf(to_float<kFp16>(bits)));
-        halves[i * 16 + l] = bits;
+    for (int i = 0; i < kPerLane; i += 2) {
+        amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
+        const uint32_t pair = to_bits2<kFp16>(v[i], v[i + 1]);
+        halves[i * 16 + l] = static_cast<uint16_t>(pair & 0xffffu);
+        halves[(i + 1) * 16 + l] = static_cast<uint16_t>(pair >> 16);
     }
     __syncwarp();
     const uint4 lo = *reinterpret_cast<const uint4*>(halves + l * 16);
@@ -157,8 +171,13 @@ __device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, cons
     packed[7] = hi.w;
 }
 
+// clamp(rint(v * inv_divisor), -127, 127) as an integer in the low byte of the result. The clamp bounds are
+// integers, so clamping first and rounding second gives the same value; adding 1.5 * 2^23 rounds to the nearest
+// even integer exactly as rint does (|value| <= 127) and leaves it, in two's complement, in the low mantissa
+// bits. No conversion instruction (quarter rate) is needed.
 __device__ __forceinline__ uint32_t code_of(float v, float inv_divisor) {
-    return static_cast<uint32_t>(static_cast<int>(fminf(fmaxf(rintf(v * inv_divisor), -127.0f), 127.0f))) & 0xffu;
+    const float clamped = fminf(fmaxf(v * inv_divisor, -127.0f), 127.0f);
+    return __float_as_uint(clamped + 12582912.0f);
 }
 
 template <bool kFp16>
@@ -166,14 +185,14 @@ __device__ __forceinline__ void store_codes(int8_t* __restrict__ q_row, int base
     uint32_t out[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint32_t pair = packed[2 * w + j];
-            word |= code_of(to_float<kFp16>(static_cast<uint16_t>(pair & 0xffffu)), inv_divisor) << (16 * j);
-            word |= code_of(to_float<kFp16>(static_cast<uint16_t>(pair >> 16)), inv_divisor) << (16 * j + 8);
-        }
-        out[w] = word;
+        const uint32_t p0 = packed[2 * w];
+        const uint32_t p1 = packed[2 * w + 1];
+        const uint32_t c0 = code_of(to_float<kFp16>(static_cast<uint16_t>(p0 & 0xffffu)), inv_divisor);
+        const uint32_t c1 = code_of(to_float<kFp16>(static_cast<uint16_t>(p0 >> 16)), inv_divisor);
+        const uint32_t c2 = code_of(to_float<kFp16>(static_cast<uint16_t>(p1 & 0xffffu)), inv_divisor);
+        const uint32_t c3 = code_of(to_float<kFp16>(static_cast<uint16_t>(p1 >> 16)), inv_divisor);
+        // low bytes of c0..c3 -> one word
+        out[w] = __byte_perm(__byte_perm(c0, c1, 0x0040u), __byte_perm(c2, c3, 0x0040u), 0x5410u);
     }
     *reinterpret_cast<uint4*>(q_row + base) = make_uint4(out[0], out[1], out[2], out[3]);
 }
@@ -222,6 +241,9 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_kernel(
     __syncthreads();
     float row_max = 0.0f;
     for (int w = 0; w < warps; ++w) row_max = fmaxf(row_max, warp_max[local_row * warps + w]);
+    // the maxima were taken before the rounding to the input dtype: rounding is monotonic, so the maximum of the
+    // rounded magnitudes is the rounded maximum
+    row_max = round_to_input<kFp16>(row_max);
     const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
     if (row_live && warp == 0 && lane == 0) row_scale[row] = rotate ? divisor * 0.0625f : divisor;
     const float inv_divisor = 1.0f / divisor;
