@@ -57,6 +57,7 @@ struct Params {
     int tiles_m;
     int tiles_n;
     uint32_t idesc;
+    int band;               // pair kernel: row tiles per band of the tile walk
 };
 
 template <int BN>
@@ -524,8 +525,10 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             Ring slot;
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-                const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-                const int n0 = (tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN;
+                int tile_m, tile_n;
+                banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+                const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+                const int n0 = tile_n * kPairN + static_cast<int>(cta) * kPairHalfN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
@@ -589,8 +592,10 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         Ring acc;
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-            const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-            const int n0 = (tile / tiles_m) * kPairN;
+            int tile_m, tile_n;
+            banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+            const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+            const int n0 = tile_n * kPairN;
             float* const col_scale = reinterpret_cast<float*>(smem + L::kColumnOff) + acc.idx * 2 * kPairN;
             float* const col_bias = col_scale + kPairN;
             if (has_scale || has_bias) {
@@ -862,6 +867,13 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.stride_kc = args.stride_kc;
     p.stride_out = args.stride_out;
     p.tiles_m = static_cast<int>((args.M + 2 * kBlockM - 1) / (2 * kBlockM));
+    {
+        // as many row tiles per band as keep one band of activations around 32 MB
+        int64_t band = (32ll << 20) / (2 * kBlockM * args.K);
+        if (band < 4) band = 4;
+        if (band > p.tiles_m) band = p.tiles_m;
+        p.band = static_cast<int>(band < 1 ? 1 : band);
+    }
     p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
     p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
     const int num_tiles = p.tiles_m * p.tiles_n;

@@ -65,6 +65,7 @@ struct Params {
     int tiles_n;
     uint32_t idesc;
     int bias_vec;  // bias pointer is 16-byte aligned
+    int band;      // pair kernel: row tiles per band of the tile walk
 };
 
 template <int BN>
@@ -470,8 +471,10 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             Ring slot;
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-                const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-                const int n0 = (tile / tiles_m) * kPairN + static_cast<int>(cta) * kPairHalfN;
+                int tile_m, tile_n;
+                banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+                const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+                const int n0 = tile_n * kPairN + static_cast<int>(cta) * kPairHalfN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
@@ -526,8 +529,10 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         Ring acc;
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-            const int m0 = (tile % tiles_m) * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-            const int n0 = (tile / tiles_m) * kPairN;
+            int tile_m, tile_n;
+            banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+            const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
+            const int n0 = tile_n * kPairN;
             ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
             if (!ok) break;
             tc_fence_after_sync();
@@ -992,6 +997,14 @@ bool launch_instance(const LaunchArgs& args) {
 }
 
 // FEATHER_SCALED_MM_PAIR=0 keeps the one-CTA kernel for every shape (A/B measurements).
+// Row tiles per band of the pair kernels' tile walk: as many as keep one band of activations around 32 MB.
+inline int tile_band(int64_t bytes_per_row_tile, int tiles_m) {
+    int64_t band = (32ll << 20) / (bytes_per_row_tile > 0 ? bytes_per_row_tile : 1);
+    if (band < 4) band = 4;
+    if (band > tiles_m) band = tiles_m;
+    return static_cast<int>(band < 1 ? 1 : band);
+}
+
 inline bool pair_kernel_enabled() {
     static const bool enabled = [] {
         const char* v = getenv("FEATHER_SCALED_MM_PAIR");
@@ -1036,6 +1049,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.N = static_cast<int>(args.N);
     p.K = static_cast<int>(args.K);
     p.tiles_m = static_cast<int>((args.M + 2 * kBlockM - 1) / (2 * kBlockM));
+    p.band = tile_band(2 * kBlockM * args.K * 2, p.tiles_m);
     p.tiles_n = static_cast<int>((args.N + kPairN - 1) / kPairN);
     p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;

@@ -350,6 +350,20 @@ __device__ __forceinline__ uint64_t make_desc_sw128_kmajor(uint32_t smem_addr) {
     return make_smem_desc(smem_addr, 16u, 1024u, kSwizzle128B);
 }
 
+// Tile walk of the persistent pair kernels: row tiles fastest inside a band of `band` row tiles, all column tiles
+// of a band before the next band. The activation rows of one band (sized by the host to a few tens of MB) then stay
+// in L2 while the band sweeps the weight; with row tiles fastest over the whole matrix, a tall activation matrix
+// would be re-read from HBM once per column tile.
+__device__ __forceinline__ void banded_tile(int tile, int tiles_m, int tiles_n, int band, int& tile_m, int& tile_n) {
+    const int per_band = band * tiles_n;
+    const int b = tile / per_band;
+    const int r = tile - b * per_band;
+    const int left = tiles_m - b * band;
+    const int rows_here = left < band ? left : band;
+    tile_n = r / rows_here;
+    tile_m = b * band + (r - tile_n * rows_here);
+}
+
 // Position of the 16-byte chunk `chunk` (0..7) of row `row` inside a 128B-swizzled tile: same mapping as
 // a TMA load with CU_TENSOR_MAP_SWIZZLE_128B produces (tile base 1024-byte aligned).
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
