@@ -59,6 +59,21 @@ def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
     return max(1, min(4, _RESIDENT_SKINNY_CTAS // tiles, k_blocks // 8))
 
 
+_TICKETS: dict = {}
+
+
+def _ticket_counters(device: torch.device, n: int) -> torch.Tensor:
+    """Zeroed ticket counters for the split-K launches of the current stream of `device`. Every launch leaves them
+    at zero, so one buffer per (device, stream) serves all calls; launches of one stream cannot overlap."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    need = -(-n // 64)
+    buf = _TICKETS.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(max(need, 1024), device=device, dtype=torch.int32)
+        _TICKETS[key] = buf
+    return buf
+
+
 def _launch(a, b_prepacked, scale, bias, out, tile) -> None:
     torch.ops.feather_ops.scaled_mm.default(a, b_prepacked, scale, bias, out, *tile[:5], bool(tile[5]))
 
@@ -70,10 +85,12 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
     n = b_prepacked.shape[1]
     if 0 < m <= _SKINNY_MAX_M:
         splits = select_scaled_mm_splits(m, n, k)
-        floats = splits * m * n if splits > 1 else 1
-        partials = torch.empty(floats, device=a.device, dtype=torch.float32)
-        counters = torch.zeros(-(-n // 64), device=a.device, dtype=torch.int32)
-        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, counters, splits)
+        if splits == 1:
+            # a narrow tile with at most one row tile is the skinny kernel without split: no scratch, no extra launch
+            _launch(a, b_prepacked, scale, bias, out, _TILE_N64)
+            return
+        partials = torch.empty(splits * m * n, device=a.device, dtype=torch.float32)
+        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, n), splits)
         return
     _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(m, n, k))
 
