@@ -18,9 +18,10 @@ _TILE_N128 = (2, 2, 2, 4, 4, 0)
 _TILE_N64 = (1, 2, 4, 1, 2, 1)
 
 _SM_COUNT = 148
-# Time of one 128 x BN tile relative to the 256-wide one, per k step: the narrow tiles pay the same
-# activation traffic and pipeline overhead for fewer columns.
-_TILE_COST = {256: 1.0, 128: 0.56, 64: 0.34}
+_PAIR_COUNT = _SM_COUNT // 2
+# Measured time of one wave of tiles per 64-deep k block, in microseconds (M > 128, N = 12288, K = 3072 sweeps):
+# 256-wide tiles run as 256 x 256 tiles on CTA pairs, the narrower ones as 128-row tiles on single CTAs.
+_WAVE_COST_US = {256: 0.42, 128: 0.475, 64: 0.37}
 _TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
 
 
@@ -28,22 +29,26 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
     """Tile tuple for one shape (same signature as the reference's `select_scaled_mm_config`,
     `feather_ops/scaled_mm.py:35-90`; the dtypes do not matter).
 
-    The kernel is persistent with one CTA per SM, so the cost of a width is
-    `waves(width) * cost(width)` with `waves = ceil(tiles / SMs)`: a wide output keeps the 256-wide UMMA
-    tile, a shape with few tiles trades it for a narrower one to fill more SMs.
+    The kernels are persistent, so the cost of a width is `waves * cost of a wave`: 256-wide tiles go to CTA
+    pairs (256 x 256 tiles, 74 pairs) as soon as there is more than one 128-row tile, the narrower widths to
+    one CTA per 128-row tile (148 CTAs). A shape with few tiles trades the wide tile for a narrower one to fill
+    more SMs.
     """
     del K, a_dtype, b_dtype, out_dtype
-    tiles_m = -(-M // 128)
     best = None
     for width in (256, 128, 64):
-        tiles = tiles_m * -(-N // width)
-        cost = -(-tiles // _SM_COUNT) * _TILE_COST[width]
+        if width == 256 and M > 128:
+            waves = -(-(-(-M // 256) * -(-N // 256)) // _PAIR_COUNT)
+        else:
+            waves = -(-(-(-M // 128) * -(-N // width)) // _SM_COUNT)
+        cost = waves * _WAVE_COST_US[width] * (1.4 if width == 256 and M <= 128 else 1.0)
         if best is None or cost < best[0] - 1e-9:
             best = (cost, width)
     return _TILE_OF_WIDTH[best[1]]
 
 
 _SKINNY_MAX_M = 128      # one row tile: the weight stream is the cost, a 64-wide tile per CTA, two CTAs per SM
+_SKINNY_WIDE_M = 64      # above this the activation re-reads of 64-wide tiles cost more than 128-wide tiles save
 _SPLIT_MAX_M = 32        # below this the fp32 partials are small against the weight and K is split as well
 _RESIDENT_SKINNY_CTAS = 2 * _SM_COUNT
 
@@ -85,6 +90,10 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
     n = b_prepacked.shape[1]
     if 0 < m <= _SKINNY_MAX_M:
         splits = select_scaled_mm_splits(m, n, k)
+        if m > _SKINNY_WIDE_M and -(-n // 128) >= _PAIR_COUNT:
+            # enough 128-wide tiles to occupy half the SMs: every activation byte is fetched half as often
+            _launch(a, b_prepacked, scale, bias, out, _TILE_N128)
+            return
         if splits == 1:
             # a narrow tile with at most one row tile is the skinny kernel without split: no scratch, no extra launch
             _launch(a, b_prepacked, scale, bias, out, _TILE_N64)
