@@ -35,8 +35,9 @@ namespace conv {
 
 constexpr int kBlockM = 128;
 constexpr int kStages = 3;
-constexpr int kTeamWarps = 8;
-constexpr int kTeams = 2;
+constexpr int kGatherWarps = 16;
+constexpr int kTeams = 2;   // one-CTA kernel (four teams over four slots measured half as fast: eight items per thread)
+constexpr int kTeamWarps = kGatherWarps / kTeams;
 constexpr int kEpilogueWarps = 4;
 constexpr int kFirstEpilogueWarp = 2;
 constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
                 }
             }
             for (int g = 0; g < p.groups; ++g, ++it) {
-                if (static_cast<int>(it & 1u) != team) continue;
+                if (static_cast<int>(it % kTeams) != team) continue;
                 const uint32_t s = it % kStages;
                 const uint32_t phase = (it / kStages) & 1u;
                 const uint16_t* const x_group = x_img + static_cast<int64_t>(g) * 16 * hw;
@@ -392,7 +393,10 @@ constexpr int kPairHaloCols = kPairBN + 2;
 constexpr int kPairHaloRows = 3;
 constexpr int kPairPlaneBytes = kPairHaloRows * kPairHaloCols * 16;
 constexpr int kPairActStageBytes = (2 * kPairPlaneBytes + 127) / 128 * 128;
-constexpr int kPairItems = 2;                      // gather items per thread per slot (396 items, 256 threads per team)
+constexpr int kPairTeams = 4;   // gather teams taking 16-channel groups in turn: that many groups' loads are in flight (2 teams: 1.19, 4: 1.24 PFLOP/s)
+constexpr int kPairTeamWarps = kGatherWarps / kPairTeams;
+constexpr int kPairItems = (2 * kPairHaloRows * (kPairBN / 2 + 2) + kPairTeamWarps * 32 - 1) / (kPairTeamWarps * 32);   // gather items per thread per slot
+static_assert(kPairStages % kPairTeams == 0, "ring depth must be a multiple of the team count");
 constexpr int kPairSmemBytes = kPairStages * (kWeightStageBytes + kPairActStageBytes) + (3 * kPairStages + 4) * 8 + 16 + 1024;
 
 template <bool kBf16>
@@ -422,7 +426,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
             mbar_init(&weight_full[s], 1);
             // a gather warp arrives only after its own CTA's weights have landed, so this one barrier tells the
             // MMA thread that both CTAs' operands of the slot are complete
-            mbar_init(&act_full[s], 2 * kTeamWarps);
+            mbar_init(&act_full[s], 2 * kPairTeamWarps);
             mbar_init(&stage_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -573,9 +577,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
         // ------------------------------------------------------------------ activation gather warps (output row h0 + cta)
         // W is even here (the launcher checks): per (plane, halo row) the halo columns 1..128 as 64 aligned pixel
         // pairs, then the edge columns 0 and 129 as single pixels.
-        const int team = (warp - kFirstGatherWarp) / kTeamWarps;
-        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kTeamWarps) * 32;
-        constexpr int kTeamThreads = kTeamWarps * 32;
+        const int team = (warp - kFirstGatherWarp) / kPairTeamWarps;
+        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kPairTeamWarps) * 32;
+        constexpr int kTeamThreads = kPairTeamWarps * 32;
         constexpr int kPerRow = kPairBN / 2 + 2;
         constexpr int kItems = 2 * kPairHaloRows * kPerRow;
         static_assert(kItems <= kPairItems * kTeamThreads, "the halo tile must fit the per-thread item count");
@@ -609,7 +613,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
                 }
             }
             for (int g = 0; g < p.groups; ++g, ++it) {
-                if (static_cast<int>(it & 1u) != team) continue;
+                if (static_cast<int>(it % kPairTeams) != team) continue;
                 const uint32_t s = it % kPairStages;
                 const uint32_t phase = (it / kPairStages) & 1u;
                 const uint16_t* const x_group = x_img + static_cast<int64_t>(g) * 16 * hw;
