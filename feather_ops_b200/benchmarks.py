@@ -1,6 +1,6 @@
 """Per-operator measurements of the BASELINE configurations (everything except the headline step of bench.py).
 
-    python -m feather_ops_b200.benchmarks [scaled_mm] [msweep] [int8] [conv] [--profile]     # default: all groups
+    python -m feather_ops_b200.benchmarks [scaled_mm] [msweep] [grid] [int8] [conv] [--profile]     # default: all groups
 
 `--profile` is for runs under a profiler: every case makes three plain launches (no CUDA graph, no timing), so a
 capture of one kernel stays a handful of launches; the printed times are then null.
@@ -103,6 +103,39 @@ def bench_msweep(device):
     _scaled_mm_case(65536, 12288, 3072, torch.bfloat16, torch.bfloat16, True, device, "cfg5 M-sweep M=65536 (one GPU)")
 
 
+# A spread of linear-layer shapes (rows x output width x contraction) of the kind the library meets in diffusion
+# transformers: text bands of a few rows, 4k-25k image/video rows including ragged ones, narrow and very wide
+# outputs, short and very long contractions. Used to check the tile heuristic against the three tile widths.
+GRID_SHAPES = [
+    (16, 4096, 4096), (32, 3840, 2560), (192, 2560, 2560), (256, 12288, 4096), (512, 5120, 5120), (1024, 1280, 1280),
+    (2048, 1152, 4304), (2304, 10240, 1280), (4096, 4608, 4608), (4112, 4096, 12288), (4128, 11520, 3840), (5251, 21504, 5376),
+    (9232, 3072, 8192), (12032, 5120, 13824), (25343, 21504, 5376), (1, 96768, 2688),
+]
+
+
+def bench_grid(device):
+    from . import scaled_mm as smm
+
+    for m, n, k in GRID_SHAPES:
+        weights = (torch.randn((k, n), device=device) * 8).to(torch.float8_e5m2)
+        packed = smm.prepack_b_for_scaled_mm(weights)
+        del weights
+        a = torch.randn((m, k), device=device).to(torch.bfloat16)
+        out = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+        scale = torch.tensor(0.01, device=device)
+        launches = 3 if 2 * m * n * k > 2e12 else 10
+        times = {}
+        for name, tile in (("n64", smm._TILE_N64), ("n128", smm._TILE_N128), ("n256", smm._TILE_N256)):
+            if name != "n256" and m * n > 64 * 1024 * 1024:
+                continue  # the narrow single-CTA tiles are never candidates for very large outputs
+            times[name] = time_graph(lambda i, tile=tile: smm._launch(a, packed, scale, None, out, tile), 1, rounds=3, launches_per_round=launches)
+        auto = time_graph(lambda i: smm._scaled_mm_auto(a, packed, scale, None, out), 1, rounds=3, launches_per_round=launches)
+        best = min(times.values())
+        emit(case=f"grid {m}x{n}x{k}", op="scaled_mm", M=m, N=n, K=k, auto_us=round(auto, 1), tflops=round(2 * m * n * k / auto / 1e6, 1),
+             tiles_us={key: round(v, 1) for key, v in times.items()}, auto_over_best=round(auto / best, 3))
+        del packed, a, out
+
+
 def bench_int8(device):
     from . import int8_convrot as ic
 
@@ -198,7 +231,7 @@ def main(argv):
     global PROFILE_MODE
     PROFILE_MODE = "--profile" in argv
     device = torch.device("cuda")
-    groups = {"scaled_mm": bench_scaled_mm, "msweep": bench_msweep, "int8": bench_int8, "conv": bench_conv}
+    groups = {"scaled_mm": bench_scaled_mm, "msweep": bench_msweep, "grid": bench_grid, "int8": bench_int8, "conv": bench_conv}
     chosen = [a for a in argv if a in groups] or list(groups)
     for name in chosen:
         groups[name](device)
