@@ -194,8 +194,18 @@ def bench_int8(device):
 
     us = time_graph(big, 2)
     tops = 2 * m * n * k / us / 1e6
+    # the vendor library's int8 GEMM at the same size as a measured denominator (there is no driver-measured int8 peak)
+    library_tops = None
+    if not PROFILE_MODE:
+        try:
+            w_t = w8.t()  # [K, N] column-major view, the layout the library kernel wants
+            lib_us = time_graph(lambda i: torch._int_mm(a8, w_t), 1)
+            library_tops = 2 * m * n * k / lib_us / 1e6
+        except Exception:  # noqa: BLE001 - the private torch entry point may be missing or refuse the layout
+            library_tops = None
     emit(case="int8_scaled_mm 8192x8192x8192 (steady state)", op="int8_scaled_mm", tile=list(tile), us=round(us, 2), tops=round(tops, 1),
-         frac_of_nominal_int8=round(tops / INT8_NOMINAL_TOPS, 3))
+         frac_of_nominal_int8=round(tops / INT8_NOMINAL_TOPS, 3), library_int8_gemm_tops=None if library_tops is None else round(library_tops, 1),
+         frac_of_library_int8_gemm=None if library_tops is None else round(tops / library_tops, 3))
 
 
 def bench_conv(device):
