@@ -21,6 +21,8 @@
 //     one of two fp32 TMEM accumulators (k order: groups ascending, taps 0..8 inside, as the reference).
 //   * four epilogue warps: TMEM lane = output channel, columns = consecutive pixels of one output row;
 //     add the bias in fp32, round once, 64-byte contiguous NCHW stores.
+// With more than 128 output channels and the two-row tile, CTA pairs take over (second kernel in this file): two
+// SMs share the pixels of a 256-channel tile.
 #include "feather_host.h"
 #include "feather_tiles_gen.h"
 #include "sm100_ptx.cuh"

@@ -20,6 +20,9 @@
 //   * four epilogue warps: int32 -> float, both scales, bias, one rounding, 16-byte stores.
 // A ragged M is handled by the TMA zero fill and a row predicate on the stores, so there is no second
 // launch for the M tail.
+//
+// 256-wide tiles run on CTA pairs instead (second half of this file): 256 x 256 tiles, the raw micro-tiles
+// fetched by TMA and re-laid shared -> shared, about twice as fast per SM as the structure above.
 #include "feather_host.h"
 #include "feather_tiles_gen.h"
 #include "sm100_ptx.cuh"
@@ -927,8 +930,10 @@ extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const f
     const i8mm::LaunchArgs args{a, b, a_scale, b_scale, bias, c, M, N_out, K_contract, b_stride_kc, b_stride_out,
                                 transposed_b, output_dtype != 0, stream};
     if (block_n >= 256) {
-        // a pair tile is 256 rows tall: worth it as soon as there is more than one 128-row tile
-        if (M > i8mm::kBlockM && i8mm::pair_eligible(args)) return i8mm::launch_pair(args);
+        // The pair kernel also serves a single row tile: its second CTA then multiplies zero rows, but the weight
+        // re-layout is shared by two SMs and streams through TMA, which the single-CTA kernel's is not (a 256-wide
+        // single-CTA tile costs four times as much per k block).
+        if (i8mm::pair_eligible(args)) return i8mm::launch_pair(args);
         return i8mm::launch_for_block_n<256>(args);
     }
     if (block_n >= 128) return i8mm::launch_for_block_n<128>(args);

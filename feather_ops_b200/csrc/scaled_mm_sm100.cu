@@ -13,7 +13,7 @@
 //   * warp 0 is the TMA producer: per 64-wide k block it brings a 128 x 64 activation tile (128-byte
 //     swizzle, zero fill past M and K) and the raw fp8 cells (boxes of 4 slabs x up to 128 cells, 2 KB
 //     contiguous per box row) into a ring of load slots;
-//   * eight upcast warps turn the raw cells into a K-major, 128-byte swizzled fp16 operand tile
+//   * sixteen upcast warps turn the raw cells into a K-major, 128-byte swizzled fp16 operand tile
 //     (e5m2 -> fp16 is a byte placement, e4m3 -> fp16 one cvt per pair; both exact for every code)
 //     in a second, shorter ring, fence it for the async proxy and hand it to the MMA warp;
 //   * one thread of warp 1 issues tcgen05.mma kind::f16 (M=128, N=BN, K=16) into one of two TMEM
@@ -21,6 +21,11 @@
 //   * four epilogue warps read the finished accumulator (thread = output row), apply the scale, round,
 //     add the bias in the output dtype, round again and store 64 contiguous bytes per thread per
 //     32-column step, while the MMA warp already fills the other accumulator.
+//
+// That is the general kernel. Three relatives follow it in this file: the CTA-pair kernel (256 x 256 tiles over
+// tcgen05 cta_group::2, used for M > 128 with the 256-wide tile: the headline path), the skinny kernel for M <= 128
+// (64-wide tiles, two CTAs per SM, optional deterministic split-K) and the entry point that keeps the split-K
+// scratch in the library's own device memory.
 //
 // The UMMA wants both operands in one 16-bit format (a bf16 x fp16 instruction descriptor is rejected as an
 // illegal instruction), so the weights are decoded to the activation's format: fp16 by byte placement,

@@ -23,10 +23,9 @@ _TILE_N64 = (2, 2, 2, 2, 2)
 _SM_COUNT = 148
 _PAIR_COUNT = _SM_COUNT // 2
 # Measured time of one wave of tiles per 128-deep k block, in microseconds (N = K = 3072 sweeps over M): 256-wide
-# tiles run as 256 x 256 tiles on CTA pairs when there is more than one 128-row tile, everything else as 128-row
-# tiles on single CTAs, whose weight re-layout is much slower.
+# tiles run as 256 x 256 tiles on CTA pairs (also for a single row tile), the others as 128-row tiles on single
+# CTAs, whose weight re-layout is much slower.
 _WAVE_COST_US = {256: 0.47, 128: 0.98, 64: 0.78}
-_SINGLE_CTA_256_COST_US = 1.9
 _TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
 
 
@@ -38,11 +37,10 @@ def select_int8_config(M: int, N: int, K: int, transposed_b: bool):
     out = K if transposed_b else N
     best = None
     for width in (256, 128, 64):
-        if width == 256 and M > 128:
+        if width == 256:
             cost = -(-(-(-M // 256) * -(-out // 256)) // _PAIR_COUNT) * _WAVE_COST_US[256]
         else:
-            per_wave = _SINGLE_CTA_256_COST_US if width == 256 else _WAVE_COST_US[width]
-            cost = -(-(-(-M // 128) * -(-out // width)) // _SM_COUNT) * per_wave
+            cost = -(-(-(-M // 128) * -(-out // width)) // _SM_COUNT) * _WAVE_COST_US[width]
         if best is None or cost < best[0] - 1e-9:
             best = (cost, width)
     return _TILE_OF_WIDTH[best[1]]
