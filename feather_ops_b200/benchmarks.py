@@ -94,6 +94,16 @@ def bench_scaled_mm(device):
     _scaled_mm_case(256, 4096, 4096, torch.float16, torch.float16, True, device, "cfg1 fp16 256x4096x4096")
     for n, k in ((12288, 3072), (3072, 12288), (9216, 3072)):
         _scaled_mm_case(4096, n, k, torch.bfloat16, torch.bfloat16, True, device, f"cfg2 bf16 4096x{n}x{k}")
+    if not PROFILE_MODE:
+        # the vendor library's plain bf16 GEMM at the metric shape (both operands already bf16, no fp8 decode, no
+        # scale): the measured tensor-core denominator for exactly this shape, with the same rotation of buffers
+        m, n, k = 4096, 12288, 3072
+        sets = 4
+        acts = [torch.randn((m, k), device=device).to(torch.bfloat16) for _ in range(sets)]
+        weights = [torch.randn((k, n), device=device).to(torch.bfloat16) for _ in range(sets)]
+        outs = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in range(sets)]
+        us = time_graph(lambda i: torch.matmul(acts[i % sets], weights[i % sets], out=outs[i % sets]), sets)
+        emit(case="library bf16 GEMM 4096x12288x3072 (torch.matmul)", op="library_gemm", us=round(us, 2), tflops=round(2 * m * n * k / us / 1e6, 1))
 
 
 def bench_msweep(device):
