@@ -13,6 +13,7 @@ step (the weights stay resident: they are model state, not step input).
 """
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -37,13 +38,15 @@ CPU_SAMPLE_ROWS = 1024
 
 
 def measured_peak():
+    """`(burst, sustained, source)`: the driver-measured cuBLAS bf16 rates of this pool (best single launch, and a
+    seconds-long loop under the power cap), or the stated fallback."""
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             peaks = json.load(f)
-        return float(peaks["bf16_tflops"]), "measured (cuBLAS bf16 burst, MEASURED_PEAKS.json)"
+        return float(peaks["bf16_tflops"]), float(peaks.get("bf16_tflops_sustained", 0.0)) or None, "measured (cuBLAS bf16 burst, MEASURED_PEAKS.json)"
     except (OSError, KeyError, ValueError):
-        return 1590.0, "fallback (earlier pool measurement, cuBLAS bf16 burst)"
+        return 1590.0, 1400.0, "fallback (earlier pool measurement, cuBLAS bf16 burst)"
 
 
 def make_inputs(seed):
@@ -59,9 +62,11 @@ def make_inputs(seed):
 
 
 class ClockSampler:
-    """nvidia-smi clock and throttle-reason samples of one GPU while the timed region runs."""
+    """nvidia-smi clock and throttle-reason samples of one GPU, every 20 ms, each with its wall-clock time. It is
+    started before the warm-up, so it is already running when the timed region begins; `stop(window)` keeps the
+    samples whose time stamps fall inside the window (the timed region)."""
 
-    QUERY = "index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    QUERY = "timestamp,index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
@@ -70,12 +75,12 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, window=None):
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -88,14 +93,21 @@ class ClockSampler:
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.file.read().splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) != 7 or not parts[0].isdigit() or int(parts[0]) != self.gpu_index:
+            if len(parts) != 8 or not parts[1].isdigit() or int(parts[1]) != self.gpu_index:
                 continue
+            if window is not None:
+                try:
+                    stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                except ValueError:
+                    continue
+                if not (window[0] <= stamp <= window[1]):
+                    continue
             try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
+                clocks.append(float(parts[2]))
+                max_clock = float(parts[3])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[3:]):
+            for name, flag in zip(names, parts[4:]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         self.file.close()
@@ -221,21 +233,27 @@ def run_library(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(3, args.warmup)):
-        step(i)
-    barrier()
+    # the clock sampler is started before the warm-up so that it is already producing samples when the timed region
+    # begins; only the samples time-stamped inside the timed region are kept
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    region_begin = datetime.datetime.now()
     start.record()
     for i in range(args.steps):
         step(i)
     stop.record()
     barrier()
+    region_end = datetime.datetime.now()
     elapsed_ms = start.elapsed_time(stop)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop((region_begin, region_end)) if rank == 0 else None
+    if clocks is not None and clocks["samples"] >= 2:
+        clocks["note"] = "nvidia-smi samples every 20 ms, time-stamped inside the timed region"
     if distributed:
         t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -244,7 +262,7 @@ def run_library(args):
     value = FLOP_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
 
     # a short sampled run may not have covered the timed region: sample clocks again under a sustained loop
-    if rank == 0 and (clocks is None or clocks["samples"] < 3):
+    if rank == 0 and (clocks is None or clocks["samples"] < 2):
         sampler = ClockSampler(local_rank)
         sampler.start()
         t_end = time.perf_counter() + 0.8
@@ -300,7 +318,7 @@ def run_library(args):
     e2e_value = FLOP_PER_STEP * world * e2e_steps / e2e_s / 1e12
 
     if rank == 0:
-        peak, peak_source = measured_peak()
+        peak, peak_sustained, peak_source = measured_peak()
         achieved = FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12
         line = {
             "metric": METRIC,
@@ -332,6 +350,10 @@ def run_library(args):
                 "peak_source": peak_source,
                 "kernel": "feather::smm::scaled_mm_pair_kernel<e5m2, bf16 operands, bf16 out> (CTA pairs, 256x256 tiles)",
                 "frac_of_nominal_2250": achieved / 2250.0,
+                # the timed region is K back-to-back launches: a long one sits between the two measured references
+                "timed_region_ms": elapsed_ms,
+                "peak_sustained": peak_sustained,
+                "frac_of_sustained": None if not peak_sustained else achieved / peak_sustained,
                 "algorithmic_bytes": ALGORITHMIC_BYTES,
             },
             "clocks": clocks,
@@ -356,7 +378,7 @@ def run_library(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=("library", "reference"), default="library")
     args = parser.parse_args()
