@@ -1106,6 +1106,164 @@ bool launch_pair(const LaunchArgs& args) {
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Vector version for one or two rows (a decode token, a modulation vector): no tensor core. A 128-row UMMA tile would spend
+// its floor of 96 clocks per 16-deep slice on one or two live rows, and the tensor-memory/barrier set-up costs as
+// much as streaming the weight. Here a warp owns 32 consecutive output columns for one eighth of the contraction:
+// per 16-deep slab it loads 32 prepack cells (512 contiguous bytes), decodes them exactly to fp32 and multiplies with
+// the activations, which sit in shared memory as fp32 and are read as broadcasts. The eight warps of a CTA cover
+// the contraction; their partial sums are added in warp order through shared memory (deterministic), then scale,
+// round, bias, round as everywhere else. Products of a 16-bit activation and an fp8 weight are exact in fp32, so
+// only the order of the fp32 additions differs from the tensor-core kernels.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kGemvMaxRows = 2;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvUnroll = 8;   // cells in flight per lane
+constexpr int kGemvSmemLimit = 64 * 1024;
+
+template <bool kE5M2>
+__device__ __forceinline__ void fp8x4_to_f32x4(uint32_t p, float (&f)[4]) {
+    uint32_t lo, hi;
+    fp8x4_to_f16x4<kE5M2>(p, lo, hi);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    f[0] = a.x;
+    f[1] = a.y;
+    f[2] = b.x;
+    f[3] = b.y;
+}
+
+template <int kRows, bool kE5M2, bool kActBf16, bool kOutBf16>
+__global__ void __launch_bounds__(32 * kGemvWarps) scaled_mm_gemv_kernel(const uint16_t* __restrict__ a, const uint4* __restrict__ cells,
+                                                                          const float* __restrict__ scale_ptr, const uint16_t* __restrict__ bias,
+                                                                          uint16_t* __restrict__ c, int N, int K, int slabs) {
+    extern __shared__ __align__(16) float gemv_smem[];
+    float* const act = gemv_smem;                                  // [kRows][slabs * 16], zero past K
+    float* const partial = gemv_smem + kRows * slabs * 16;         // [kGemvWarps][kRows][32]
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const int k_pad = slabs * 16;
+    for (int i = static_cast<int>(threadIdx.x); i < kRows * k_pad; i += 32 * kGemvWarps) {
+        const int r = i / k_pad;
+        const int k = i - r * k_pad;
+        float v = 0.0f;
+        if (k < K) {
+            const uint16_t bits = __ldg(a + static_cast<int64_t>(r) * K + k);
+            v = kActBf16 ? __uint_as_float(static_cast<uint32_t>(bits) << 16) : __half2float(__ushort_as_half(bits));
+        }
+        act[i] = v;
+    }
+    __syncthreads();
+
+    const int n = static_cast<int>(blockIdx.x) * 32 + lane;
+    const bool live = n < N;
+    const int per_warp = (slabs + kGemvWarps - 1) / kGemvWarps;
+    const int s_begin = warp * per_warp;
+    const int s_end = s_begin + per_warp < slabs ? s_begin + per_warp : slabs;
+    float acc[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) acc[r] = 0.0f;
+    const uint4* const column = cells + (live ? n : 0);
+    for (int s0 = s_begin; s0 < s_end; s0 += kGemvUnroll) {
+        uint4 cell[kGemvUnroll];
+#pragma unroll
+        for (int u = 0; u < kGemvUnroll; ++u) {
+            cell[u] = (live && s0 + u < s_end) ? __ldg(column + static_cast<int64_t>(s0 + u) * N) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kGemvUnroll; ++u) {
+            if (s0 + u >= s_end) break;
+            const uint32_t w[4] = {cell[u].x, cell[u].y, cell[u].z, cell[u].w};
+            float f[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float g[4];
+                fp8x4_to_f32x4<kE5M2>(w[q], g);
+                f[4 * q] = g[0];
+                f[4 * q + 1] = g[1];
+                f[4 * q + 2] = g[2];
+                f[4 * q + 3] = g[3];
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                const float4* const av = reinterpret_cast<const float4*>(act + r * k_pad + (s0 + u) * 16);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 x = av[q];
+                    acc[r] = fmaf(f[4 * q], x.x, acc[r]);
+                    acc[r] = fmaf(f[4 * q + 1], x.y, acc[r]);
+                    acc[r] = fmaf(f[4 * q + 2], x.z, acc[r]);
+                    acc[r] = fmaf(f[4 * q + 3], x.w, acc[r]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) partial[(warp * kRows + r) * 32 + lane] = acc[r];
+    __syncthreads();
+    if (warp == 0 && live) {
+        const float scale = scale_ptr != nullptr ? __ldg(scale_ptr) : 1.0f;
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kGemvWarps; ++w) sum += partial[(w * kRows + r) * 32 + lane];
+            uint32_t o = pack_out<kOutBf16>(sum * scale, 0.0f);
+            if (bias != nullptr) {
+                const float2 x = unpack_out<kOutBf16>(o);
+                const float2 b = unpack_out<kOutBf16>(static_cast<uint32_t>(__ldg(bias + n)));
+                o = pack_out<kOutBf16>(x.x + b.x, 0.0f);
+            }
+            c[static_cast<int64_t>(r) * N + n] = static_cast<uint16_t>(o & 0xffffu);
+        }
+    }
+}
+
+template <int kRows, bool kE5M2, bool kActBf16, bool kOutBf16>
+bool launch_gemv_rows(const LaunchArgs& args, int slabs, size_t smem_bytes) {
+    auto* kernel = &scaled_mm_gemv_kernel<kRows, kE5M2, kActBf16, kOutBf16>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+    const unsigned grid = static_cast<unsigned>((args.N + 31) / 32);
+    kernel<<<grid, 32 * kGemvWarps, smem_bytes, args.stream>>>(args.a, reinterpret_cast<const uint4*>(args.b), args.scale, args.bias, args.c,
+                                                                 static_cast<int>(args.N), static_cast<int>(args.K), slabs);
+    return cudaGetLastError() == cudaSuccess;
+}
+
+// True when the vector kernel takes the problem. Measured at 12288 x 3072: one row 11 us against 22 for the skinny
+// tensor-core kernel, four rows 25 against 22 (16 fused multiply-adds per weight and row), so it is used for one
+// or two rows, when there are at least two CTAs of 32 columns per SM and the activations leave room for several
+// CTAs per SM (3072 x 12288 with its 96 CTAs, or a 16384-deep contraction, are slower than the skinny kernel).
+inline bool gemv_eligible(const LaunchArgs& args, int* slabs, size_t* smem_bytes) {
+    if (args.M > 2) return false;
+    *slabs = static_cast<int>((args.K + 15) / 16);
+    *smem_bytes = (static_cast<size_t>(args.M) * *slabs * 16 + static_cast<size_t>(kGemvWarps) * args.M * 32) * sizeof(float);
+    return *smem_bytes <= 64u * 1024u && args.N >= 64ll * device_info().sm_count && (reinterpret_cast<uintptr_t>(args.b) & 15u) == 0;
+}
+
+bool launch_gemv(const LaunchArgs& args, int slabs, size_t smem_bytes) {
+#define FEATHER_SMM_GEMV_CASE(E5, AB, OUT)                                                                   \
+    if (args.e5m2 == E5 && args.a_bf16 == AB && args.out_bf16 == OUT) {                                       \
+        return args.M == 1 ? launch_gemv_rows<1, E5, AB, OUT>(args, slabs, smem_bytes)                        \
+                           : launch_gemv_rows<2, E5, AB, OUT>(args, slabs, smem_bytes);                       \
+    }
+    FEATHER_SMM_GEMV_CASE(true, false, true)
+    FEATHER_SMM_GEMV_CASE(true, false, false)
+    FEATHER_SMM_GEMV_CASE(false, false, true)
+    FEATHER_SMM_GEMV_CASE(false, false, false)
+    FEATHER_SMM_GEMV_CASE(true, true, true)
+    FEATHER_SMM_GEMV_CASE(true, true, false)
+    FEATHER_SMM_GEMV_CASE(false, true, true)
+    FEATHER_SMM_GEMV_CASE(false, true, false)
+#undef FEATHER_SMM_GEMV_CASE
+    return false;
+}
+
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
 bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
     auto* kernel = &scaled_mm_skinny_kernel<kE5M2, kOperandBf16, kOutBf16>;
@@ -1170,6 +1328,11 @@ bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials,
 
 bool launch_skinny(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
     const bool operand_bf16 = args.a_bf16;
+    {
+        int slabs = 0;
+        size_t smem_bytes = 0;
+        if (gemv_eligible(args, &slabs, &smem_bytes)) return launch_gemv(args, slabs, smem_bytes);
+    }
 #define FEATHER_SMM_SKINNY_CASE(E5, OB, OUT)                               \
     if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
         return launch_skinny_instance<E5, OB, OUT>(args, splits, partials, counters); \
