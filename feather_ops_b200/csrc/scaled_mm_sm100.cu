@@ -1264,6 +1264,186 @@ bool launch_gemv(const LaunchArgs& args, int slabs, size_t smem_bytes) {
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Warp-MMA version for 3..16 rows and wide outputs. tcgen05 has no shape below 64 rows, and its set-up (tensor
+// memory, barriers, a CTA per SM) costs more than streaming the weight once, so a problem this skinny is served by
+// mma.sync m16n8k16: it is HBM bound, not tensor bound. Same decomposition as the vector kernel (a warp = 32 columns
+// x one eighth of the contraction, partial sums added in warp order), and no shuffles or shared-memory staging:
+// the contraction index inside a 16-deep slab is permuted the same way for both operands (fragment slots 2j, 2j+1,
+// 2j+8, 2j+9 take k = 4j .. 4j+3), so a lane's B fragment is four consecutive bytes of one prepack cell (a warp
+// reads eight cells = 128 contiguous bytes per 8-column block) and its A fragment four consecutive activations
+// of a row (8 bytes), both straight from global memory.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kWmmaMaxRows = 16;   // two 16-row tiles per warp were measured too: 33-36 us at 12288 x 3072, slower than the tensor-memory kernel (23)
+constexpr int kWmmaWarps = 8;
+constexpr int kWmmaUnroll = 4;   // slabs in flight per warp with one 16-row tile (16 weight loads per lane), half as many with two
+
+template <bool kBf16>
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (kBf16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+
+template <int kRowTiles, bool kE5M2, bool kActBf16, bool kOutBf16>
+__global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scaled_mm_wmma_kernel(const uint16_t* __restrict__ a, const uint8_t* __restrict__ cells,
+                                                                          const float* __restrict__ scale_ptr, const uint16_t* __restrict__ bias,
+                                                                          uint16_t* __restrict__ c, int M, int N, int K, int slabs) {
+    __shared__ float partial[kWmmaWarps][kRowTiles][4][4][32];   // [warp][16-row tile][8-column block][fragment register][lane]
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const int g = lane >> 2;   // fragment row (and row + 8), B column inside an 8-column block
+    const int j = lane & 3;    // which four k of the slab
+    const int n0 = static_cast<int>(blockIdx.x) * 32;
+    const int per_warp = (slabs + kWmmaWarps - 1) / kWmmaWarps;
+    const int s_begin = warp * per_warp;
+    const int s_end = s_begin + per_warp < slabs ? s_begin + per_warp : slabs;
+
+    float acc[kRowTiles][4][4];
+#pragma unroll
+    for (int t = 0; t < kRowTiles; ++t) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[t][b][r] = 0.0f;
+        }
+    }
+    // rows of this lane's A fragments: 16 t + g and 16 t + g + 8
+    bool row_live[kRowTiles][2];
+    const uint16_t* a_row[kRowTiles][2];
+#pragma unroll
+    for (int t = 0; t < kRowTiles; ++t) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = 16 * t + g + 8 * h;
+            row_live[t][h] = row < M;
+            a_row[t][h] = a + static_cast<int64_t>(row_live[t][h] ? row : 0) * K + 4 * j;
+        }
+    }
+    // byte address of this lane's four weights in slab 0, block 0; a block is 8 cells = 128 bytes further
+    const uint8_t* const w_lane = cells + (static_cast<int64_t>(n0 + g) * 16 + 4 * j);
+    const int64_t slab_stride = static_cast<int64_t>(N) * 16;
+    bool col_live[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) col_live[b] = n0 + 8 * b + g < N;
+
+    constexpr int kUnroll = kWmmaUnroll / kRowTiles;
+    for (int s0 = s_begin; s0 < s_end; s0 += kUnroll) {
+        uint32_t w[kUnroll][4];
+        uint2 x[kUnroll][kRowTiles][2];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const bool slab_live = s0 + u < s_end;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                w[u][b] = (slab_live && col_live[b]) ? __ldg(reinterpret_cast<const uint32_t*>(w_lane + (s0 + u) * slab_stride + b * 128)) : 0u;
+            }
+#pragma unroll
+            for (int t = 0; t < kRowTiles; ++t) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    x[u][t][h] = (slab_live && row_live[t][h]) ? __ldg(reinterpret_cast<const uint2*>(a_row[t][h] + (s0 + u) * 16)) : make_uint2(0u, 0u);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                uint32_t b0, b1;
+                fp8x4_to_f16x4<kE5M2>(w[u][b], b0, b1);
+                if constexpr (kActBf16) {
+                    b0 = f16x2_to_bf16x2(b0);
+                    b1 = f16x2_to_bf16x2(b1);
+                }
+#pragma unroll
+                for (int t = 0; t < kRowTiles; ++t) {
+                    // A fragment: {row g: k 4j, 4j+1}, {row g+8: same}, {row g: k 4j+2, 4j+3}, {row g+8: same}
+                    const uint32_t af[4] = {x[u][t][0].x, x[u][t][1].x, x[u][t][0].y, x[u][t][1].y};
+                    mma_m16n8k16<kActBf16>(acc[t][b], af, b0, b1);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < kRowTiles; ++t) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) partial[warp][t][b][r][lane] = acc[t][b][r];
+        }
+    }
+    __syncthreads();
+    // warp b adds the eight partial sums of block b in warp order and writes the block: accumulator registers 0, 1 are
+    // row g, columns 2j and 2j+1 of the block; registers 2, 3 the same columns of row g + 8
+    if (warp < 4) {
+        const int b = warp;
+        const float scale = scale_ptr != nullptr ? __ldg(scale_ptr) : 1.0f;
+        const int col = n0 + 8 * b + 2 * j;
+        if (col < N) {  // N is a multiple of 16 and col is even: col + 1 exists as well
+            uint32_t bias_pair = 0u;
+            if (bias != nullptr) bias_pair = static_cast<uint32_t>(__ldg(bias + col)) | (static_cast<uint32_t>(__ldg(bias + col + 1)) << 16);
+#pragma unroll
+            for (int t = 0; t < kRowTiles; ++t) {
+                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int w2 = 0; w2 < kWmmaWarps; ++w2) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) sum[r] += partial[w2][t][b][r][lane];
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = 16 * t + g + 8 * h;
+                    if (row >= M) continue;
+                    uint32_t o = pack_out<kOutBf16>(sum[2 * h] * scale, sum[2 * h + 1] * scale);
+                    if (bias != nullptr) {
+                        const float2 xo = unpack_out<kOutBf16>(o);
+                        const float2 bb = unpack_out<kOutBf16>(bias_pair);
+                        o = pack_out<kOutBf16>(xo.x + bb.x, xo.y + bb.y);
+                    }
+                    *reinterpret_cast<uint32_t*>(c + static_cast<int64_t>(row) * N + col) = o;
+                }
+            }
+        }
+    }
+}
+
+// True when the warp-MMA kernel takes the problem: 3..16 rows and at least two CTAs of 32 columns per SM; the
+// activation rows are read with 8-byte loads and the output with 4-byte stores.
+inline bool wmma_eligible(const LaunchArgs& args) {
+    return args.M <= kWmmaMaxRows && args.N >= 64ll * device_info().sm_count && args.K % 16 == 0 &&
+           (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0;
+}
+
+bool launch_wmma(const LaunchArgs& args) {
+    const int slabs = static_cast<int>(args.K / 16);
+    const unsigned grid = static_cast<unsigned>((args.N + 31) / 32);
+#define FEATHER_SMM_WMMA_CASE(E5, AB, OUT)                                                                              \
+    if (args.e5m2 == E5 && args.a_bf16 == AB && args.out_bf16 == OUT) {                                                  \
+        scaled_mm_wmma_kernel<1, E5, AB, OUT><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(                                \
+            args.a, args.b, args.scale, args.bias, args.c, static_cast<int>(args.M), static_cast<int>(args.N),           \
+            static_cast<int>(args.K), slabs);                                                                            \
+        return cudaGetLastError() == cudaSuccess;                                                                        \
+    }
+    FEATHER_SMM_WMMA_CASE(true, false, true)
+    FEATHER_SMM_WMMA_CASE(true, false, false)
+    FEATHER_SMM_WMMA_CASE(false, false, true)
+    FEATHER_SMM_WMMA_CASE(false, false, false)
+    FEATHER_SMM_WMMA_CASE(true, true, true)
+    FEATHER_SMM_WMMA_CASE(true, true, false)
+    FEATHER_SMM_WMMA_CASE(false, true, true)
+    FEATHER_SMM_WMMA_CASE(false, true, false)
+#undef FEATHER_SMM_WMMA_CASE
+    return false;
+}
+
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
 bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
     auto* kernel = &scaled_mm_skinny_kernel<kE5M2, kOperandBf16, kOutBf16>;
@@ -1333,6 +1513,7 @@ bool launch_skinny(const LaunchArgs& args, int splits, float* partials, uint32_t
         size_t smem_bytes = 0;
         if (gemv_eligible(args, &slabs, &smem_bytes)) return launch_gemv(args, slabs, smem_bytes);
     }
+    if (wmma_eligible(args) && std::getenv("FEATHER_SKINNY_WMMA_OFF") == nullptr) return launch_wmma(args);
 #define FEATHER_SMM_SKINNY_CASE(E5, OB, OUT)                               \
     if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
         return launch_skinny_instance<E5, OB, OUT>(args, splits, partials, counters); \

@@ -210,6 +210,25 @@ def test_one_and_two_rows_take_the_vector_kernel(cuda_device, shape, a_dtype, b_
     _compare(no_bias, osm.scaled_mm_f32(a, packed, None, None, out_dtype, b_prepacked=True), out_dtype, 1e-3)
 
 
+@pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16),
+                                                       (torch.float16, torch.float8_e5m2, torch.bfloat16)])
+@pytest.mark.parametrize("shape", [(3, 9472, 512), (8, 12288, 3072), (9, 9488, 1040), (16, 20000, 256), (16, 9600, 16)])
+def test_three_to_sixteen_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype, out_dtype):
+    # wide outputs with 3..16 rows run on mma.sync with the contraction index permuted inside each 16-deep slab:
+    # same oracle and tolerance, ragged last column block (9488 = 296.5 x 32), same bits on every call
+    m, n, k = shape
+    a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype, seed=n + k)
+    ref = osm.scaled_mm_f32(a, packed, scale, bias, out_dtype, b_prepacked=True)
+    dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+    first = _cabi.scaled_mm(*dev, out_dtype, (1, 2, 4, 1, 2, 1))
+    _cabi.assert_clean(STATUS)
+    _compare(first, ref, out_dtype, 1e-3)
+    again, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 3)
+    assert torch.equal(first, again)
+    no_scale = _cabi.scaled_mm(dev[0], dev[1], None, None, out_dtype, (1, 2, 4, 1, 2, 1))
+    _compare(no_scale, osm.scaled_mm_f32(a, packed, None, None, out_dtype, b_prepacked=True), out_dtype, 1e-3)
+
+
 def test_skinny_shapes_through_the_python_api(cuda_device):
     import feather_ops_b200 as fo
     from feather_ops_b200.scaled_mm import select_scaled_mm_splits
