@@ -49,7 +49,6 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;            // one 128-byte swizzle span of 16-bit elements
 constexpr int kSlabsPerBlock = kBlockK / 16;
 constexpr int kLoadStages = 4;
-constexpr int kOperandStages = 2;
 constexpr int kUpcastWarps = 16;
 constexpr int kEpilogueWarps = 4;
 constexpr int kFirstEpilogueWarp = 2;
@@ -80,6 +79,11 @@ struct Smem {
     static constexpr int kBoxes = BN / kBoxCells;                   // weight boxes per slot
     static constexpr int kBoxBytes = kSlabsPerBlock * kBoxCells * 16;
     static constexpr int kOperandBytes = BN * 128;
+    // the upcast warps work as kTeams teams taking k blocks in turn (their barrier hand-offs overlap); ring depths are
+    // multiples of the team count, and the widest tile only has room for two operand slots
+    static constexpr int kTeams = 2;
+    static constexpr int kOperandStages = BN == 256 ? 2 : 4;
+    static_assert(kLoadStages % kTeams == 0 && kOperandStages % kTeams == 0, "ring depths must be multiples of the team count");
     static constexpr int kAOff = 0;
     static constexpr int kOperandOff = kAOff + kLoadStages * kATileBytes;
     static constexpr int kRawOff = kOperandOff + kOperandStages * kOperandBytes;
@@ -154,8 +158,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* const load_full = bars;
     uint64_t* const load_empty = load_full + kLoadStages;
     uint64_t* const operand_full = load_empty + kLoadStages;
-    uint64_t* const operand_empty = operand_full + kOperandStages;
-    uint64_t* const tmem_full = operand_empty + kOperandStages;
+    uint64_t* const operand_empty = operand_full + L::kOperandStages;
+    uint64_t* const tmem_full = operand_empty + L::kOperandStages;
     uint64_t* const tmem_empty = tmem_full + 2;
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
@@ -170,8 +174,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(&load_full[s], 1);
             mbar_init(&load_empty[s], 1);
         }
-        for (int s = 0; s < kOperandStages; ++s) {
-            mbar_init(&operand_full[s], kUpcastWarps);
+        for (int s = 0; s < L::kOperandStages; ++s) {
+            mbar_init(&operand_full[s], kUpcastWarps / L::kTeams);
             mbar_init(&operand_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -241,7 +245,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     umma_commit(&load_empty[slot.idx]);
                     umma_commit(&operand_empty[operand.idx]);
                     slot.advance(kLoadStages);
-                    operand.advance(kOperandStages);
+                    operand.advance(L::kOperandStages);
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full[acc.idx]);
@@ -315,52 +319,58 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------------------------------------------ upcast warps
         // Work unit = one 16-byte cell (row n, slab j): unit u = t + i * threads, row = u % BN, slab = u / BN.
         const int t = static_cast<int>(threadIdx.x) - kFirstUpcastWarp * 32;
-        constexpr int kUpcastThreads = kUpcastWarps * 32;
+        constexpr int kTeamThreads = kUpcastWarps * 32 / L::kTeams;
         constexpr int kUnits = BN * kSlabsPerBlock;
-        constexpr int kUnitsPerThread = (kUnits + kUpcastThreads - 1) / kUpcastThreads;
+        constexpr int kUnitsPerThread = (kUnits + kTeamThreads - 1) / kTeamThreads;
+        const int team = t / kTeamThreads;
+        const int tt = t % kTeamThreads;
         Ring slot, operand;
         bool ok = true;
+        uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
         for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
-                     guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
-                if (!ok) break;
-                const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
-                uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
-                uint4 cells[kUnitsPerThread];
+                if (turn == static_cast<uint32_t>(team)) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
+                         guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
+                    if (!ok) break;
+                    const uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                    uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
+                    uint4 cells[kUnitsPerThread];
 #pragma unroll
-                for (int i = 0; i < kUnitsPerThread; ++i) {
-                    const int u = t + i * kUpcastThreads;
-                    if (kUnits % kUpcastThreads == 0 || u < kUnits) {
-                        const int row = u % BN;
-                        const int slab = u / BN;
-                        cells[i] = *reinterpret_cast<const uint4*>(raw + (row / L::kBoxCells) * L::kBoxBytes + (slab * L::kBoxCells + row % L::kBoxCells) * 16);
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < kUnitsPerThread; ++i) {
-                    const int u = t + i * kUpcastThreads;
-                    if (kUnits % kUpcastThreads != 0 && u >= kUnits) continue;
-                    const int row = u % BN;
-                    const int slab = u / BN;
-                    const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
-                    uint32_t h[8];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
-                        if constexpr (kOperandBf16) {
-                            h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
-                            h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        const int u = tt + i * kTeamThreads;
+                        if (kUnits % kTeamThreads == 0 || u < kUnits) {
+                            const int row = u % BN;
+                            const int slab = u / BN;
+                            cells[i] = *reinterpret_cast<const uint4*>(raw + (row / L::kBoxCells) * L::kBoxBytes + (slab * L::kBoxCells + row % L::kBoxCells) * 16);
                         }
                     }
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+#pragma unroll
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        const int u = tt + i * kTeamThreads;
+                        if (kUnits % kTeamThreads != 0 && u >= kUnits) continue;
+                        const int row = u % BN;
+                        const int slab = u / BN;
+                        const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
+                        uint32_t h[8];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            fp8x4_to_f16x4<kE5M2>(w[q], h[2 * q], h[2 * q + 1]);
+                            if constexpr (kOperandBf16) {
+                                h[2 * q] = f16x2_to_bf16x2(h[2 * q]);
+                                h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&operand_full[operand.idx]);
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&operand_full[operand.idx]);
+                turn = turn + 1 == L::kTeams ? 0 : turn + 1;
                 slot.advance(kLoadStages);
-                operand.advance(kOperandStages);
+                operand.advance(L::kOperandStages);
             }
         }
     }
