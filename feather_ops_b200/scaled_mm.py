@@ -21,7 +21,7 @@ _SM_COUNT = 148
 _PAIR_COUNT = _SM_COUNT // 2
 # Measured time of one wave of tiles per 64-deep k block, in microseconds (M > 128, N = 12288, K = 3072 sweeps):
 # 256-wide tiles run as 256 x 256 tiles on CTA pairs, the narrower ones as 128-row tiles on single CTAs.
-_WAVE_COST_US = {256: 0.42, 128: 0.475, 64: 0.37}
+_WAVE_COST_US = {256: 0.40, 128: 0.42, 64: 0.35}
 _TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
 
 
