@@ -22,6 +22,8 @@ _PAIR_COUNT = _SM_COUNT // 2
 # Measured time of one wave of tiles per 64-deep k block, in microseconds (M > 128, N = 12288, K = 3072 sweeps):
 # 256-wide tiles run as 256 x 256 tiles on CTA pairs, the narrower ones as 128-row tiles on single CTAs.
 _WAVE_COST_US = {256: 0.40, 128: 0.42, 64: 0.35}
+# launch, pipeline fill and the last tile's epilogue: what a launch costs before its k blocks count
+_FIXED_COST_US = {256: 8.0, 128: 6.0, 64: 6.0}
 _TILE_OF_WIDTH = {256: _TILE_N256, 128: _TILE_N128, 64: _TILE_N64}
 
 
@@ -29,19 +31,22 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
     """Tile tuple for one shape (same signature as the reference's `select_scaled_mm_config`,
     `feather_ops/scaled_mm.py:35-90`; the dtypes do not matter).
 
-    The kernels are persistent, so the cost of a width is `waves * cost of a wave`: 256-wide tiles go to CTA
+    The kernels are persistent, so the cost of a width is `fixed + waves * k blocks * cost of a wave per k block`: 256-wide tiles go to CTA
     pairs (256 x 256 tiles, 74 pairs) as soon as there is more than one 128-row tile, the narrower widths to
     one CTA per 128-row tile (148 CTAs). A shape with few tiles trades the wide tile for a narrower one to fill
     more SMs.
     """
-    del K, a_dtype, b_dtype, out_dtype
+    del a_dtype, b_dtype, out_dtype
+    k_blocks = -(-K // 64)
     best = None
     for width in (256, 128, 64):
         if width == 256 and M > 128:
             waves = -(-(-(-M // 256) * -(-N // 256)) // _PAIR_COUNT)
+            fixed = _FIXED_COST_US[256]
         else:
             waves = -(-(-(-M // 128) * -(-N // width)) // _SM_COUNT)
-        cost = waves * _WAVE_COST_US[width] * (1.4 if width == 256 and M <= 128 else 1.0)
+            fixed = _FIXED_COST_US[width if width != 256 else 128]
+        cost = fixed + waves * k_blocks * _WAVE_COST_US[width] * (1.4 if width == 256 and M <= 128 else 1.0)
         if best is None or cost < best[0] - 1e-9:
             best = (cost, width)
     return _TILE_OF_WIDTH[best[1]]
