@@ -109,16 +109,21 @@ __device__ __forceinline__ void two_stages(float (&v)[kPerLane]) {
 // results as 16-bit patterns, `amax` the running maximum magnitude before that rounding. `region` is this half warp's transpose
 // buffer. Every lane of the warp must call this together (it synchronizes the warp); `live` says whether
 // the half warp has a group at all.
+// This lane's sixteen consecutive input values as two 16-byte loads (zeros when the half warp has no group).
+__device__ __forceinline__ void load_raw(const uint16_t* __restrict__ x_row, int base, bool live, uint4 (&raw)[2]) {
+    raw[0] = make_uint4(0u, 0u, 0u, 0u);
+    raw[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (live) {
+        raw[0] = __ldg(reinterpret_cast<const uint4*>(x_row + base));
+        raw[1] = __ldg(reinterpret_cast<const uint4*>(x_row + base + 8));
+    }
+}
+
 template <bool kFp16>
-__device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, const float* __restrict__ col_scale, int base, int l, bool live,
-                                        bool rotate, float* region, uint32_t (&packed)[8], float& amax) {
+__device__ __forceinline__ void produce_from(const uint4 (&raw)[2], const float* __restrict__ col_scale, int base, int l, bool live, bool rotate,
+                                             float* region, uint32_t (&packed)[8], float& amax) {
     float v[kPerLane];
     {
-        uint4 raw[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-        if (live) {
-            raw[0] = __ldg(reinterpret_cast<const uint4*>(x_row + base));
-            raw[1] = __ldg(reinterpret_cast<const uint4*>(x_row + base + 8));
-        }
         const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) v[i] = to_float<kFp16>(static_cast<uint16_t>(w[i / 2] >> (16 * (i % 2))));
@@ -169,6 +174,14 @@ __device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, cons
     packed[5] = hi.y;
     packed[6] = hi.z;
     packed[7] = hi.w;
+}
+
+template <bool kFp16>
+__device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, const float* __restrict__ col_scale, int base, int l, bool live,
+                                        bool rotate, float* region, uint32_t (&packed)[8], float& amax) {
+    uint4 raw[2];
+    load_raw(x_row, base, live, raw);
+    produce_from<kFp16>(raw, col_scale, base, l, live, rotate, region, packed, amax);
 }
 
 // clamp(rint(v * inv_divisor), -127, 127) as an integer in the low byte of the result. The clamp bounds are
@@ -264,6 +277,54 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_kernel(
     }
 }
 
+// Rows up to 2 * 256 * blockDim.y wide (one round: every half warp has at most one group per row). A fixed number of
+// resident CTAs walk the rows, and a CTA asks for its next row's values before it works on the current one: with
+// one row per CTA lifetime the pass ran at the pace of one HBM latency per wave of CTAs, not at the HBM rate.
+template <bool kFp16>
+__global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_stream_kernel(const uint16_t* __restrict__ x, const float* __restrict__ col_scale,
+                                                                                      int8_t* __restrict__ q, float* __restrict__ row_scale, int64_t M, int K,
+                                                                                      int groups, bool rotate) {
+    extern __shared__ __align__(16) float regions[];  // 2 * kRegionWords per warp of the CTA
+    __shared__ float warp_max[2][kMaxWarpsPerCta];     // by row parity: one barrier per row is enough
+    const int lane = static_cast<int>(threadIdx.x);
+    const int half = lane >> 4;
+    const int l = lane & 15;
+    const int warp = static_cast<int>(threadIdx.y);
+    const int warps = static_cast<int>(blockDim.y);
+    const int local_row = static_cast<int>(threadIdx.z);
+    const int cta_warp = local_row * warps + warp;
+    float* const region = regions + (cta_warp * 2 + half) * kRegionWords;
+    const int g = 2 * warp + half;
+    const bool group_live = g < groups;
+    const int base = g * kGroup + l * kPerLane;
+    const int64_t row_step = static_cast<int64_t>(gridDim.x) * blockDim.z;
+
+    int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.z + local_row;
+    uint4 raw[2];
+    load_raw(x + (row < M ? row : 0) * K, base, group_live && row < M, raw);
+    uint32_t parity = 0;
+    for (int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.z; first < M; first += row_step, row += row_step, parity ^= 1u) {
+        const bool row_live = row < M;
+        uint4 next[2];
+        load_raw(x + (row + row_step < M ? row + row_step : 0) * K, base, group_live && row + row_step < M, next);
+        uint32_t packed[8];
+        float amax = 0.0f;
+        produce_from<kFp16>(raw, col_scale, base, l, row_live && group_live, rotate, region, packed, amax);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        if (lane == 0) warp_max[parity][cta_warp] = amax;
+        __syncthreads();
+        float row_max = 0.0f;
+        for (int w = 0; w < warps; ++w) row_max = fmaxf(row_max, warp_max[parity][local_row * warps + w]);
+        row_max = round_to_input<kFp16>(row_max);  // maxima were taken before the rounding, which is monotonic
+        const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
+        if (row_live && warp == 0 && lane == 0) row_scale[row] = rotate ? divisor * 0.0625f : divisor;
+        if (row_live && group_live) store_codes<kFp16>(q + row * K, base, packed, 1.0f / divisor);
+        raw[0] = next[0];
+        raw[1] = next[1];
+    }
+}
+
 }  // namespace quant
 }  // namespace feather
 
@@ -288,6 +349,27 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
     const uint16_t* const xp = static_cast<const uint16_t*>(x);
     const int k = static_cast<int>(K);
     const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kRegionWords * sizeof(float);
+    if (groups <= 2 * warps) {
+        // one round per row: resident CTAs walk the rows and prefetch the next one
+        int per_sm = 0;
+        const int threads = 32 * warps * rows_per_cta;
+        const cudaError_t occ = input_fp16 != 0
+                                    ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, convrot_quantize_stream_kernel<true>, threads, smem)
+                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, convrot_quantize_stream_kernel<false>, threads, smem);
+        if (occ != cudaSuccess || per_sm < 1) {
+            (void)cudaGetLastError();
+            per_sm = 1;
+        }
+        const int64_t resident = static_cast<int64_t>(per_sm) * feather::device_info().sm_count;
+        const int64_t wanted = (M + rows_per_cta - 1) / rows_per_cta;
+        const dim3 stream_grid(static_cast<unsigned>(wanted < resident ? wanted : resident));
+        if (input_fp16 != 0) {
+            convrot_quantize_stream_kernel<true><<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
+        } else {
+            convrot_quantize_stream_kernel<false><<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
+        }
+        return cudaGetLastError() == cudaSuccess;
+    }
     if (input_fp16 != 0) {
         if (cache) {
             convrot_quantize_kernel<true, true><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
