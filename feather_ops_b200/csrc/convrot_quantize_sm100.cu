@@ -351,14 +351,23 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
     const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kRegionWords * sizeof(float);
     if (groups <= 2 * warps) {
         // one round per row: resident CTAs walk the rows and prefetch the next one
-        int per_sm = 0;
+        // CTAs resident per SM for this block shape (the shared-memory size follows from it), asked once per device
+        static int resident_per_sm[2][64][kMaxWarpsPerCta + 1] = {};
         const int threads = 32 * warps * rows_per_cta;
-        const cudaError_t occ = input_fp16 != 0
-                                    ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, convrot_quantize_stream_kernel<true>, threads, smem)
-                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, convrot_quantize_stream_kernel<false>, threads, smem);
-        if (occ != cudaSuccess || per_sm < 1) {
-            (void)cudaGetLastError();
-            per_sm = 1;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64) dev = 0;
+        int& per_sm = resident_per_sm[input_fp16 != 0 ? 1 : 0][dev][threads / 32];
+        if (per_sm == 0) {
+            int value = 0;
+            const cudaError_t occ = input_fp16 != 0
+                                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<true>, threads, smem)
+                                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<false>, threads, smem);
+            if (occ != cudaSuccess || value < 1) {
+                (void)cudaGetLastError();
+                value = 1;
+            }
+            per_sm = value;
         }
         const int64_t resident = static_cast<int64_t>(per_sm) * feather::device_info().sm_count;
         const int64_t wanted = (M + rows_per_cta - 1) / rows_per_cta;
