@@ -27,6 +27,8 @@
 #include "feather_tiles_gen.h"
 #include "sm100_ptx.cuh"
 
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -886,6 +888,151 @@ bool launch_pair_instance(const LaunchArgs& args) {
     return cudaGetLastError() == cudaSuccess;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Warp-MMA version of the forward direction for at most 16 rows (a text band, a decode step): tcgen05 has no shape
+// below 64 rows and a CTA-pair launch costs more than streaming a few MB of weight, so this case runs on mma.sync
+// m16n8k32 (int8, exact int32 accumulation). A warp owns 32 output columns for one eighth of the contraction; the
+// eight warps' int32 partial sums are added through shared memory (integer addition: any order gives the same bits).
+// The contraction index inside a 32-deep block is permuted identically for both operands (fragment bytes 4t..4t+3
+// and 16+4t..16+4t+3 take k = 8t..8t+7), so a lane's A fragment is eight consecutive activation bytes and its B
+// fragment two dwords of the prepack (contraction steps 2t and 2t+1 of one output column): no shuffles, no staging.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kWmmaMaxRows = 16;
+constexpr int kWmmaWarps = 8;
+constexpr int kWmmaUnroll = 2;   // 32-deep blocks in flight per warp (16 weight dwords per lane)
+
+__device__ __forceinline__ void mma_m16n8k32_s8(int32_t (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool kOutBf16>
+__global__ void __launch_bounds__(32 * kWmmaWarps, 3) int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
+                                                                           const float* __restrict__ a_scale, const float* __restrict__ b_scale,
+                                                                           const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N,
+                                                                           int K, int64_t stride_kc, int64_t stride_out) {
+    __shared__ int32_t partial[kWmmaWarps][4][4][32];   // [warp][8-column block][fragment register][lane]
+    const int warp = static_cast<int>(threadIdx.x) / 32;
+    const int lane = static_cast<int>(threadIdx.x) % 32;
+    const int g = lane >> 2;   // fragment row (and row + 8), B column inside an 8-column block
+    const int t = lane & 3;    // which eight k of the 32-deep block
+    const int n0 = static_cast<int>(blockIdx.x) * 32;
+    const int blocks = K / 32 + (K % 32 != 0 ? 1 : 0);   // K is a multiple of 16: the last block may be half
+    const int per_warp = (blocks + kWmmaWarps - 1) / kWmmaWarps;
+    const int s_begin = warp * per_warp;
+    const int s_end = s_begin + per_warp < blocks ? s_begin + per_warp : blocks;
+    const int k4_total = K / 4;
+
+    int32_t acc[4][4];
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[blk][r] = 0;
+    }
+    const bool row_lo = g < M;
+    const bool row_hi = g + 8 < M;
+    const int8_t* const a_lo = a + static_cast<int64_t>(row_lo ? g : 0) * K + 8 * t;
+    const int8_t* const a_hi = a + static_cast<int64_t>(row_hi ? g + 8 : 0) * K + 8 * t;
+    // dword (contraction step k4, output column n) of the prepack: micro-tile (k4, n / 4), dword n % 4
+    const uint8_t* w_col[4];
+    bool col_live[4];
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+        const int n = n0 + 8 * blk + g;
+        col_live[blk] = n < N;
+        w_col[blk] = b + (static_cast<int64_t>(col_live[blk] ? n / 4 : 0) * stride_out) * 16 + (n % 4) * 4;
+    }
+
+    for (int s0 = s_begin; s0 < s_end; s0 += kWmmaUnroll) {
+        uint32_t w[kWmmaUnroll][4][2];
+        uint2 x_lo[kWmmaUnroll], x_hi[kWmmaUnroll];
+#pragma unroll
+        for (int u = 0; u < kWmmaUnroll; ++u) {
+            const int k4 = (s0 + u) * 8 + 2 * t;            // this lane's two contraction steps of the block
+            const bool live = s0 + u < s_end && k4 < k4_total;   // k4 + 1 exists as well: K / 4 is a multiple of 4
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) {
+                const uint8_t* const src = w_col[blk] + static_cast<int64_t>(k4) * stride_kc * 16;
+                w[u][blk][0] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src)) : 0u;
+                w[u][blk][1] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src + stride_kc * 16)) : 0u;
+            }
+            x_lo[u] = (live && row_lo) ? __ldg(reinterpret_cast<const uint2*>(a_lo + (s0 + u) * 32)) : make_uint2(0u, 0u);
+            x_hi[u] = (live && row_hi) ? __ldg(reinterpret_cast<const uint2*>(a_hi + (s0 + u) * 32)) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kWmmaUnroll; ++u) {
+            // A fragment: {row g: k 8t..8t+3}, {row g+8: same}, {row g: k 8t+4..8t+7}, {row g+8: same}
+            const uint32_t af[4] = {x_lo[u].x, x_hi[u].x, x_lo[u].y, x_hi[u].y};
+#pragma unroll
+            for (int blk = 0; blk < 4; ++blk) mma_m16n8k32_s8(acc[blk], af, w[u][blk][0], w[u][blk][1]);
+        }
+    }
+#pragma unroll
+    for (int blk = 0; blk < 4; ++blk) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) partial[warp][blk][r][lane] = acc[blk][r];
+    }
+    __syncthreads();
+    // warp blk adds the eight partial sums of block blk and writes it: accumulator registers 0, 1 are row g, columns
+    // 2t and 2t+1 of the block; registers 2, 3 the same columns of row g + 8
+    if (warp < 4) {
+        const int blk = warp;
+        const int col = n0 + 8 * blk + 2 * t;
+        int32_t sum[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int w2 = 0; w2 < kWmmaWarps; ++w2) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) sum[r] += partial[w2][blk][r][lane];
+        }
+        if (col < N) {  // N is a multiple of 4 and col is even: col + 1 exists as well
+            const float s0 = b_scale != nullptr ? __ldg(b_scale + col) : 1.0f;
+            const float s1 = b_scale != nullptr ? __ldg(b_scale + col + 1) : 1.0f;
+            const float z0 = bias != nullptr ? out_bits_to_float<kOutBf16>(__ldg(bias + col)) : 0.0f;
+            const float z1 = bias != nullptr ? out_bits_to_float<kOutBf16>(__ldg(bias + col + 1)) : 0.0f;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = g + 8 * h;
+                if (row >= M) continue;
+                const float rs = __ldg(a_scale + row);
+                float v0 = static_cast<float>(sum[2 * h]) * rs;
+                float v1 = static_cast<float>(sum[2 * h + 1]) * rs;
+                if (b_scale != nullptr) {
+                    v0 *= s0;
+                    v1 *= s1;
+                }
+                if (bias != nullptr) {
+                    v0 += z0;
+                    v1 += z1;
+                }
+                *reinterpret_cast<uint32_t*>(c + static_cast<int64_t>(row) * N + col) = pack_out<kOutBf16>(v0, v1);
+            }
+        }
+    }
+}
+
+// True when the warp-MMA kernel takes the problem: forward direction, at most 16 rows, operands aligned for its 8-byte
+// activation loads, dword weight loads and 4-byte stores.
+bool wmma_eligible(const LaunchArgs& args) {
+    return !args.transposed_b && args.M <= kWmmaMaxRows && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
+           (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 3u) == 0 &&
+           (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0 && std::getenv("FEATHER_INT8_WMMA_OFF") == nullptr;
+}
+
+bool launch_wmma(const LaunchArgs& args) {
+    const unsigned grid = static_cast<unsigned>((args.N_out + 31) / 32);
+    if (args.out_bf16) {
+        int8_mm_wmma_kernel<true><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,
+                                                                              static_cast<int>(args.M), static_cast<int>(args.N_out),
+                                                                              static_cast<int>(args.K), args.stride_kc, args.stride_out);
+    } else {
+        int8_mm_wmma_kernel<false><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,
+                                                                               static_cast<int>(args.M), static_cast<int>(args.N_out),
+                                                                               static_cast<int>(args.K), args.stride_kc, args.stride_out);
+    }
+    return cudaGetLastError() == cudaSuccess;
+}
+
 // The pair kernel fetches the weight by TMA: the micro-tile axis that its boxes run along must be contiguous,
 // the other stride must fit a tensor map, and the base must be 16-byte aligned.
 bool pair_eligible(const LaunchArgs& args) {
@@ -929,6 +1076,7 @@ extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const f
     if (M == 0) return true;
     const i8mm::LaunchArgs args{a, b, a_scale, b_scale, bias, c, M, N_out, K_contract, b_stride_kc, b_stride_out,
                                 transposed_b, output_dtype != 0, stream};
+    if (i8mm::wmma_eligible(args)) return i8mm::launch_wmma(args);
     if (block_n >= 256) {
         // The pair kernel also serves a single row tile: its second CTA then multiplies zero rows, but the weight
         // re-layout is shared by two SMs and streams through TMA, which the single-CTA kernel's is not (a 256-wide

@@ -187,3 +187,26 @@ def test_benchmark_shape_by_properties(cuda_device):
     assert _max_rel(y[rows.to(cuda_device)], ref) < 0.02
     full = x.float()[rows] @ w.float().T
     assert ((y[rows.to(cuda_device)].float().cpu() - full).norm() / full.norm()).item() < 2e-2
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 256, 64), (5, 3072, 3072), (16, 1040, 528), (9, 260, 16), (16, 12288, 1024)])
+def test_at_most_sixteen_rows_take_the_warp_mma_kernel(cuda_device, shape, out_dtype):
+    # forward direction with at most 16 rows runs on mma.sync with a permuted contraction index: exact int32 sums, the
+    # same oracle and tolerance, ragged last column block (260, 1040), a contraction with a half block (528 = 16.5 x 32)
+    m, n, k = shape
+    w, a, a_scale, w_scale, bias, n_out = _gemm_case(m, n, k, False, out_dtype, seed=m + n + k)
+    ref = o8.int8_scaled_mm(a, w, a_scale, w_scale, bias, out_dtype, False)
+    dev = lambda t: None if t is None else t.to(cuda_device)  # noqa: E731
+    packed = dev(o8.prepack_int8_weight(w))
+    out = _cabi.int8_scaled_mm(dev(a), packed, dev(a_scale), dev(w_scale), dev(bias), out_dtype, False, n_out)
+    _cabi.assert_clean(STATUS)
+    assert _max_rel(out, ref) < 0.02
+    plain = _cabi.int8_scaled_mm(dev(a), packed, dev(a_scale), None, None, out_dtype, False, n_out)
+    assert _max_rel(plain, o8.int8_scaled_mm(a, w, a_scale, None, None, out_dtype, False)) < 0.02
+    # unit scales: the result is the exact integer product wherever it is representable in the output dtype
+    ones = torch.ones(m, device=cuda_device)
+    exact = _cabi.int8_scaled_mm(dev(a), packed, ones, None, None, torch.float16, False, n_out).double().cpu()
+    want = a.double() @ w.double().T
+    small = want.abs() <= 2048
+    assert torch.equal(exact[small], want[small])
