@@ -41,8 +41,9 @@ constexpr int kPerLane = 16;          // consecutive values of one lane
 constexpr int kMaxWarpsPerRow = 16;   // a warp handles two groups per round
 constexpr int kCachedRounds = 4;
 constexpr int kMaxWarpsPerCta = 16;
-constexpr int kPadded = 17;           // row pitch (in words) of the transpose buffer
-constexpr int kRegionWords = 16 * kPadded;
+constexpr int kPadded = 20;           // row pitch (in words) of the transpose buffer: rows start on 16 bytes, and both a
+                                      // quarter warp's 16-byte row stores and a half warp's column loads are conflict free
+constexpr int kRegionWords = 16 * kPadded + 16;  // 16 mod 32: the two half warps of a warp read different banks
 
 template <bool kFp16>
 __device__ __forceinline__ float to_float(uint16_t bits) {
@@ -148,7 +149,9 @@ __device__ __forceinline__ void produce_from(const uint4 (&raw)[2], const float*
     }
     two_stages(v);  // digits 0 and 1: element index = l * 16 + i
 #pragma unroll
-    for (int i = 0; i < kPerLane; ++i) region[l * kPadded + i] = v[i];
+    for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<float4*>(region + l * kPadded + 4 * c) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    }
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) v[i] = region[i * kPadded + l];  // now element index = i * 16 + l
@@ -188,8 +191,12 @@ __device__ __forceinline__ void produce(const uint16_t* __restrict__ x_row, cons
 // integers, so clamping first and rounding second gives the same value; adding 1.5 * 2^23 rounds to the nearest
 // even integer exactly as rint does (|value| <= 127) and leaves it, in two's complement, in the low mantissa
 // bits. No conversion instruction (quarter rate) is needed.
+// Only the lower clamp is written out. |v| never exceeds the row maximum, so the product is at most
+// 127 * (1 + 2^-22) in magnitude, which rounds to 127 without any clamp; the other possible product is NaN
+// (a NaN input, or an infinite row maximum times the zero that 1 / inf gives), and fmaxf(NaN, -127) = -127 is
+// what the two-sided clamp returned for it too.
 __device__ __forceinline__ uint32_t code_of(float v, float inv_divisor) {
-    const float clamped = fminf(fmaxf(v * inv_divisor, -127.0f), 127.0f);
+    const float clamped = fmaxf(v * inv_divisor, -127.0f);
     return __float_as_uint(clamped + 12582912.0f);
 }
 
@@ -280,48 +287,96 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_kernel(
 // Rows up to 2 * 256 * blockDim.y wide (one round: every half warp has at most one group per row). A fixed number of
 // resident CTAs walk the rows, and a CTA asks for its next row's values before it works on the current one: with
 // one row per CTA lifetime the pass ran at the pace of one HBM latency per wave of CTAs, not at the HBM rate.
-template <bool kFp16>
+//
+// The pass is bound by instruction issue, so the per-row bookkeeping is kept short: the warp maximum is one
+// `redux` on the bit pattern (magnitudes are non-negative, so they order like unsigned integers), the row maximum
+// one shared-memory atomic per warp and one load per thread, and the two row buffers swap roles by unrolling.
+constexpr int kMaxRowsPerCta = 8;
+
+template <bool kFp16, bool kRotate>
+struct StreamRow {
+    const float* col_scale;
+    float* region;
+    uint32_t* row_max_bits;  // [3][kMaxRowsPerCta]: slot t % 3 collects row t, slot (t + 1) % 3 is cleared meanwhile
+    float* row_scale;
+    int l;
+    int base;
+    int local_row;
+    bool group_live;
+    bool writes_scale;
+
+    // One row: `raw` holds its values, `q_row` / `row` say where the codes and the scale go.
+    __device__ __forceinline__ void run(const uint4 (&raw)[2], bool row_live, int8_t* q_row, int64_t row, uint32_t turn) const {
+        uint32_t packed[8];
+        float amax = 0.0f;
+        produce_from<kFp16>(raw, col_scale, base, l, row_live && group_live, kRotate, region, packed, amax);
+        const uint32_t warp_bits = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+        uint32_t* const slot = row_max_bits + turn * kMaxRowsPerCta + local_row;
+        if (threadIdx.x == 0) atomicMax(slot, warp_bits);
+        if (threadIdx.x == 1 && threadIdx.y == 0) row_max_bits[(turn == 2u ? 0u : turn + 1u) * kMaxRowsPerCta + local_row] = 0u;
+        __syncthreads();
+        // maxima were taken before the rounding to the input dtype, which is monotonic
+        const float row_max = round_to_input<kFp16>(__uint_as_float(*slot));
+        const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
+        if (row_live && writes_scale) row_scale[row] = kRotate ? divisor * 0.0625f : divisor;
+        if (row_live && group_live) store_codes<kFp16>(q_row, base, packed, 1.0f / divisor);
+    }
+};
+
+template <bool kFp16, bool kRotate>
 __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_stream_kernel(const uint16_t* __restrict__ x, const float* __restrict__ col_scale,
                                                                                       int8_t* __restrict__ q, float* __restrict__ row_scale, int64_t M, int K,
-                                                                                      int groups, bool rotate) {
+                                                                                      int groups) {
     extern __shared__ __align__(16) float regions[];  // 2 * kRegionWords per warp of the CTA
-    __shared__ float warp_max[2][kMaxWarpsPerCta];     // by row parity: one barrier per row is enough
+    __shared__ uint32_t row_max_bits[3 * kMaxRowsPerCta];
     const int lane = static_cast<int>(threadIdx.x);
     const int half = lane >> 4;
-    const int l = lane & 15;
     const int warp = static_cast<int>(threadIdx.y);
     const int warps = static_cast<int>(blockDim.y);
     const int local_row = static_cast<int>(threadIdx.z);
-    const int cta_warp = local_row * warps + warp;
-    float* const region = regions + (cta_warp * 2 + half) * kRegionWords;
     const int g = 2 * warp + half;
-    const bool group_live = g < groups;
-    const int base = g * kGroup + l * kPerLane;
-    const int64_t row_step = static_cast<int64_t>(gridDim.x) * blockDim.z;
 
+    StreamRow<kFp16, kRotate> ctx;
+    ctx.col_scale = col_scale;
+    ctx.region = regions + ((local_row * warps + warp) * 2 + half) * kRegionWords;
+    ctx.row_max_bits = row_max_bits;
+    ctx.row_scale = row_scale;
+    ctx.l = lane & 15;
+    ctx.base = g * kGroup + ctx.l * kPerLane;
+    ctx.local_row = local_row;
+    ctx.group_live = g < groups;
+    ctx.writes_scale = warp == 0 && lane == 0;
+
+    const int flat = (local_row * warps + warp) * 32 + lane;
+    if (flat < 3 * kMaxRowsPerCta) row_max_bits[flat] = 0u;
+    __syncthreads();
+
+    const int64_t row_step = static_cast<int64_t>(gridDim.x) * blockDim.z;
+    const int64_t step_elems = row_step * K;
     int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.z + local_row;
-    uint4 raw[2];
-    load_raw(x + (row < M ? row : 0) * K, base, group_live && row < M, raw);
-    uint32_t parity = 0;
-    for (int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.z; first < M; first += row_step, row += row_step, parity ^= 1u) {
-        const bool row_live = row < M;
-        uint4 next[2];
-        load_raw(x + (row + row_step < M ? row + row_step : 0) * K, base, group_live && row + row_step < M, next);
-        uint32_t packed[8];
-        float amax = 0.0f;
-        produce_from<kFp16>(raw, col_scale, base, l, row_live && group_live, rotate, region, packed, amax);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-        if (lane == 0) warp_max[parity][cta_warp] = amax;
-        __syncthreads();
-        float row_max = 0.0f;
-        for (int w = 0; w < warps; ++w) row_max = fmaxf(row_max, warp_max[parity][local_row * warps + w]);
-        row_max = round_to_input<kFp16>(row_max);  // maxima were taken before the rounding, which is monotonic
-        const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
-        if (row_live && warp == 0 && lane == 0) row_scale[row] = rotate ? divisor * 0.0625f : divisor;
-        if (row_live && group_live) store_codes<kFp16>(q + row * K, base, packed, 1.0f / divisor);
-        raw[0] = next[0];
-        raw[1] = next[1];
+    int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.z;   // the CTA's lowest row: the same for all its threads
+    const uint16_t* x_row = x + (row < M ? row : 0) * K;
+    int8_t* q_row = q + (row < M ? row : 0) * K;
+    uint4 raw_a[2];
+    uint4 raw_b[2];
+    load_raw(x_row, ctx.base, ctx.group_live && row < M, raw_a);
+    uint32_t turn = 0;
+    while (first < M) {
+        load_raw(x_row + step_elems, ctx.base, ctx.group_live && row + row_step < M, raw_b);
+        ctx.run(raw_a, row < M, q_row, row, turn);
+        turn = turn == 2u ? 0u : turn + 1u;
+        first += row_step;
+        row += row_step;
+        x_row += step_elems;
+        q_row += step_elems;
+        if (first >= M) break;
+        load_raw(x_row + step_elems, ctx.base, ctx.group_live && row + row_step < M, raw_a);
+        ctx.run(raw_b, row < M, q_row, row, turn);
+        turn = turn == 2u ? 0u : turn + 1u;
+        first += row_step;
+        row += row_step;
+        x_row += step_elems;
+        q_row += step_elems;
     }
 }
 
@@ -358,11 +413,15 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
         cudaGetDevice(&dev);
         if (dev < 0 || dev >= 64) dev = 0;
         int& per_sm = resident_per_sm[input_fp16 != 0 ? 1 : 0][dev][threads / 32];
+        using StreamKernel = void (*)(const uint16_t*, const float*, int8_t*, float*, int64_t, int, int);
+        const StreamKernel kernel = input_fp16 != 0 ? (rotate ? convrot_quantize_stream_kernel<true, true> : convrot_quantize_stream_kernel<true, false>)
+                                                    : (rotate ? convrot_quantize_stream_kernel<false, true> : convrot_quantize_stream_kernel<false, false>);
         if (per_sm == 0) {
             int value = 0;
+            // asked for the rotating variant, the one with more registers
             const cudaError_t occ = input_fp16 != 0
-                                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<true>, threads, smem)
-                                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<false>, threads, smem);
+                                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<true, true>, threads, smem)
+                                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<false, true>, threads, smem);
             if (occ != cudaSuccess || value < 1) {
                 (void)cudaGetLastError();
                 value = 1;
@@ -372,11 +431,7 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
         const int64_t resident = static_cast<int64_t>(per_sm) * feather::device_info().sm_count;
         const int64_t wanted = (M + rows_per_cta - 1) / rows_per_cta;
         const dim3 stream_grid(static_cast<unsigned>(wanted < resident ? wanted : resident));
-        if (input_fp16 != 0) {
-            convrot_quantize_stream_kernel<true><<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
-        } else {
-            convrot_quantize_stream_kernel<false><<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
-        }
+        kernel<<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups);
         return cudaGetLastError() == cudaSuccess;
     }
     if (input_fp16 != 0) {
