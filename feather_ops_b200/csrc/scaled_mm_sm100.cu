@@ -70,6 +70,11 @@ struct Params {
     uint32_t idesc;
     int bias_vec;  // bias pointer is 16-byte aligned
     int band;      // pair kernel: row tiles per band of the tile walk
+    // one-CTA kernel with K split `splits` ways (1 = no split, the other three are then unused)
+    int splits;
+    int kb_per_split;
+    float* partials;      // [splits][M][N] fp32
+    uint32_t* counters;   // [tiles_m * tiles_n] tickets, zero before the launch and zero again after it
 };
 
 template <int BN>
@@ -148,6 +153,45 @@ __device__ __forceinline__ float2 unpack_out(uint32_t v) {
     }
 }
 
+// Thirty-two consecutive accumulator columns of one output row (fp32 bit patterns): scale, round, add the bias,
+// round again, store. Shared by the direct epilogue and the split-K reduction of the one-CTA kernel.
+template <bool kOutBf16>
+__device__ __forceinline__ void finish_columns(const Params& p, const uint32_t (&v)[32], float scale, int row, int col0, uint16_t* c_row) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int col = col0 + g * 8;
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[i] = pack_out<kOutBf16>(__uint_as_float(v[g * 8 + 2 * i]) * scale, __uint_as_float(v[g * 8 + 2 * i + 1]) * scale);
+        }
+        if (p.bias != nullptr && col < p.N) {
+            uint32_t bw[4];
+            if (p.bias_vec) {
+                const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                bw[0] = b4.x;
+                bw[1] = b4.y;
+                bw[2] = b4.z;
+                bw[3] = b4.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    bw[i] = static_cast<uint32_t>(__ldg(p.bias + col + 2 * i)) | (static_cast<uint32_t>(__ldg(p.bias + col + 2 * i + 1)) << 16);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 x = unpack_out<kOutBf16>(o[i]);
+                const float2 b = unpack_out<kOutBf16>(bw[i]);
+                o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
+            }
+        }
+        if (row < p.M && col < p.N) {
+            *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 template <int BN, bool kE5M2, bool kOperandBf16, bool kOutBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -163,6 +207,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* const tmem_empty = tmem_full + 2;
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
+    volatile uint32_t* const last_flag = tmem_slot + 2;  // split K: this CTA drew a tile's last ticket
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
@@ -197,16 +242,23 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+    // work item = (tile, K split); without a split an item is a tile and covers every k block
+    const int splits = p.splits > 1 ? p.splits : 1;
+    const int kb_per_split = splits > 1 ? p.kb_per_split : num_kb;
+    const int num_items = num_tiles * splits;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (elect_one()) {
             Ring slot;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            for (int item = static_cast<int>(blockIdx.x); ok && item < num_items; item += static_cast<int>(gridDim.x)) {
+                const int tile = item / splits;
+                const int kb_begin = (item - tile * splits) * kb_per_split;
+                const int kb_end = kb_begin + kb_per_split < num_kb ? kb_begin + kb_per_split : num_kb;
                 const int m0 = (tile % p.tiles_m) * kBlockM;
                 const int n0 = (tile / p.tiles_m) * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
@@ -225,12 +277,14 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (elect_one()) {
             Ring slot, operand, acc;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+            for (int item = static_cast<int>(blockIdx.x); ok && item < num_items; item += static_cast<int>(gridDim.x)) {
                 ok = guard.wait(&tmem_empty[acc.idx], acc.phase ^ 1u, kSiteTmemEmpty);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc.idx * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int kb_begin = (item % splits) * kb_per_split;
+                const int kb_end = kb_begin + kb_per_split < num_kb ? kb_begin + kb_per_split : num_kb;
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 1) &&
                          guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
                     if (!ok) break;
@@ -240,7 +294,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k) {
                         umma_f16(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
-                                 (kb | k) != 0 ? 1u : 0u);
+                                 (kb != kb_begin || k != 0) ? 1u : 0u);
                     }
                     umma_commit(&load_empty[slot.idx]);
                     umma_commit(&operand_empty[operand.idx]);
@@ -258,58 +312,108 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
         Ring acc;
         bool ok = true;
-        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+        for (int item = static_cast<int>(blockIdx.x); ok && item < num_items; item += static_cast<int>(gridDim.x)) {
+            const int tile = item / splits;
+            const int split = item - tile * splits;
             const int m0 = (tile % p.tiles_m) * kBlockM;
             const int n0 = (tile / p.tiles_m) * BN;
-            ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
-            if (!ok) break;
+            const bool got = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
+            if (splits == 1 && !got) {
+                ok = false;
+                break;
+            }
             tc_fence_after_sync();
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * BN;
             uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+            if (splits == 1) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(taddr + c * 32, v);
-                tmem_wait_ld();
-                if (c == BN / 32 - 1) {
-                    // the accumulator is in registers: hand the TMEM buffer back before the stores
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
-                }
-                const int col0 = n0 + c * 32;
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int col = col0 + g * 8;
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        o[i] = pack_out<kOutBf16>(__uint_as_float(v[g * 8 + 2 * i]) * scale, __uint_as_float(v[g * 8 + 2 * i + 1]) * scale);
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_wait_ld();
+                    if (c == BN / 32 - 1) {
+                        // the accumulator is in registers: hand the TMEM buffer back before the stores
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
                     }
-                    if (p.bias != nullptr && col < p.N) {
-                        uint32_t bw[4];
-                        if (p.bias_vec) {
-                            const uint4 b4 = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-                            bw[0] = b4.x;
-                            bw[1] = b4.y;
-                            bw[2] = b4.z;
-                            bw[3] = b4.w;
-                        } else {
+                    finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
+                }
+            } else {
+                // K split: this CTA's fp32 partial goes to scratch, a ticket per tile says which CTA came last, and
+                // that one adds the partials in split order (so the sum does not depend on who it was) and finishes.
+                // The four epilogue warps meet at two named barriers per item, so none of them may leave the loop
+                // between the two: a warp whose wait ran out skips the work, and the second barrier tells all four.
+                // Scratch layout: [split][tile][32-column chunk][4-column group][row of the tile][4], so that the 32
+                // lanes of a warp (32 rows) write and read 512 consecutive bytes per instruction.
+                constexpr int kTileFloats = kBlockM * BN;
+                const int slot_row = (quarter * 32 + lane) * 4;
+                float* const part_tile = p.partials + (static_cast<int64_t>(split) * num_tiles + tile) * kTileFloats;
+#pragma unroll 1
+                for (int c = 0; got && c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_wait_ld();
+                    if (c == BN / 32 - 1) {
+                        // the accumulator is in registers: hand the TMEM buffer back before the stores
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
+                    }
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                bw[i] = static_cast<uint32_t>(__ldg(p.bias + col + 2 * i)) | (static_cast<uint32_t>(__ldg(p.bias + col + 2 * i + 1)) << 16);
+                    for (int g = 0; g < 8; ++g) {
+                        __stcg(reinterpret_cast<uint4*>(part_tile + (c * 8 + g) * (kBlockM * 4) + slot_row),
+                               make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]));
+                    }
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == kFirstEpilogueWarp * 32) {
+                    const uint32_t ticket = atomicAdd(p.counters + tile, 1u);
+                    const bool last = ticket == static_cast<uint32_t>(splits - 1);
+                    if (last) p.counters[tile] = 0u;  // every other split has drawn its ticket: ready for the next launch
+                    *last_flag = last ? 1u : 0u;
+                }
+                uint32_t any_failed;
+                asm volatile(
+                    "{\n\t"
+                    ".reg .pred P, Q;\n\t"
+                    "setp.ne.u32 P, %1, 0;\n\t"
+                    "bar.red.or.pred Q, 1, 128, P;\n\t"
+                    "selp.u32 %0, 1, 0, Q;\n\t"
+                    "}"
+                    : "=r"(any_failed)
+                    : "r"(got ? 0u : 1u)
+                    : "memory");
+                if (any_failed != 0u) {
+                    ok = false;
+                    break;
+                }
+                if (*last_flag != 0u) {
+                    // Holding the accumulator back so that the last CTA could add its own partial from tensor memory
+                    // was measured slower than reading all of them from the scratch: the MMA warp waits for the buffer.
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < BN / 32; ++c) {
+                        float sum[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                        for (int sp = 0; sp < splits; ++sp) {
+                            const float* const src = p.partials + (static_cast<int64_t>(sp) * num_tiles + tile) * kTileFloats + slot_row;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + g) * (kBlockM * 4)));
+                                sum[4 * g] += x.x;
+                                sum[4 * g + 1] += x.y;
+                                sum[4 * g + 2] += x.z;
+                                sum[4 * g + 3] += x.w;
                             }
                         }
+                        uint32_t v[32];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 x = unpack_out<kOutBf16>(o[i]);
-                            const float2 b = unpack_out<kOutBf16>(bw[i]);
-                            o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
-                        }
-                    }
-                    if (row < p.M && col < p.N) {
-                        *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
+                        finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
                     }
                 }
             }
@@ -327,8 +431,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         Ring slot, operand;
         bool ok = true;
         uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
-        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+        for (int item = static_cast<int>(blockIdx.x); ok && item < num_items; item += static_cast<int>(gridDim.x)) {
+            const int kb_begin = (item % splits) * kb_per_split;
+            const int kb_end = kb_begin + kb_per_split < num_kb ? kb_begin + kb_per_split : num_kb;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
                 if (turn == static_cast<uint32_t>(team)) {
                     ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
                          guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
@@ -958,7 +1064,13 @@ struct LaunchArgs {
     int64_t M, N, K;
     bool e5m2, a_bf16, out_bf16;
     cudaStream_t stream;
+    // K split of the one-CTA kernel (1 = none): fp32 scratch [splits][M][N] and one zeroed ticket per tile
+    int splits = 1;
+    float* partials = nullptr;
+    uint32_t* counters = nullptr;
 };
+
+inline int effective_splits(int64_t K, int splits);
 
 template <int BN, bool kE5M2, bool kOperandBf16, bool kOutBf16>
 bool launch_instance(const LaunchArgs& args) {
@@ -1004,9 +1116,18 @@ bool launch_instance(const LaunchArgs& args) {
     p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, kBlockM, BN);
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    p.splits = 1;
+    if (args.splits > 1 && args.partials != nullptr && args.counters != nullptr) {
+        const int num_kb = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
+        p.splits = effective_splits(args.K, args.splits);
+        p.kb_per_split = (num_kb + p.splits - 1) / p.splits;
+        p.partials = args.partials;
+        p.counters = args.counters;
+    }
+    const int64_t num_items = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
+    if (num_items > (1 << 30)) return false;
     const int sms = device_info().sm_count;
-    const int grid = num_tiles < sms ? num_tiles : sms;
+    const int grid = num_items < sms ? static_cast<int>(num_items) : sms;
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
 }
@@ -1615,6 +1736,36 @@ extern "C" bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prep
     const smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
                                use_fp8_e5m2, a_bf16, output_bf16, stream};
     return smm::launch_skinny(args, splits, partials, counters);
+}
+
+// launch_scaled_mm_splitk for taller problems, on the one-CTA kernel with 128 x `block_n` tiles (`block_n` 128 or 256):
+// a work item is (tile, K split), so a product with too few tiles for the SMs (a few hundred rows) still occupies
+// them all. `partials` holds feather_scaled_mm_splitk_wide_partial_floats(M, N, K, block_n, splits) floats; `counters` holds ceil(M / 128) * ceil(N / block_n) zeroed uint32, left zero again.
+// Any M. Returns false for another `block_n` or an unsupported shape.
+extern "C" bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
+                                             int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
+                                             bool output_bf16, int block_n, int splits, float* partials, uint32_t* counters, cudaStream_t stream) {
+    using namespace feather;
+    if (block_n != 128 && block_n != 256) return false;
+    if (M < 0 || N <= 0 || K <= 0 || N % 16 != 0 || K % 16 != 0) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+    if (M == 0) return true;
+    if (smm::effective_splits(K, splits) > 1 && (partials == nullptr || counters == nullptr)) return false;
+    smm::LaunchArgs args{a, b_prepacked, has_scale ? scale : nullptr, has_bias ? bias : nullptr, c, M, N, K,
+                         use_fp8_e5m2, a_bf16, output_bf16, stream};
+    args.splits = splits;
+    args.partials = partials;
+    args.counters = counters;
+    return block_n == 256 ? smm::launch_for_block_n<256>(args) : smm::launch_for_block_n<128>(args);
+}
+
+// Floats of `partials` scratch that `launch_scaled_mm_splitk_wide` needs: whole 128 x block_n tiles per split
+// (0 when the request collapses to one split or `block_n` is not 128 or 256).
+extern "C" int64_t feather_scaled_mm_splitk_wide_partial_floats(int64_t M, int64_t N, int64_t K, int block_n, int splits) {
+    if (M <= 0 || N <= 0 || K <= 0 || (block_n != 128 && block_n != 256)) return 0;
+    const int effective = feather::smm::effective_splits(K, splits);
+    const int64_t tiles = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
+    return effective > 1 ? static_cast<int64_t>(effective) * tiles * feather::smm::kBlockM * block_n : 0;
 }
 
 // Floats of `partials` scratch that `launch_scaled_mm_splitk` needs (0 when the request collapses to one split).

@@ -101,11 +101,12 @@ void scaled_mm(const Tensor& a, const Tensor& b_prepacked, const std::optional<T
     STD_TORCH_CHECK(launched, "Unsupported config");
 }
 
-// Split-K scaled_mm for skinny problems. Same tensor contract as `scaled_mm`, plus caller-provided scratch:
-// `partials` (float32, at least feather_scaled_mm_splitk_partial_floats elements) and `counters` (int32,
-// ceil(N / 64) zeros). The Python wrapper allocates both with torch, so they are stream ordered.
+// Split-K scaled_mm. `block_n` 64: the skinny kernel (M <= 128); 128 or 256: the one-CTA kernel walking (tile, K split)
+// items, any M. Same tensor contract as `scaled_mm`, plus caller-provided scratch: `partials` (float32, at least
+// feather_scaled_mm_splitk_partial_floats elements) and `counters` (int32 zeros, one per tile of 128 x block_n; ceil(N / 64)
+// for the skinny kernel). The Python wrapper allocates both with torch, so they are stream ordered.
 void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::optional<Tensor>& scale, const std::optional<Tensor>& bias, Tensor& c,
-                      Tensor& partials, Tensor& counters, int64_t splits) {
+                      Tensor& partials, Tensor& counters, int64_t splits, int64_t block_n) {
     STD_TORCH_CHECK(a.is_cuda() && b_prepacked.is_cuda() && c.is_cuda() && partials.is_cuda() && counters.is_cuda(), "tensors must be CUDA tensors");
     const auto device = a.get_device_index();
     STD_TORCH_CHECK(b_prepacked.get_device_index() == device && c.get_device_index() == device && partials.get_device_index() == device &&
@@ -120,7 +121,8 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
     const int64_t M = a.size(0);
     const int64_t K = a.size(1);
     const int64_t N = b_prepacked.size(1);
-    STD_TORCH_CHECK(M <= 128, "the split-K path is for M <= 128");
+    STD_TORCH_CHECK(block_n == 64 || block_n == 128 || block_n == 256, "block_n must be 64, 128 or 256");
+    STD_TORCH_CHECK(block_n != 64 || M <= 128, "the 64-wide split-K path is for M <= 128");
     STD_TORCH_CHECK(K % 16 == 0, "K must be divisible by 16");
     STD_TORCH_CHECK(N % 16 == 0, "N must be divisible by 16");
     STD_TORCH_CHECK(b_prepacked.size(0) >= K / 16 && b_prepacked.size(0) % 8 == 0, "b_prepacked.shape[0] must cover K padded to 128");
@@ -128,8 +130,11 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
     STD_TORCH_CHECK(a.is_contiguous() && b_prepacked.is_contiguous() && c.is_contiguous(), "a, b_prepacked and c must be contiguous");
     STD_TORCH_CHECK(partials.scalar_type() == ScalarType::Float && partials.is_contiguous(), "partials must be contiguous float32");
     STD_TORCH_CHECK(counters.scalar_type() == ScalarType::Int && counters.is_contiguous(), "counters must be contiguous int32");
-    STD_TORCH_CHECK(partials.numel() >= feather_scaled_mm_splitk_partial_floats(M, N, K, static_cast<int>(splits)), "partials is too small");
-    STD_TORCH_CHECK(counters.numel() >= (N + 63) / 64, "counters must have ceil(N / 64) elements");
+    const int64_t scratch = block_n == 64 ? feather_scaled_mm_splitk_partial_floats(M, N, K, static_cast<int>(splits))
+                                          : feather_scaled_mm_splitk_wide_partial_floats(M, N, K, static_cast<int>(block_n), static_cast<int>(splits));
+    STD_TORCH_CHECK(partials.numel() >= scratch, "partials is too small");
+    const int64_t tickets = block_n == 64 ? (N + 63) / 64 : ((M + 127) / 128) * ((N + block_n - 1) / block_n);
+    STD_TORCH_CHECK(counters.numel() >= tickets, "counters must have one element per tile");
     if (scale.has_value()) {
         STD_TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == ScalarType::Float && scale->numel() == 1, "scale must be one float32 on the device");
     }
@@ -142,13 +147,22 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
                     "data pointers must be 16-byte aligned");
     torch::stable::accelerator::DeviceGuard guard(device);
     const feather_stream_t stream = current_stream(device);
-    const bool launched = launch_scaled_mm_splitk(
-        static_cast<const uint16_t*>(a.const_data_ptr()), static_cast<const uint8_t*>(b_prepacked.const_data_ptr()),
-        scale.has_value() ? static_cast<const float*>(scale->const_data_ptr()) : nullptr,
-        bias.has_value() ? static_cast<const uint16_t*>(bias->const_data_ptr()) : nullptr, static_cast<uint16_t*>(c.mutable_data_ptr()), M, N, K,
-        scale.has_value() ? 1 : 0, bias.has_value() ? 1 : 0, b_type == ScalarType::Float8_e5m2, a.scalar_type() == ScalarType::BFloat16,
-        c.scalar_type() == ScalarType::BFloat16, static_cast<int>(splits), static_cast<float*>(partials.mutable_data_ptr()),
-        static_cast<uint32_t*>(counters.mutable_data_ptr()), stream);
+    const uint16_t* const a_ptr = static_cast<const uint16_t*>(a.const_data_ptr());
+    const uint8_t* const b_ptr = static_cast<const uint8_t*>(b_prepacked.const_data_ptr());
+    const float* const scale_ptr = scale.has_value() ? static_cast<const float*>(scale->const_data_ptr()) : nullptr;
+    const uint16_t* const bias_ptr = bias.has_value() ? static_cast<const uint16_t*>(bias->const_data_ptr()) : nullptr;
+    uint16_t* const c_ptr = static_cast<uint16_t*>(c.mutable_data_ptr());
+    float* const partials_ptr = static_cast<float*>(partials.mutable_data_ptr());
+    uint32_t* const counters_ptr = static_cast<uint32_t*>(counters.mutable_data_ptr());
+    const bool e5m2 = b_type == ScalarType::Float8_e5m2;
+    const bool a_bf16 = a.scalar_type() == ScalarType::BFloat16;
+    const bool c_bf16 = c.scalar_type() == ScalarType::BFloat16;
+    const bool launched =
+        block_n == 64 ? launch_scaled_mm_splitk(a_ptr, b_ptr, scale_ptr, bias_ptr, c_ptr, M, N, K, scale.has_value() ? 1 : 0, bias.has_value() ? 1 : 0,
+                                                e5m2, a_bf16, c_bf16, static_cast<int>(splits), partials_ptr, counters_ptr, stream)
+                      : launch_scaled_mm_splitk_wide(a_ptr, b_ptr, scale_ptr, bias_ptr, c_ptr, M, N, K, scale.has_value() ? 1 : 0,
+                                                     bias.has_value() ? 1 : 0, e5m2, a_bf16, c_bf16, static_cast<int>(block_n),
+                                                     static_cast<int>(splits), partials_ptr, counters_ptr, stream);
     STD_TORCH_CHECK(launched, "scaled_mm_splitk: unsupported problem");
 }
 
@@ -310,7 +324,7 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
         "int unroll_k, int repeat_m, int repeat_n, bool prefetch) -> ()");
     m.def(
         "scaled_mm_splitk(Tensor a, Tensor b_prepacked, Tensor? scale, Tensor? bias, Tensor(a!) c, Tensor(b!) partials, Tensor(c!) counters, "
-        "int splits) -> ()");
+        "int splits, int block_n=64) -> ()");
     m.def(
         "int8_scaled_mm(Tensor a, Tensor b_prepacked, Tensor a_scale, Tensor? b_scale, Tensor? bias, Tensor(a!) c, bool transposed_b, "
         "int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n) -> ()");

@@ -70,6 +70,23 @@ def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
     return max(1, min(4, _RESIDENT_SKINNY_CTAS // tiles, k_blocks // 16))
 
 
+_WIDE_SPLIT_MIN_K_BLOCKS = 128   # 64-deep k blocks: below this the fp32 partials cost more than the idle SMs
+
+
+def select_wide_splits(M: int, N: int, K: int) -> int:
+    """K splits of the one-CTA kernel with 128 x 128 tiles for more than one row tile (1 = none). Worth it only when
+    the tiles leave at least half of the SMs idle and the contraction is long: measured 58 -> 44 us at
+    384 x 3072 x 12288 and 41 -> 34 us at 256 x 3072 x 8192 with two splits, no gain at 256 x 4096 x 4096, a loss
+    whenever the tiles alone fill the SMs or with three and more splits (the CTA that draws a tile's last ticket reads
+    every partial back through four warps)."""
+    if M <= _SKINNY_MAX_M:
+        return 1
+    tiles = -(-M // 128) * -(-N // 128)
+    if tiles > _PAIR_COUNT or -(-K // 64) < _WIDE_SPLIT_MIN_K_BLOCKS:
+        return 1
+    return 2
+
+
 _TICKETS: dict = {}
 
 
@@ -106,6 +123,12 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
             return
         partials = torch.empty(splits * m * n, device=a.device, dtype=torch.float32)
         torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, n), splits)
+        return
+    splits = select_wide_splits(m, n, k)
+    if splits > 1:
+        tiles = -(-m // 128) * -(-n // 128)
+        partials = torch.empty(splits * tiles * 128 * 128, device=a.device, dtype=torch.float32)
+        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, 64 * tiles), splits, 128)
         return
     _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(m, n, k))
 

@@ -64,6 +64,27 @@ def assert_clean(symbol):
     assert _lib.read_status(symbol) == (0, 0)
 
 
+def scaled_mm_splitk_wide(a, b_prepacked, scale, bias, out_dtype, block_n, splits, partials=None, counters=None):
+    """Split-K launcher of the one-CTA kernel (128 x block_n tiles) with caller-provided scratch. Returns (c, partials, counters)."""
+    m, k = a.shape
+    n = b_prepacked.shape[1]
+    lib = _lib.load()
+    floats = lib.feather_scaled_mm_splitk_wide_partial_floats(m, n, k, block_n, splits)
+    if partials is None:
+        partials = torch.empty(max(int(floats), 1), device=a.device, dtype=torch.float32)
+    if counters is None:
+        counters = torch.zeros(-(-m // 128) * -(-n // block_n), device=a.device, dtype=torch.int32)
+    assert partials.numel() >= floats
+    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    ok = lib.launch_scaled_mm_splitk_wide(
+        _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), m, n, k, int(scale is not None), int(bias is not None),
+        b_prepacked.dtype == torch.float8_e5m2, a.dtype == torch.bfloat16, out_dtype == torch.bfloat16, block_n, splits, _ptr(partials), _ptr(counters),
+        _stream(),
+    )
+    assert ok, "launch_scaled_mm_splitk_wide refused the call"
+    return c, partials, counters
+
+
 def scaled_mm_splitk(a, b_prepacked, scale, bias, out_dtype, splits, partials=None, counters=None):
     """Skinny split-K launcher with caller-provided scratch. Returns (c, partials, counters)."""
     m, k = a.shape

@@ -191,6 +191,46 @@ def test_skinny_split_k_through_the_c_abi(cuda_device, shape, a_dtype, b_dtype, 
             partials, counters, previous = partials_used, counters_used, out
 
 
+@pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16)])
+@pytest.mark.parametrize("shape", [(129, 272, 1040), (384, 3072, 4096), (256, 1040, 8192), (200, 48, 64), (700, 528, 2000 // 16 * 16)])
+def test_split_k_of_the_one_cta_kernel_through_the_c_abi(cuda_device, shape, a_dtype, b_dtype, out_dtype):
+    # (tile, K split) work items on the persistent kernel: ragged rows and columns, more splits than k blocks, a
+    # persistent CTA that meets several items, tickets back at zero, and the same bits whoever draws the last ticket
+    m, n, k = shape
+    a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype, seed=m + k)
+    ref = osm.scaled_mm_f32(a, packed, scale, bias, out_dtype, b_prepacked=True)
+    dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+    for block_n in (128, 256):
+        partials = counters = previous = None
+        for splits in (1, 2, 3, 5, 5, 5):
+            reuse = splits == 5 and partials is not None
+            out, partials_used, counters_used = _cabi.scaled_mm_splitk_wide(*dev, out_dtype, block_n, splits, partials if reuse else None,
+                                                                            counters if reuse else None)
+            _cabi.assert_clean(STATUS)
+            _compare(out, ref, out_dtype, 1e-3)
+            assert int(counters_used.abs().sum().item()) == 0
+            if splits == 5:
+                if previous is not None:
+                    assert torch.equal(out, previous)
+                partials, counters, previous = partials_used, counters_used, out
+
+
+def test_split_k_of_the_one_cta_kernel_is_what_the_heuristic_picks_for_few_tiles_and_long_k(cuda_device):
+    import feather_ops_b200 as fo
+    from feather_ops_b200 import scaled_mm as sm
+
+    assert sm.select_wide_splits(384, 3072, 12288) == 2
+    assert sm.select_wide_splits(4096, 12288, 3072) == 1 and sm.select_wide_splits(128, 3072, 12288) == 1
+    assert sm.select_wide_splits(256, 4096, 4096) == 1
+    a, packed, scale, bias = osm.make_inputs(384, 3072, 8192, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, seed=5)
+    ref = osm.scaled_mm_f32(a, packed, scale, bias, torch.bfloat16, b_prepacked=True)
+    dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+    out = fo.scaled_mm_hip(*dev, torch.bfloat16)
+    _cabi.assert_clean(STATUS)
+    _compare(out, ref, torch.bfloat16, 1e-3)
+    assert torch.equal(out, fo.scaled_mm_hip(*dev, torch.bfloat16))
+
+
 @pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16),
                                                        (torch.float16, torch.float8_e5m2, torch.bfloat16)])
 @pytest.mark.parametrize("shape", [(1, 9472, 512), (2, 12288, 3072), (1, 20000, 1040), (2, 9600, 16)])
