@@ -8,6 +8,7 @@ is self-contained: the tests never need the reference checkout.
 """
 
 import importlib
+import os
 import pathlib
 import sys
 import types
@@ -24,7 +25,7 @@ def load_reference(root: str):
 
 
 def main() -> None:
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FEATHER_OPS_REFERENCE", "/root/reference"))
     gen = torch.Generator().manual_seed(20240607)
     out: dict = {}
 
