@@ -889,7 +889,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Warp-MMA version of the forward direction for at most 16 rows (a text band, a decode step): tcgen05 has no shape
+// Warp-MMA version of the forward direction for at most 32 rows (a text band, a decode step): tcgen05 has no shape
 // below 64 rows and a CTA-pair launch costs more than streaming a few MB of weight, so this case runs on mma.sync
 // m16n8k32 (int8, exact int32 accumulation). A warp owns 32 output columns for one eighth of the contraction; the
 // eight warps' int32 partial sums are added through shared memory (integer addition: any order gives the same bits).
@@ -897,9 +897,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
 // and 16+4t..16+4t+3 take k = 8t..8t+7), so a lane's A fragment is eight consecutive activation bytes and its B
 // fragment two dwords of the prepack (contraction steps 2t and 2t+1 of one output column): no shuffles, no staging.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kWmmaMaxRows = 16;
+constexpr int kWmmaMaxRows = 32;
+constexpr int kWmmaTwoTileMaxN = 8192;   // 17..32 rows: from this width on the CTA-pair kernel has enough tiles and wins
 constexpr int kWmmaWarps = 8;
-constexpr int kWmmaUnroll = 2;   // 32-deep blocks in flight per warp (16 weight dwords per lane)
 
 __device__ __forceinline__ void mma_m16n8k32_s8(int32_t (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -907,12 +907,15 @@ __device__ __forceinline__ void mma_m16n8k32_s8(int32_t (&d)[4], const uint32_t 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool kOutBf16>
-__global__ void __launch_bounds__(32 * kWmmaWarps, 3) int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
-                                                                           const float* __restrict__ a_scale, const float* __restrict__ b_scale,
-                                                                           const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N,
-                                                                           int K, int64_t stride_kc, int64_t stride_out) {
-    __shared__ int32_t partial[kWmmaWarps][4][4][32];   // [warp][8-column block][fragment register][lane]
+// kRowTiles 16-row tiles per warp (1 or 2: up to 32 rows); every weight dword is fetched once and used for all of them.
+// Four tiles per warp (64 rows) were measured slower than the CTA-pair kernel at every shape tried: 128 registers, one
+// block in flight.
+template <int kRowTiles, bool kOutBf16>
+__global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2)
+int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b, const float* __restrict__ a_scale, const float* __restrict__ b_scale,
+                    const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, int64_t stride_kc, int64_t stride_out) {
+    constexpr int kUnroll = 2;   // 32-deep blocks in flight per warp (8 weight dwords per lane each)
+    __shared__ int32_t partial[kWmmaWarps][4][4][32];   // [warp][8-column block][fragment register][lane], one row tile at a time
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
     const int g = lane >> 2;   // fragment row (and row + 8), B column inside an 8-column block
@@ -924,16 +927,27 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, 3) int8_mm_wmma_kernel(const 
     const int s_end = s_begin + per_warp < blocks ? s_begin + per_warp : blocks;
     const int k4_total = K / 4;
 
-    int32_t acc[4][4];
+    int32_t acc[kRowTiles][4][4];
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk) {
+    for (int rt = 0; rt < kRowTiles; ++rt) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) acc[blk][r] = 0;
+        for (int blk = 0; blk < 4; ++blk) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[rt][blk][r] = 0;
+        }
     }
-    const bool row_lo = g < M;
-    const bool row_hi = g + 8 < M;
-    const int8_t* const a_lo = a + static_cast<int64_t>(row_lo ? g : 0) * K + 8 * t;
-    const int8_t* const a_hi = a + static_cast<int64_t>(row_hi ? g + 8 : 0) * K + 8 * t;
+    // rows of this lane's A fragments: 16 rt + g and 16 rt + g + 8
+    bool row_live[kRowTiles][2];
+    const int8_t* a_row[kRowTiles][2];
+#pragma unroll
+    for (int rt = 0; rt < kRowTiles; ++rt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int row = 16 * rt + g + 8 * h;
+            row_live[rt][h] = row < M;
+            a_row[rt][h] = a + static_cast<int64_t>(row_live[rt][h] ? row : 0) * K + 8 * t;
+        }
+    }
     // dword (contraction step k4, output column n) of the prepack: micro-tile (k4, n / 4), dword n % 4
     const uint8_t* w_col[4];
     bool col_live[4];
@@ -944,11 +958,11 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, 3) int8_mm_wmma_kernel(const 
         w_col[blk] = b + (static_cast<int64_t>(col_live[blk] ? n / 4 : 0) * stride_out) * 16 + (n % 4) * 4;
     }
 
-    for (int s0 = s_begin; s0 < s_end; s0 += kWmmaUnroll) {
-        uint32_t w[kWmmaUnroll][4][2];
-        uint2 x_lo[kWmmaUnroll], x_hi[kWmmaUnroll];
+    for (int s0 = s_begin; s0 < s_end; s0 += kUnroll) {
+        uint32_t w[kUnroll][4][2];
+        uint2 x[kUnroll][kRowTiles][2];
 #pragma unroll
-        for (int u = 0; u < kWmmaUnroll; ++u) {
+        for (int u = 0; u < kUnroll; ++u) {
             const int k4 = (s0 + u) * 8 + 2 * t;            // this lane's two contraction steps of the block
             const bool live = s0 + u < s_end && k4 < k4_total;   // k4 + 1 exists as well: K / 4 is a multiple of 4
 #pragma unroll
@@ -957,80 +971,99 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, 3) int8_mm_wmma_kernel(const 
                 w[u][blk][0] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src)) : 0u;
                 w[u][blk][1] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src + stride_kc * 16)) : 0u;
             }
-            x_lo[u] = (live && row_lo) ? __ldg(reinterpret_cast<const uint2*>(a_lo + (s0 + u) * 32)) : make_uint2(0u, 0u);
-            x_hi[u] = (live && row_hi) ? __ldg(reinterpret_cast<const uint2*>(a_hi + (s0 + u) * 32)) : make_uint2(0u, 0u);
+#pragma unroll
+            for (int rt = 0; rt < kRowTiles; ++rt) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    x[u][rt][h] = (live && row_live[rt][h]) ? __ldg(reinterpret_cast<const uint2*>(a_row[rt][h] + (s0 + u) * 32)) : make_uint2(0u, 0u);
+                }
+            }
         }
 #pragma unroll
-        for (int u = 0; u < kWmmaUnroll; ++u) {
-            // A fragment: {row g: k 8t..8t+3}, {row g+8: same}, {row g: k 8t+4..8t+7}, {row g+8: same}
-            const uint32_t af[4] = {x_lo[u].x, x_hi[u].x, x_lo[u].y, x_hi[u].y};
+        for (int u = 0; u < kUnroll; ++u) {
 #pragma unroll
-            for (int blk = 0; blk < 4; ++blk) mma_m16n8k32_s8(acc[blk], af, w[u][blk][0], w[u][blk][1]);
+            for (int rt = 0; rt < kRowTiles; ++rt) {
+                // A fragment: {row g: k 8t..8t+3}, {row g+8: same}, {row g: k 8t+4..8t+7}, {row g+8: same}
+                const uint32_t af[4] = {x[u][rt][0].x, x[u][rt][1].x, x[u][rt][0].y, x[u][rt][1].y};
+#pragma unroll
+                for (int blk = 0; blk < 4; ++blk) mma_m16n8k32_s8(acc[rt][blk], af, w[u][blk][0], w[u][blk][1]);
+            }
         }
     }
+    // per row tile: the eight warps' partial sums meet in shared memory, warp blk adds those of column block blk and
+    // writes it: accumulator registers 0, 1 are row g, columns 2t and 2t+1 of the block; registers 2, 3 the same
+    // columns of row g + 8
+    const int col = n0 + 8 * (warp & 3) + 2 * t;
+    const bool writes = warp < 4 && col < N;  // N is a multiple of 4 and col is even: col + 1 exists as well
+    const float s0 = (writes && b_scale != nullptr) ? __ldg(b_scale + col) : 1.0f;
+    const float s1 = (writes && b_scale != nullptr) ? __ldg(b_scale + col + 1) : 1.0f;
+    const float z0 = (writes && bias != nullptr) ? out_bits_to_float<kOutBf16>(__ldg(bias + col)) : 0.0f;
+    const float z1 = (writes && bias != nullptr) ? out_bits_to_float<kOutBf16>(__ldg(bias + col + 1)) : 0.0f;
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk) {
+    for (int rt = 0; rt < kRowTiles; ++rt) {
+        if (rt > 0) __syncthreads();   // the previous row tile's sums have been read
 #pragma unroll
-        for (int r = 0; r < 4; ++r) partial[warp][blk][r][lane] = acc[blk][r];
-    }
-    __syncthreads();
-    // warp blk adds the eight partial sums of block blk and writes it: accumulator registers 0, 1 are row g, columns
-    // 2t and 2t+1 of the block; registers 2, 3 the same columns of row g + 8
-    if (warp < 4) {
-        const int blk = warp;
-        const int col = n0 + 8 * blk + 2 * t;
-        int32_t sum[4] = {0, 0, 0, 0};
+        for (int blk = 0; blk < 4; ++blk) {
 #pragma unroll
-        for (int w2 = 0; w2 < kWmmaWarps; ++w2) {
-#pragma unroll
-            for (int r = 0; r < 4; ++r) sum[r] += partial[w2][blk][r][lane];
+            for (int r = 0; r < 4; ++r) partial[warp][blk][r][lane] = acc[rt][blk][r];
         }
-        if (col < N) {  // N is a multiple of 4 and col is even: col + 1 exists as well
-            const float s0 = b_scale != nullptr ? __ldg(b_scale + col) : 1.0f;
-            const float s1 = b_scale != nullptr ? __ldg(b_scale + col + 1) : 1.0f;
-            const float z0 = bias != nullptr ? out_bits_to_float<kOutBf16>(__ldg(bias + col)) : 0.0f;
-            const float z1 = bias != nullptr ? out_bits_to_float<kOutBf16>(__ldg(bias + col + 1)) : 0.0f;
+        __syncthreads();
+        if (warp < 4) {
+            int32_t sum[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int row = g + 8 * h;
-                if (row >= M) continue;
-                const float rs = __ldg(a_scale + row);
-                float v0 = static_cast<float>(sum[2 * h]) * rs;
-                float v1 = static_cast<float>(sum[2 * h + 1]) * rs;
-                if (b_scale != nullptr) {
-                    v0 *= s0;
-                    v1 *= s1;
+            for (int w2 = 0; w2 < kWmmaWarps; ++w2) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) sum[r] += partial[w2][warp][r][lane];
+            }
+            if (writes) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = 16 * rt + g + 8 * h;
+                    if (row >= M) continue;
+                    const float rs = __ldg(a_scale + row);
+                    float v0 = static_cast<float>(sum[2 * h]) * rs;
+                    float v1 = static_cast<float>(sum[2 * h + 1]) * rs;
+                    if (b_scale != nullptr) {
+                        v0 *= s0;
+                        v1 *= s1;
+                    }
+                    if (bias != nullptr) {
+                        v0 += z0;
+                        v1 += z1;
+                    }
+                    *reinterpret_cast<uint32_t*>(c + static_cast<int64_t>(row) * N + col) = pack_out<kOutBf16>(v0, v1);
                 }
-                if (bias != nullptr) {
-                    v0 += z0;
-                    v1 += z1;
-                }
-                *reinterpret_cast<uint32_t*>(c + static_cast<int64_t>(row) * N + col) = pack_out<kOutBf16>(v0, v1);
             }
         }
     }
 }
 
-// True when the warp-MMA kernel takes the problem: forward direction, at most 16 rows, operands aligned for its 8-byte
+// True when the warp-MMA kernel takes the problem: forward direction, at most 16 rows (32 for outputs narrower than
+// 8192 columns: measured 6.7-7.2 against 13.7 us at 3072 x 3072, 18.7 against 36 at 3072 x 12288, but 15.7-18.6 against
+// 15.1 at 12288 x 3072, where the pair kernel has 48 tiles to spread), operands aligned for its 8-byte
 // activation loads, dword weight loads and 4-byte stores.
 bool wmma_eligible(const LaunchArgs& args) {
-    return !args.transposed_b && args.M <= kWmmaMaxRows && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
+    return !args.transposed_b && args.M <= kWmmaMaxRows && (args.M <= 16 || args.N_out < kWmmaTwoTileMaxN) && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
            (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 3u) == 0 &&
            (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0 && std::getenv("FEATHER_INT8_WMMA_OFF") == nullptr;
 }
 
 bool launch_wmma(const LaunchArgs& args) {
     const unsigned grid = static_cast<unsigned>((args.N_out + 31) / 32);
-    if (args.out_bf16) {
-        int8_mm_wmma_kernel<true><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,
-                                                                              static_cast<int>(args.M), static_cast<int>(args.N_out),
-                                                                              static_cast<int>(args.K), args.stride_kc, args.stride_out);
-    } else {
-        int8_mm_wmma_kernel<false><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,
-                                                                               static_cast<int>(args.M), static_cast<int>(args.N_out),
-                                                                               static_cast<int>(args.K), args.stride_kc, args.stride_out);
+    const int row_tiles = args.M <= 16 ? 1 : 2;
+#define FEATHER_I8_WMMA_CASE(RT, OUT)                                                                                              \
+    if (row_tiles == RT && args.out_bf16 == OUT) {                                                                                 \
+        int8_mm_wmma_kernel<RT, OUT><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,  \
+                                                                                 static_cast<int>(args.M), static_cast<int>(args.N_out),      \
+                                                                                 static_cast<int>(args.K), args.stride_kc, args.stride_out);  \
+        return cudaGetLastError() == cudaSuccess;                                                                                  \
     }
-    return cudaGetLastError() == cudaSuccess;
+    FEATHER_I8_WMMA_CASE(1, true)
+    FEATHER_I8_WMMA_CASE(1, false)
+    FEATHER_I8_WMMA_CASE(2, true)
+    FEATHER_I8_WMMA_CASE(2, false)
+#undef FEATHER_I8_WMMA_CASE
+    return false;
 }
 
 // The pair kernel fetches the weight by TMA: the micro-tile axis that its boxes run along must be contiguous,
