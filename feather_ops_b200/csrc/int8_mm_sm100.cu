@@ -889,7 +889,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Warp-MMA version of the forward direction for at most 32 rows (a text band, a decode step): tcgen05 has no shape
+// Warp-MMA version of the forward direction for at most 64 rows (a text band, a decode step): tcgen05 has no shape
 // below 64 rows and a CTA-pair launch costs more than streaming a few MB of weight, so this case runs on mma.sync
 // m16n8k32 (int8, exact int32 accumulation). A warp owns 32 output columns for one eighth of the contraction; the
 // eight warps' int32 partial sums are added through shared memory (integer addition: any order gives the same bits).
@@ -897,7 +897,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
 // and 16+4t..16+4t+3 take k = 8t..8t+7), so a lane's A fragment is eight consecutive activation bytes and its B
 // fragment two dwords of the prepack (contraction steps 2t and 2t+1 of one output column): no shuffles, no staging.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kWmmaMaxRows = 32;
+constexpr int kWmmaMaxRows = 64;    // two grid rows of 32: beyond that the pair kernel wins (128 rows at K = 12288: 54 against 38 us)
 constexpr int kWmmaTwoTileMaxN = 8192;   // 17..32 rows: from this width on the CTA-pair kernel has enough tiles and wins
 constexpr int kWmmaWarps = 8;
 
@@ -921,6 +921,7 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
     const int g = lane >> 2;   // fragment row (and row + 8), B column inside an 8-column block
     const int t = lane & 3;    // which eight k of the 32-deep block
     const int n0 = static_cast<int>(blockIdx.x) * 32;
+    const int row0 = static_cast<int>(blockIdx.y) * 16 * kRowTiles;   // more rows than a warp's tiles: one grid row per block of them
     const int blocks = K / 32 + (K % 32 != 0 ? 1 : 0);   // K is a multiple of 16: the last block may be half
     const int per_warp = (blocks + kWmmaWarps - 1) / kWmmaWarps;
     const int s_begin = warp * per_warp;
@@ -943,7 +944,7 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
     for (int rt = 0; rt < kRowTiles; ++rt) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int row = 16 * rt + g + 8 * h;
+            const int row = row0 + 16 * rt + g + 8 * h;
             row_live[rt][h] = row < M;
             a_row[rt][h] = a + static_cast<int64_t>(row_live[rt][h] ? row : 0) * K + 8 * t;
         }
@@ -1018,7 +1019,7 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
             if (writes) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int row = 16 * rt + g + 8 * h;
+                    const int row = row0 + 16 * rt + g + 8 * h;
                     if (row >= M) continue;
                     const float rs = __ldg(a_scale + row);
                     float v0 = static_cast<float>(sum[2 * h]) * rs;
@@ -1038,9 +1039,9 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
     }
 }
 
-// True when the warp-MMA kernel takes the problem: forward direction, at most 16 rows (32 for outputs narrower than
-// 8192 columns: measured 6.7-7.2 against 13.7 us at 3072 x 3072, 18.7 against 36 at 3072 x 12288, but 15.7-18.6 against
-// 15.1 at 12288 x 3072, where the pair kernel has 48 tiles to spread), operands aligned for its 8-byte
+// True when the warp-MMA kernel takes the problem: forward direction, at most 16 rows (64 for outputs narrower than
+// 8192 columns: measured 6.9-10.3 against 13.7-14.3 us at 3072 x 3072, 18.4-30.4 against 36 at 3072 x 12288, but 15.7-18.6
+// against 15.1 at 12288 x 3072, where the pair kernel has 48 tiles to spread), operands aligned for its 8-byte
 // activation loads, dword weight loads and 4-byte stores.
 bool wmma_eligible(const LaunchArgs& args) {
     return !args.transposed_b && args.M <= kWmmaMaxRows && (args.M <= 16 || args.N_out < kWmmaTwoTileMaxN) && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
@@ -1049,8 +1050,8 @@ bool wmma_eligible(const LaunchArgs& args) {
 }
 
 bool launch_wmma(const LaunchArgs& args) {
-    const unsigned grid = static_cast<unsigned>((args.N_out + 31) / 32);
     const int row_tiles = args.M <= 16 ? 1 : 2;
+    const dim3 grid(static_cast<unsigned>((args.N_out + 31) / 32), static_cast<unsigned>((args.M + 16 * row_tiles - 1) / (16 * row_tiles)));
 #define FEATHER_I8_WMMA_CASE(RT, OUT)                                                                                              \
     if (row_tiles == RT && args.out_bf16 == OUT) {                                                                                 \
         int8_mm_wmma_kernel<RT, OUT><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,  \

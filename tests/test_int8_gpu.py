@@ -193,7 +193,7 @@ def test_benchmark_shape_by_properties(cuda_device):
 @pytest.mark.parametrize("shape", [(1, 256, 64), (5, 3072, 3072), (16, 1040, 528), (9, 260, 16), (16, 12288, 1024), (17, 3072, 3072), (32, 1040, 528),
                                    (33, 260, 16), (47, 3072, 1040), (64, 3072, 3072)])
 def test_few_rows_take_the_warp_mma_kernel(cuda_device, shape, out_dtype):
-    # forward direction with at most 16 rows (32 for narrow outputs; one or two 16-row tiles per warp) runs on mma.sync with a permuted contraction index: exact int32 sums, the
+    # forward direction with at most 16 rows (64 for narrow outputs; two 16-row tiles per warp, one grid row per 32 rows) runs on mma.sync with a permuted contraction index: exact int32 sums, the
     # same oracle and tolerance, ragged last column block (260, 1040), a contraction with a half block (528 = 16.5 x 32)
     m, n, k = shape
     w, a, a_scale, w_scale, bias, n_out = _gemm_case(m, n, k, False, out_dtype, seed=m + n + k)
