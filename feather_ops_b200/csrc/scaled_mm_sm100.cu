@@ -1545,10 +1545,14 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scale
     }
 }
 
-// True when the warp-MMA kernel takes the problem: 3..16 rows and at least two CTAs of 32 columns per SM; the
-// activation rows are read with 8-byte loads and the output with 4-byte stores.
+// True when the warp-MMA kernel takes the problem: at most 16 rows (one and two rows of a wide output go to the vector
+// kernel first) and at least sixteen CTAs of 32 columns; the activation rows are read with 8-byte loads and the output
+// with 4-byte stores. It was first limited to outputs of two CTAs per SM and more; measured against the skinny tcgen05
+// kernel it also wins below that: 16 rows at 4096 x 4096 11.4 against 18.3 us, 3072 x 3072 9.0 against 14.9,
+// 1280 x 1280 5.0 against 8.8, 8192 x 3072 12.1 against 18.0; level at N = 3072, K = 12288 (29 us).
+constexpr int64_t kWmmaMinN = 512;
 inline bool wmma_eligible(const LaunchArgs& args) {
-    return args.M <= kWmmaMaxRows && args.N >= 64ll * device_info().sm_count && args.K % 16 == 0 &&
+    return args.M <= kWmmaMaxRows && args.N >= kWmmaMinN && args.K % 16 == 0 &&
            (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 15u) == 0 &&
            (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0;
 }

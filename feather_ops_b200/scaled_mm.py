@@ -52,6 +52,8 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
     return _TILE_OF_WIDTH[best[1]]
 
 
+_WARP_MMA_MAX_M = 16     # the launcher's vector (1-2 rows, wide outputs) and warp-MMA kernels take these rows
+_WARP_MMA_MIN_N = 512
 _SKINNY_MAX_M = 128      # one row tile: the weight stream is the cost, a 64-wide tile per CTA, two CTAs per SM
 _SKINNY_WIDE_M = 64      # above this the activation re-reads of 64-wide tiles cost more than 128-wide tiles save
 _SPLIT_MAX_M = 32        # below this the fp32 partials are small against the weight and K is split as well
@@ -111,6 +113,10 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
     """Tile choice + launch as one opaque node, so a compiled caller does not specialize on the heuristic."""
     m, k = a.shape
     n = b_prepacked.shape[1]
+    if 0 < m <= _WARP_MMA_MAX_M and n >= _WARP_MMA_MIN_N:
+        # the launcher runs these on the vector or the warp-MMA kernel whatever the tile: no scratch to allocate
+        _launch(a, b_prepacked, scale, bias, out, _TILE_N64)
+        return
     if 0 < m <= _SKINNY_MAX_M:
         splits = select_scaled_mm_splits(m, n, k)
         if m > _SKINNY_WIDE_M and -(-n // 128) >= _PAIR_COUNT:

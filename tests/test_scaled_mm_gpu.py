@@ -252,9 +252,10 @@ def test_one_and_two_rows_take_the_vector_kernel(cuda_device, shape, a_dtype, b_
 
 @pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16),
                                                        (torch.float16, torch.float8_e5m2, torch.bfloat16)])
-@pytest.mark.parametrize("shape", [(3, 9472, 512), (8, 12288, 3072), (9, 9488, 1040), (16, 20000, 256), (16, 9600, 16)])
-def test_three_to_sixteen_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype, out_dtype):
-    # wide outputs with 3..16 rows run on mma.sync with the contraction index permuted inside each 16-deep slab:
+@pytest.mark.parametrize("shape", [(3, 9472, 512), (8, 12288, 3072), (9, 9488, 1040), (16, 20000, 256), (16, 9600, 16), (1, 4096, 4096), (2, 528, 1040),
+                                   (16, 3072, 3072), (7, 1296, 272)])
+def test_at_most_sixteen_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype, out_dtype):
+    # 3..16 rows (1..16 for outputs too narrow for the vector kernel) run on mma.sync with the contraction index permuted inside each 16-deep slab:
     # same oracle and tolerance, ragged last column block (9488 = 296.5 x 32), same bits on every call
     m, n, k = shape
     a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype, seed=n + k)
