@@ -1405,7 +1405,7 @@ bool launch_gemv(const LaunchArgs& args, int slabs, size_t smem_bytes) {
 // reads eight cells = 128 contiguous bytes per 8-column block) and its A fragment four consecutive activations
 // of a row (8 bytes), both straight from global memory.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kWmmaMaxRows = 16;   // two 16-row tiles per warp were measured too: 33-36 us at 12288 x 3072, slower than the tensor-memory kernel (23)
+constexpr int kWmmaMaxRows = 16;   // rows of one CTA; two 16-row tiles per warp were measured too: 33-36 us at 12288 x 3072, slower than the tensor-memory kernel (23)
 constexpr int kWmmaWarps = 8;
 constexpr int kWmmaUnroll = 4;   // slabs in flight per warp with one 16-row tile (16 weight loads per lane), half as many with two
 
@@ -1432,6 +1432,7 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scale
     const int g = lane >> 2;   // fragment row (and row + 8), B column inside an 8-column block
     const int j = lane & 3;    // which four k of the slab
     const int n0 = static_cast<int>(blockIdx.x) * 32;
+    const int row0 = static_cast<int>(blockIdx.y) * 16 * kRowTiles;   // more rows than a warp's tiles: one grid row per block of them
     const int per_warp = (slabs + kWmmaWarps - 1) / kWmmaWarps;
     const int s_begin = warp * per_warp;
     const int s_end = s_begin + per_warp < slabs ? s_begin + per_warp : slabs;
@@ -1452,7 +1453,7 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scale
     for (int t = 0; t < kRowTiles; ++t) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int row = 16 * t + g + 8 * h;
+            const int row = row0 + 16 * t + g + 8 * h;
             row_live[t][h] = row < M;
             a_row[t][h] = a + static_cast<int64_t>(row_live[t][h] ? row : 0) * K + 4 * j;
         }
@@ -1530,7 +1531,7 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scale
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int row = 16 * t + g + 8 * h;
+                    const int row = row0 + 16 * t + g + 8 * h;
                     if (row >= M) continue;
                     uint32_t o = pack_out<kOutBf16>(sum[2 * h] * scale, sum[2 * h + 1] * scale);
                     if (bias != nullptr) {
@@ -1551,15 +1552,23 @@ __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2) scale
 // kernel it also wins below that: 16 rows at 4096 x 4096 11.4 against 18.3 us, 3072 x 3072 9.0 against 14.9,
 // 1280 x 1280 5.0 against 8.8, 8192 x 3072 12.1 against 18.0; level at N = 3072, K = 12288 (29 us).
 constexpr int64_t kWmmaMinN = 512;
+// 17..128 rows run as one grid row of CTAs per 16 rows (the weight comes from L2 again for every grid row) while all of
+// them are resident at once and the contraction is at most 8192 long. Measured against the skinny tcgen05 kernel:
+// 32 rows at 4096 x 4096 15.0 against 20.5 us, 64 rows at 3072 x 3072 14.7 against 16.2, 128 rows at 1280 x 1280 8.3
+// against 12.2; at N = 3072, K = 12288 it loses below 48 rows (36-39 against 30-33), hence the limit on K.
+constexpr int64_t kWmmaGridMaxK = 8192;
 inline bool wmma_eligible(const LaunchArgs& args) {
-    return args.M <= kWmmaMaxRows && args.N >= kWmmaMinN && args.K % 16 == 0 &&
+    // more than 16 rows: one grid row per 16, as long as every CTA is resident at once (three per SM) and K is short
+    const int64_t ctas = ((args.N + 31) / 32) * ((args.M + 15) / 16);
+    const bool rows_ok = args.M <= kWmmaMaxRows || (args.M <= kBlockM && ctas <= 3ll * device_info().sm_count && args.K <= kWmmaGridMaxK);
+    return rows_ok && args.N >= kWmmaMinN && args.K % 16 == 0 &&
            (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 15u) == 0 &&
            (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0;
 }
 
 bool launch_wmma(const LaunchArgs& args) {
     const int slabs = static_cast<int>(args.K / 16);
-    const unsigned grid = static_cast<unsigned>((args.N + 31) / 32);
+    const dim3 grid(static_cast<unsigned>((args.N + 31) / 32), static_cast<unsigned>((args.M + 15) / 16));
 #define FEATHER_SMM_WMMA_CASE(E5, AB, OUT)                                                                              \
     if (args.e5m2 == E5 && args.a_bf16 == AB && args.out_bf16 == OUT) {                                                  \
         scaled_mm_wmma_kernel<1, E5, AB, OUT><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(                                \

@@ -54,6 +54,7 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
 
 _WARP_MMA_MAX_M = 16     # the launcher's vector (1-2 rows, wide outputs) and warp-MMA kernels take these rows
 _WARP_MMA_MIN_N = 512
+_WARP_MMA_GRID_MAX_K = 8192
 _SKINNY_MAX_M = 128      # one row tile: the weight stream is the cost, a 64-wide tile per CTA, two CTAs per SM
 _SKINNY_WIDE_M = 64      # above this the activation re-reads of 64-wide tiles cost more than 128-wide tiles save
 _SPLIT_MAX_M = 32        # below this the fp32 partials are small against the weight and K is split as well
@@ -75,18 +76,38 @@ def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
 _WIDE_SPLIT_MIN_K_BLOCKS = 128   # 64-deep k blocks: below this the fp32 partials cost more than the idle SMs
 
 
+def warp_mma_takes(M: int, N: int, K: int) -> bool:
+    """Whether the launcher runs a 64-wide tile of this shape on the vector / warp-MMA kernels (the same rule as
+    `wmma_eligible` in `csrc/scaled_mm_sm100.cu`): at most 16 rows, or at most 128 rows as one grid row of CTAs per
+    16 rows while all of them fit on the device at once and K is at most 8192."""
+    if N < _WARP_MMA_MIN_N:
+        return False
+    if M <= _WARP_MMA_MAX_M:
+        return True
+    return M <= _SKINNY_MAX_M and -(-N // 32) * -(-M // 16) <= 3 * _SM_COUNT and K <= _WARP_MMA_GRID_MAX_K
+
+
 def select_wide_splits(M: int, N: int, K: int) -> int:
-    """K splits of the one-CTA kernel with 128 x 128 tiles for more than one row tile (1 = none). Worth it only when
-    the tiles leave at least half of the SMs idle and the contraction is long: measured 58 -> 44 us at
-    384 x 3072 x 12288 and 41 -> 34 us at 256 x 3072 x 8192 with two splits, no gain at 256 x 4096 x 4096, a loss
-    whenever the tiles alone fill the SMs or with three and more splits (the CTA that draws a tile's last ticket reads
-    every partial back through four warps)."""
-    if M <= _SKINNY_MAX_M:
-        return 1
+    """K splits of the one-CTA kernel with 128 x 128 tiles (1 = none): for shapes whose tiles leave at least half of
+    the SMs idle.
+
+    One row tile (32 < M <= 128; up to 64 rows only with K >= 8192): as many splits as keep every (tile, split) item
+    resident at once, at most four and at least eight 64-deep k blocks each. Measured against the skinny kernel at 65 and
+    128 rows: N = 3072, K = 12288 85-90 -> 29-30 us (four splits), 4096 x 4096 31-33 -> 20, 3072 x 3072 25-26 -> 18-19,
+    5120 x 5120 38-40 -> 24-25 (three), 8192 x 3072 25-26 -> 20 (two); one split too many and the items need a
+    second wave (5120 x 5120 with four: 34-35 us).
+    More row tiles (M > 128): two splits, only with K >= 8192 (58 -> 44 us at 384 x 3072 x 12288, 41 -> 34 at
+    256 x 3072 x 8192, no gain at 256 x 4096 x 4096): the CTA that draws a tile's last ticket reads every partial back
+    through four warps, and three or more splits lose more there than the extra CTAs win."""
     tiles = -(-M // 128) * -(-N // 128)
-    if tiles > _PAIR_COUNT or -(-K // 64) < _WIDE_SPLIT_MIN_K_BLOCKS:
+    k_blocks = -(-K // 64)
+    if M <= 32 or tiles > _PAIR_COUNT:
         return 1
-    return 2
+    if M > _SKINNY_MAX_M:
+        return 2 if k_blocks >= _WIDE_SPLIT_MIN_K_BLOCKS else 1
+    if M <= 64 and k_blocks < _WIDE_SPLIT_MIN_K_BLOCKS:
+        return 1
+    return max(1, min(4, _SM_COUNT // tiles, k_blocks // 8))
 
 
 _TICKETS: dict = {}
@@ -113,9 +134,15 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
     """Tile choice + launch as one opaque node, so a compiled caller does not specialize on the heuristic."""
     m, k = a.shape
     n = b_prepacked.shape[1]
-    if 0 < m <= _WARP_MMA_MAX_M and n >= _WARP_MMA_MIN_N:
-        # the launcher runs these on the vector or the warp-MMA kernel whatever the tile: no scratch to allocate
+    if 0 < m <= _SKINNY_MAX_M and warp_mma_takes(m, n, k):
+        # the launcher runs these on the vector or the warp-MMA kernel when the tile is 64 wide: no scratch to allocate
         _launch(a, b_prepacked, scale, bias, out, _TILE_N64)
+        return
+    splits = select_wide_splits(m, n, k)
+    if splits > 1:
+        tiles = -(-m // 128) * -(-n // 128)
+        partials = torch.empty(splits * tiles * 128 * 128, device=a.device, dtype=torch.float32)
+        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, 64 * tiles), splits, 128)
         return
     if 0 < m <= _SKINNY_MAX_M:
         splits = select_scaled_mm_splits(m, n, k)
@@ -129,12 +156,6 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
             return
         partials = torch.empty(splits * m * n, device=a.device, dtype=torch.float32)
         torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, n), splits)
-        return
-    splits = select_wide_splits(m, n, k)
-    if splits > 1:
-        tiles = -(-m // 128) * -(-n // 128)
-        partials = torch.empty(splits * tiles * 128 * 128, device=a.device, dtype=torch.float32)
-        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, 64 * tiles), splits, 128)
         return
     _launch(a, b_prepacked, scale, bias, out, select_scaled_mm_config(m, n, k))
 

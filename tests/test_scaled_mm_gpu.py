@@ -220,8 +220,19 @@ def test_split_k_of_the_one_cta_kernel_is_what_the_heuristic_picks_for_few_tiles
     from feather_ops_b200 import scaled_mm as sm
 
     assert sm.select_wide_splits(384, 3072, 12288) == 2
-    assert sm.select_wide_splits(4096, 12288, 3072) == 1 and sm.select_wide_splits(128, 3072, 12288) == 1
-    assert sm.select_wide_splits(256, 4096, 4096) == 1
+    assert sm.select_wide_splits(4096, 12288, 3072) == 1 and sm.select_wide_splits(16, 3072, 12288) == 1
+    assert sm.select_wide_splits(256, 4096, 4096) == 1 and sm.select_wide_splits(128, 12288, 3072) == 1
+    assert sm.select_wide_splits(128, 3072, 12288) == 4 and sm.select_wide_splits(100, 5120, 5120) == 3 and sm.select_wide_splits(48, 8192, 3072) == 1
+    assert sm.warp_mma_takes(16, 4096, 4096) and sm.warp_mma_takes(64, 3072, 3072) and not sm.warp_mma_takes(64, 12288, 3072)
+    assert not sm.warp_mma_takes(32, 3072, 12288) and not sm.warp_mma_takes(8, 256, 4096)
+    for m, n, k in [(100, 2064, 1040), (65, 528, 4096), (48, 1040, 528), (128, 1296, 272), (33, 3072, 8192 + 64)]:
+        a, packed, scale, bias = osm.make_inputs(m, n, k, torch.float16, torch.float8_e4m3fn, torch.float16, seed=m + n)
+        ref = osm.scaled_mm_f32(a, packed, scale, bias, torch.float16, b_prepacked=True)
+        dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
+        out = fo.scaled_mm_hip(*dev, torch.float16)
+        _cabi.assert_clean(STATUS)
+        _compare(out, ref, torch.float16, 1e-3)
+        assert torch.equal(out, fo.scaled_mm_hip(*dev, torch.float16))
     a, packed, scale, bias = osm.make_inputs(384, 3072, 8192, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, seed=5)
     ref = osm.scaled_mm_f32(a, packed, scale, bias, torch.bfloat16, b_prepacked=True)
     dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
@@ -253,9 +264,10 @@ def test_one_and_two_rows_take_the_vector_kernel(cuda_device, shape, a_dtype, b_
 @pytest.mark.parametrize("a_dtype,b_dtype,out_dtype", [(torch.bfloat16, torch.float8_e5m2, torch.bfloat16), (torch.float16, torch.float8_e4m3fn, torch.float16),
                                                        (torch.float16, torch.float8_e5m2, torch.bfloat16)])
 @pytest.mark.parametrize("shape", [(3, 9472, 512), (8, 12288, 3072), (9, 9488, 1040), (16, 20000, 256), (16, 9600, 16), (1, 4096, 4096), (2, 528, 1040),
-                                   (16, 3072, 3072), (7, 1296, 272)])
-def test_at_most_sixteen_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype, out_dtype):
-    # 3..16 rows (1..16 for outputs too narrow for the vector kernel) run on mma.sync with the contraction index permuted inside each 16-deep slab:
+                                   (16, 3072, 3072), (7, 1296, 272), (17, 3072, 3072), (40, 1296, 272), (128, 1040, 528), (100, 528, 8192)])
+def test_few_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype, out_dtype):
+    # 3..16 rows (1..16 for outputs too narrow for the vector kernel; up to 128 as grid rows of 16 while every CTA is
+    # resident and K <= 8192) run on mma.sync with the contraction index permuted inside each 16-deep slab:
     # same oracle and tolerance, ragged last column block (9488 = 296.5 x 32), same bits on every call
     m, n, k = shape
     a, packed, scale, bias = osm.make_inputs(m, n, k, a_dtype, b_dtype, out_dtype, seed=n + k)
