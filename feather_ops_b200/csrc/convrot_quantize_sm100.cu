@@ -23,7 +23,8 @@
 // rounded 16-bit results are transposed back so that every lane ends up with the sixteen consecutive
 // outputs it stores as one 16-byte vector. No shuffle is used for the rotation.
 //
-// The pass is HBM bound (2 bytes in, 1 byte out per element). A warp keeps its groups as packed 16-bit
+// The floor of the pass is HBM traffic (2 bytes in, 1 byte out per element); as measured it is bound by instruction
+// issue (about 26 warp instructions per value, a third of them the fp32 butterflies). A warp keeps its groups as packed 16-bit
 // values in registers between the absmax and the quantize step (up to four rounds of two groups, i.e. rows
 // up to 32768 wide with 16 warps per row); wider rows recompute the groups from global memory, which is L2
 // resident by then. One CTA owns one or more whole rows, so the only reduction is a per-row maximum across
