@@ -66,7 +66,7 @@ class ClockSampler:
     started before the warm-up, so it is already running when the timed region begins; `stop(window)` keeps the
     samples whose time stamps fall inside the window (the timed region)."""
 
-    QUERY = "timestamp,index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    QUERY = "timestamp,index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,clocks_event_reasons.active,power.draw"
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
@@ -89,11 +89,11 @@ class ClockSampler:
                 self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        clocks, max_clock, reasons = [], None, set()
+        clocks, max_clock, reasons, mask, watts = [], None, set(), 0, []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.file.read().splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) != 8 or not parts[1].isdigit() or int(parts[1]) != self.gpu_index:
+            if len(parts) != 10 or not parts[1].isdigit() or int(parts[1]) != self.gpu_index:
                 continue
             if window is not None:
                 try:
@@ -110,11 +110,17 @@ class ClockSampler:
             for name, flag in zip(names, parts[4:]):
                 if flag.lower().startswith("active"):
                     reasons.add(name)
+            try:
+                mask |= int(parts[8], 16)   # every event reason the driver reports, as its bit mask
+                watts.append(float(parts[9]))
+            except ValueError:
+                pass
         self.file.close()
         os.unlink(self.file.name)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": max_clock, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks),
+                "reasons_mask": hex(mask), "power_w": statistics.median(watts) if watts else None}
 
 
 def use_all_host_threads():
