@@ -76,7 +76,15 @@ def _scaled_mm_case(m, n, k, a_dtype, out_dtype, cold, device, label):
     acts = [torch.randn((m, k), device=device).to(a_dtype) for _ in range(sets)]
     outs = [torch.empty((m, n), device=device, dtype=out_dtype) for _ in range(sets)]
     scale = torch.tensor(0.01, device=device)
-    tile = smm.select_scaled_mm_config(m, n, k) if m > 128 else ("skinny", smm.select_scaled_mm_splits(m, n, k))
+    # what the public path picks, in its order of preference
+    if m <= 128 and smm.warp_mma_takes(m, n, k):
+        tile = ("vector or warp-MMA kernel",)
+    elif smm.select_wide_splits(m, n, k) > 1:
+        tile = ("one-CTA kernel, 128 x 128 tiles, K splits", smm.select_wide_splits(m, n, k))
+    elif m <= 128:
+        tile = ("skinny", smm.select_scaled_mm_splits(m, n, k))
+    else:
+        tile = smm.select_scaled_mm_config(m, n, k)
 
     def launch(i):
         j = i % sets

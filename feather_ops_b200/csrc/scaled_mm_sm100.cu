@@ -75,6 +75,7 @@ struct Params {
     int kb_per_split;
     float* partials;      // [splits][M][N] fp32
     uint32_t* counters;   // [tiles_m * tiles_n] tickets, zero before the launch and zero again after it
+    int single_item;      // every CTA has exactly one (tile, split) item: the whole CTA adds the partials, not four warps
 };
 
 template <int BN>
@@ -216,6 +217,7 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
+        *last_flag = 0u;
         for (int s = 0; s < kLoadStages; ++s) {
             mbar_init(&load_full[s], 1);
             mbar_init(&load_empty[s], 1);
@@ -391,7 +393,9 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     ok = false;
                     break;
                 }
-                if (*last_flag != 0u) {
+                if (p.single_item != 0) {
+                    // the whole CTA adds the partials after the role loops (below): twenty warps instead of four
+                } else if (*last_flag != 0u) {
                     // Holding the accumulator back so that the last CTA could add its own partial from tensor memory
                     // was measured slower than reading all of them from the scratch: the MMA warp waits for the buffer.
                     __threadfence();
@@ -480,6 +484,50 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 turn = turn + 1 == L::kTeams ? 0 : turn + 1;
                 slot.advance(kLoadStages);
                 operand.advance(L::kOperandStages);
+            }
+        }
+    }
+
+    if constexpr (kSplitK) {
+        if (p.single_item != 0 && splits > 1) {
+            // One item per CTA: every role loop has ended, so all warps but the first two add the partials of the tile
+            // whose last ticket this CTA drew. Four epilogue warps alone keep too few loads in flight (about 16 GB/s).
+            __syncthreads();
+            if (!guard.aborted() && *last_flag != 0u && threadIdx.x >= kFirstEpilogueWarp * 32) {
+                constexpr int kTileFloats = kBlockM * BN;
+                constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
+                const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
+                const int group = t / kBlockM;
+                const int r = t % kBlockM;
+                const int tile = static_cast<int>(blockIdx.x) / splits;
+                const int row = (tile % p.tiles_m) * kBlockM + r;
+                const int n0 = (tile / p.tiles_m) * BN;
+                const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+                uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+                __threadfence();
+                if (group < kGroups) {
+#pragma unroll 1
+                    for (int c = group; c < BN / 32; c += kGroups) {
+                        float sum[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                        for (int sp = 0; sp < splits; ++sp) {  // split order: the sum does not depend on which CTA came last
+                            const float* const src = p.partials + (static_cast<int64_t>(sp) * num_tiles + tile) * kTileFloats + r * 4;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + g) * (kBlockM * 4)));
+                                sum[4 * g] += x.x;
+                                sum[4 * g + 1] += x.y;
+                                sum[4 * g + 2] += x.z;
+                                sum[4 * g + 3] += x.w;
+                            }
+                        }
+                        uint32_t v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
+                        finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
+                    }
+                }
             }
         }
     }
@@ -1132,6 +1180,7 @@ bool launch_instance(const LaunchArgs& args) {
     if (num_items > (1 << 30)) return false;
     const int sms = device_info().sm_count;
     const int grid = num_items < sms ? static_cast<int>(num_items) : sms;
+    p.single_item = (split && num_items <= sms) ? 1 : 0;
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
 }

@@ -89,25 +89,29 @@ def warp_mma_takes(M: int, N: int, K: int) -> bool:
 
 def select_wide_splits(M: int, N: int, K: int) -> int:
     """K splits of the one-CTA kernel with 128 x 128 tiles (1 = none): for shapes whose tiles leave at least half of
-    the SMs idle.
+    the SMs idle. The splits are chosen so that every (tile, split) item is resident at once; then the whole CTA that
+    draws a tile's last ticket adds the partials (twenty warps; with more items than SMs only the four epilogue warps
+    can, and that costs more than the split wins).
 
-    One row tile (32 < M <= 128; up to 64 rows only with K >= 8192): as many splits as keep every (tile, split) item
-    resident at once, at most four and at least eight 64-deep k blocks each. Measured against the skinny kernel at 65 and
-    128 rows: N = 3072, K = 12288 85-90 -> 29-30 us (four splits), 4096 x 4096 31-33 -> 20, 3072 x 3072 25-26 -> 18-19,
-    5120 x 5120 38-40 -> 24-25 (three), 8192 x 3072 25-26 -> 20 (two); one split too many and the items need a
-    second wave (5120 x 5120 with four: 34-35 us).
-    More row tiles (M > 128): two splits, only with K >= 8192 (58 -> 44 us at 384 x 3072 x 12288, 41 -> 34 at
-    256 x 3072 x 8192, no gain at 256 x 4096 x 4096): the CTA that draws a tile's last ticket reads every partial back
-    through four warps, and three or more splits lose more there than the extra CTAs win."""
+    One row tile (33..128 rows that the warp-MMA kernel does not take): up to four splits, six with K >= 8192, at least
+    eight 64-deep k blocks each; up to 64 rows only with three splits or more (below that the skinny kernel is level).
+    Measured at 65 and 128 rows against the skinny kernel: N = 3072, K = 12288 85-90 -> 22-24 us (six splits),
+    4096 x 4096 31-33 -> 16-17 (four), 3072 x 3072 25-26 -> 15-16, 5120 x 5120 38-40 -> 19-20 (three), 8192 x 3072
+    25-26 -> 18 (two); one split too many and the items need a second wave (5120 x 5120 with four: 34-35 us).
+    More row tiles: up to three splits of at least sixteen k blocks, from K = 3072 on: 256 x 4096 x 4096 21.8 -> 19.6 us,
+    256 x 3072 x 3072 18.7 -> 16.9, 256 x 3072 x 8192 41 -> 25, 384 x 3072 x 12288 58 -> 42."""
     tiles = -(-M // 128) * -(-N // 128)
     k_blocks = -(-K // 64)
     if M <= 32 or tiles > _PAIR_COUNT:
         return 1
     if M > _SKINNY_MAX_M:
-        return 2 if k_blocks >= _WIDE_SPLIT_MIN_K_BLOCKS else 1
-    if M <= 64 and k_blocks < _WIDE_SPLIT_MIN_K_BLOCKS:
+        if k_blocks < 48:
+            return 1
+        return max(1, min(3, _SM_COUNT // tiles, k_blocks // 16))
+    splits = max(1, min(6 if k_blocks >= _WIDE_SPLIT_MIN_K_BLOCKS else 4, _SM_COUNT // tiles, k_blocks // 8))
+    if M <= 64 and splits < 3:
         return 1
-    return max(1, min(4, _SM_COUNT // tiles, k_blocks // 8))
+    return splits
 
 
 _TICKETS: dict = {}

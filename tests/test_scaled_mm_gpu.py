@@ -219,10 +219,11 @@ def test_split_k_of_the_one_cta_kernel_is_what_the_heuristic_picks_for_few_tiles
     import feather_ops_b200 as fo
     from feather_ops_b200 import scaled_mm as sm
 
-    assert sm.select_wide_splits(384, 3072, 12288) == 2
-    assert sm.select_wide_splits(4096, 12288, 3072) == 1 and sm.select_wide_splits(16, 3072, 12288) == 1
-    assert sm.select_wide_splits(256, 4096, 4096) == 1 and sm.select_wide_splits(128, 12288, 3072) == 1
-    assert sm.select_wide_splits(128, 3072, 12288) == 4 and sm.select_wide_splits(100, 5120, 5120) == 3 and sm.select_wide_splits(48, 8192, 3072) == 1
+    assert sm.select_wide_splits(384, 3072, 12288) == 2 and sm.select_wide_splits(256, 4096, 4096) == 2 and sm.select_wide_splits(256, 3072, 8192) == 3
+    assert sm.select_wide_splits(4096, 12288, 3072) == 1 and sm.select_wide_splits(16, 3072, 12288) == 1 and sm.select_wide_splits(192, 2560, 2560) == 1
+    assert sm.select_wide_splits(512, 2560, 2560) == 1 and sm.select_wide_splits(128, 12288, 3072) == 1
+    assert sm.select_wide_splits(128, 3072, 12288) == 6 and sm.select_wide_splits(100, 5120, 5120) == 3 and sm.select_wide_splits(128, 4096, 4096) == 4
+    assert sm.select_wide_splits(48, 8192, 3072) == 1 and sm.select_wide_splits(64, 5120, 5120) == 3
     assert sm.warp_mma_takes(16, 4096, 4096) and sm.warp_mma_takes(64, 3072, 3072) and not sm.warp_mma_takes(64, 12288, 3072)
     assert not sm.warp_mma_takes(32, 3072, 12288) and not sm.warp_mma_takes(8, 256, 4096)
     for m, n, k in [(100, 2064, 1040), (65, 528, 4096), (48, 1040, 528), (128, 1296, 272), (33, 3072, 8192 + 64)]:
