@@ -81,6 +81,8 @@ def _scaled_mm_case(m, n, k, a_dtype, out_dtype, cold, device, label):
         tile = ("vector or warp-MMA kernel",)
     elif smm.select_wide_splits(m, n, k) > 1:
         tile = ("one-CTA kernel, 128 x 128 tiles, K splits", smm.select_wide_splits(m, n, k))
+    elif 64 < m <= 128 and -(-n // 128) >= 74:
+        tile = smm._TILE_N128
     elif m <= 128:
         tile = ("skinny", smm.select_scaled_mm_splits(m, n, k))
     else:
