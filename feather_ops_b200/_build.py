@@ -32,6 +32,7 @@ KERNEL_SOURCES = [
     "convrot_quantize_sm100.cu",
     "int8_mm_sm100.cu",
     "conv3x3_sm100.cu",
+    "selftest_sm100.cu",
 ]
 NVCC_FLAGS = [
     "-gencode",

@@ -47,6 +47,7 @@ PROTOTYPES = {
         [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
     ),
     "feather_conv3x3_status": (_c_int, [_ptr]),
+    "feather_selftest_wait_runs_out": (_c_int, [ctypes.c_longlong, _ptr, _ptr, _ptr]),
 }
 
 _lib = None
@@ -74,4 +75,9 @@ def read_status(symbol: str) -> tuple[int, int]:
     rc = getattr(load(), symbol)(out)
     if rc != 0:
         raise RuntimeError(f"{symbol} failed (a CUDA error is pending on this device)")
+    if symbol == "feather_scaled_mm_status" and out[0] != 0:
+        # a split-K launch that gave up may have left its tickets non-zero: never reuse them
+        from . import scaled_mm
+
+        scaled_mm.reset_split_k_state()
     return int(out[0]), int(out[1])

@@ -693,14 +693,11 @@ int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B,
     p.idesc = make_idesc(kAccF32, kBf16 ? kFmtBF16 : kFmtF16, kBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, 2 * kPairBN);
     p.pairs = 1;
 
-    static bool configured[64] = {};
-    static int resident_pairs[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (!configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 1;
-        // a persistent grid must be resident at once: a pair needs both SMs of a TPC
+    // once per device: the shared-memory limit and how many CTA pairs fit at once (a persistent grid must be resident as a
+    // whole, and a pair needs both SMs of a TPC)
+    static PerDeviceState resident_pairs;
+    const int pairs = resident_pairs.get([&] {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 0;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
         config.blockDim = dim3(kThreads);
@@ -717,16 +714,15 @@ int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B,
             (void)cudaGetLastError();
             clusters = device_info().sm_count / 2;
         }
-        resident_pairs[dev] = clusters;
-        configured[dev] = true;
-    }
+        return clusters;
+    });
+    if (pairs <= 0) return 1;
 
     CUtensorMap map_w;
     if (!encode_weight_map(&map_w, wp, C_out, p.groups)) return 1;
     const int64_t tiles_m = (C_out + 2 * kBlockM - 1) / (2 * kBlockM);
     const int64_t num_tiles = static_cast<int64_t>(B) * tiles_m * ((H + 1) / 2) * ((W + kPairBN - 1) / kPairBN);
     if (num_tiles > (1ll << 30)) return 1;
-    const int pairs = resident_pairs[dev];
     const int grid = 2 * static_cast<int>(num_tiles < pairs ? num_tiles : pairs);
     kernel<<<grid, kThreads, kPairSmemBytes, stream>>>(map_w, p);
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
@@ -758,12 +754,9 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
     if (2 * (rows + 2) * per_row > kMaxItems * kTeamWarps * 32) return 1;
 
     const int smem_bytes = kStages * (kWeightStageBytes + p.act_stage_bytes) + (3 * kStages + 4) * 8 + 16 + 1024;
-    static int configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && configured[dev] < smem_bytes) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 1;
-        configured[dev] = smem_bytes;
+    static PerDeviceState smem_limit;
+    if (!smem_limit.at_least(smem_bytes, [&](int need) { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, need) == cudaSuccess; })) {
+        return 1;
     }
 
     CUtensorMap map_w;
@@ -774,6 +767,12 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
     const int grid = num_tiles < sms ? static_cast<int>(num_tiles) : sms;
     kernel<<<grid, kThreads, smem_bytes, stream>>>(map_w, p);
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+// FEATHER_CONV_PAIR_OFF=1 keeps every shape on the one-CTA kernel (A/B measurements). Read once per process.
+inline bool pair_off() {
+    static const bool off = env_switch("FEATHER_CONV_PAIR_OFF");
+    return off;
 }
 
 }  // namespace conv
@@ -803,7 +802,7 @@ extern "C" int feather_conv3x3_launch(const void* x, const void* wp, const void*
     const void* const bias_ptr = has_bias ? bias : nullptr;
     // two rows of 128 pixels and more than one 128-channel tile: the CTA-pair kernel computes the same tile
     // shape (same accumulation order) with two SMs sharing the pixels
-    if (rows == 2 && bn == 128 && C_out > conv::kBlockM && std::getenv("FEATHER_CONV_PAIR_OFF") == nullptr) {
+    if (rows == 2 && bn == 128 && C_out > conv::kBlockM && !conv::pair_off()) {
         return is_bf16 != 0 ? conv::launch_pair<true>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, stream)
                             : conv::launch_pair<false>(x, wp, bias_ptr, y, B, C_in, C_out, H, W, stream);
     }

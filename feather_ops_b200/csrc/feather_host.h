@@ -8,6 +8,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace feather {
@@ -70,6 +71,47 @@ inline const DeviceInfo& device_info() {
         cudaDeviceGetAttribute(&info[dev].max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     });
     return info[dev];
+}
+
+// State that a launcher keeps per device and kernel (the raised shared-memory limit, the number of resident CTA
+// pairs): looked up under a lock, so launchers may be called from several host threads at once.
+class PerDeviceState {
+public:
+    // The remembered value for the current device; `setup()` computes it on first use and returns a positive
+    // number (1 when there is nothing else to remember) or 0 on failure, in which case the next call tries again.
+    template <class Setup>
+    int get(Setup&& setup) {
+        const int dev = current_device();
+        std::lock_guard<std::mutex> hold(lock_);
+        if (value_[dev] == 0) value_[dev] = setup();
+        return value_[dev];
+    }
+
+    // For a limit that grows with the request: `raise(need)` is called when `need` exceeds what was set before.
+    template <class Raise>
+    bool at_least(int need, Raise&& raise) {
+        const int dev = current_device();
+        std::lock_guard<std::mutex> hold(lock_);
+        if (value_[dev] >= need) return true;
+        if (!raise(need)) return false;
+        value_[dev] = need;
+        return true;
+    }
+
+private:
+    static int current_device() {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        return (dev < 0 || dev >= 64) ? 0 : dev;
+    }
+    std::mutex lock_;
+    int value_[64] = {};
+};
+
+// An A/B switch from the environment: set to anything but "" or "0". Callers cache the answer (read once per process).
+inline bool env_switch(const char* name) {
+    const char* v = std::getenv(name);
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
 }
 
 }  // namespace feather

@@ -779,13 +779,8 @@ template <int BN, bool kTransposedB, bool kOutBf16>
 bool launch_instance(const LaunchArgs& args) {
     using L = Smem<BN>;
     auto* kernel = &int8_mm_kernel<BN, kTransposedB, kOutBf16>;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
-        configured[dev] = true;
-    }
+    static PerDeviceState configured;
+    if (configured.get([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) == cudaSuccess ? 1 : 0; }) == 0) return false;
     CUtensorMap map_a;
     const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(args.K)};
@@ -817,14 +812,11 @@ template <bool kTransposedB, bool kOutBf16>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
     auto* kernel = &int8_mm_pair_kernel<kTransposedB, kOutBf16>;
-    static bool configured[64] = {};
-    static int resident_pairs[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (!configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
-        // a persistent grid must fit at once: pairs need both SMs of a TPC
+    // once per device: the shared-memory limit and how many CTA pairs fit at once (a persistent grid must be resident as a
+    // whole, and a pair needs both SMs of a TPC)
+    static PerDeviceState resident_pairs;
+    const int pairs = resident_pairs.get([&] {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return 0;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
         config.blockDim = dim3(kPairThreads);
@@ -841,9 +833,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
             (void)cudaGetLastError();
             clusters = device_info().sm_count / 2;
         }
-        resident_pairs[dev] = clusters;
-        configured[dev] = true;
-    }
+        return clusters;
+    });
+    if (pairs <= 0) return false;
     CUtensorMap map_a;
     const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
     const uint64_t strides[1] = {static_cast<uint64_t>(args.K)};
@@ -882,7 +874,6 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
     p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int pairs = resident_pairs[dev];
     const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
     kernel<<<grid, kPairThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
@@ -1043,10 +1034,16 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
 // 8192 columns: measured 6.9-10.3 against 13.7-14.3 us at 3072 x 3072, 18.4-30.4 against 36 at 3072 x 12288, but 15.7-18.6
 // against 15.1 at 12288 x 3072, where the pair kernel has 48 tiles to spread), operands aligned for its 8-byte
 // activation loads, dword weight loads and 4-byte stores.
+// FEATHER_INT8_WMMA_OFF=1 keeps few-row problems on the tcgen05 kernels (A/B measurements). Read once per process.
+inline bool wmma_off() {
+    static const bool off = env_switch("FEATHER_INT8_WMMA_OFF");
+    return off;
+}
+
 bool wmma_eligible(const LaunchArgs& args) {
     return !args.transposed_b && args.M <= kWmmaMaxRows && (args.M <= 16 || args.N_out < kWmmaTwoTileMaxN) && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
            (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 3u) == 0 &&
-           (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0 && std::getenv("FEATHER_INT8_WMMA_OFF") == nullptr;
+           (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0 && !wmma_off();
 }
 
 bool launch_wmma(const LaunchArgs& args) {

@@ -1128,12 +1128,9 @@ bool launch_instance(const LaunchArgs& args) {
     using L = Smem<BN>;
     const bool split = args.splits > 1 && args.partials != nullptr && args.counters != nullptr && effective_splits(args.K, args.splits) > 1;
     auto* kernel = split ? &scaled_mm_kernel<BN, kE5M2, kOperandBf16, kOutBf16, true> : &scaled_mm_kernel<BN, kE5M2, kOperandBf16, kOutBf16, false>;
-    static bool configured[64][2] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev][split ? 1 : 0]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
-        configured[dev][split ? 1 : 0] = true;
+    static PerDeviceState configured[2];
+    if (configured[split ? 1 : 0].get([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) == cudaSuccess ? 1 : 0; }) == 0) {
+        return false;
     }
 
     CUtensorMap map_a, map_b;
@@ -1202,17 +1199,42 @@ inline bool pair_kernel_enabled() {
     return enabled;
 }
 
+// FEATHER_SKINNY_WMMA_OFF=1 keeps few-row problems on the tcgen05 kernel with 64-wide tiles (A/B measurements).
+// Read once per process.
+inline bool skinny_wmma_off() {
+    static const bool off = env_switch("FEATHER_SKINNY_WMMA_OFF");
+    return off;
+}
+
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
     auto* kernel = &scaled_mm_pair_kernel<kE5M2, kOperandBf16, kOutBf16>;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return false;
-        configured[dev] = true;
-    }
+    // Set-up once per device: the shared-memory limit, and how many CTA pairs can be resident at once. A persistent
+    // grid must not exceed that: pairs need both SMs of a TPC, and parts with an odd number of enabled SMs in some
+    // TPCs hold fewer pairs than sm_count / 2.
+    static PerDeviceState resident_pairs;
+    const int pairs = resident_pairs.get([&] {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
+        config.blockDim = dim3(kThreads);
+        config.dynamicSmemBytes = L::kDynamic;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs = attr;
+        config.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
+            (void)cudaGetLastError();
+            clusters = device_info().sm_count / 2;
+        }
+        return clusters;
+    });
+    if (pairs <= 0) return false;
     CUtensorMap map_a, map_b;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
@@ -1243,30 +1265,6 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
     const int num_tiles = p.tiles_m * p.tiles_n;
-    // A persistent grid must not exceed what can be resident at once: CTA pairs need both SMs of a TPC, and
-    // parts with an odd number of enabled SMs in some TPCs hold fewer pairs than sm_count / 2.
-    static int resident_pairs[64] = {};
-    if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
-        config.blockDim = dim3(kThreads);
-        config.dynamicSmemBytes = L::kDynamic;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        config.attrs = attr;
-        config.numAttrs = 1;
-        int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters <= 0) {
-            (void)cudaGetLastError();
-            clusters = device_info().sm_count / 2;
-        }
-        resident_pairs[dev] = clusters;
-        if (getenv("FEATHER_DEBUG") != nullptr) fprintf(stderr, "feather: %d CTA pairs resident per launch\n", clusters);
-    }
-    const int pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : device_info().sm_count / 2;
     const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
@@ -1406,13 +1404,8 @@ __global__ void __launch_bounds__(32 * kGemvWarps) scaled_mm_gemv_kernel(const u
 template <int kRows, bool kE5M2, bool kActBf16, bool kOutBf16>
 bool launch_gemv_rows(const LaunchArgs& args, int slabs, size_t smem_bytes) {
     auto* kernel = &scaled_mm_gemv_kernel<kRows, kE5M2, kActBf16, kOutBf16>;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit) != cudaSuccess) return false;
-        configured[dev] = true;
-    }
+    static PerDeviceState configured;
+    if (configured.get([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit) == cudaSuccess ? 1 : 0; }) == 0) return false;
     const unsigned grid = static_cast<unsigned>((args.N + 31) / 32);
     kernel<<<grid, 32 * kGemvWarps, smem_bytes, args.stream>>>(args.a, reinterpret_cast<const uint4*>(args.b), args.scale, args.bias, args.c,
                                                                  static_cast<int>(args.N), static_cast<int>(args.K), slabs);
@@ -1644,13 +1637,8 @@ bool launch_wmma(const LaunchArgs& args) {
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
 bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
     auto* kernel = &scaled_mm_skinny_kernel<kE5M2, kOperandBf16, kOutBf16>;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBudget) != cudaSuccess) return false;
-        configured[dev] = true;
-    }
+    static PerDeviceState configured;
+    if (configured.get([&] { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBudget) == cudaSuccess ? 1 : 0; }) == 0) return false;
     CUtensorMap map_a, map_b;
     const uint32_t a_rows = static_cast<uint32_t>((args.M + 7) / 8 * 8);
     const uint32_t a_slot_bytes = a_rows * kBlockK * 2;
@@ -1703,14 +1691,20 @@ bool launch_skinny_instance(const LaunchArgs& args, int splits, float* partials,
     return cudaGetLastError() == cudaSuccess;
 }
 
+// A caller that asks for a K split (more than one effective split, with scratch) gets the tcgen05 kernel that
+// splits K: the scratch and the tickets are then really used, whatever the shape. Without a split the fastest
+// kernel for the shape runs: the vector kernel for one or two rows of a wide output, the warp-MMA kernel for few
+// rows, else the tcgen05 kernel with 64-wide tiles.
 bool launch_skinny(const LaunchArgs& args, int splits, float* partials, uint32_t* counters) {
     const bool operand_bf16 = args.a_bf16;
-    {
+    const bool split_requested = effective_splits(args.K, splits) > 1 && partials != nullptr && counters != nullptr;
+    if (!split_requested) {
         int slabs = 0;
         size_t smem_bytes = 0;
         if (gemv_eligible(args, &slabs, &smem_bytes)) return launch_gemv(args, slabs, smem_bytes);
+        if (wmma_eligible(args) && !skinny_wmma_off()) return launch_wmma(args);
+        splits = 1;
     }
-    if (wmma_eligible(args) && std::getenv("FEATHER_SKINNY_WMMA_OFF") == nullptr) return launch_wmma(args);
 #define FEATHER_SMM_SKINNY_CASE(E5, OB, OUT)                               \
     if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
         return launch_skinny_instance<E5, OB, OUT>(args, splits, partials, counters); \

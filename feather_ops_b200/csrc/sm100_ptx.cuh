@@ -96,6 +96,11 @@ struct WaitGuard {
     // Wait for the phase with `parity` to complete. False means the CTA is aborting (this wait ran out,
     // or another one did): the caller must stop touching the pipeline and fall through to the teardown.
     __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t site, uint32_t tag = 0) const {
+        return wait_at_most(bar, parity, site, tag, kWaitLimitCycles);
+    }
+
+    // The same wait with the limit given by the caller (the kernels use `wait`; the self-test passes a short limit).
+    __device__ __forceinline__ bool wait_at_most(uint64_t* bar, uint32_t parity, uint32_t site, uint32_t tag, long long limit_cycles) const {
         if (mbar_try_wait(bar, parity)) return true;
         const long long start = clock64();
         uint32_t polls = 0;
@@ -103,7 +108,7 @@ struct WaitGuard {
             if (mbar_try_wait(bar, parity)) return true;
             if ((++polls & 0x3fu) == 0u) {
                 if (aborted()) return false;
-                if (clock64() - start > kWaitLimitCycles) {
+                if (clock64() - start > limit_cycles) {
                     give_up(site, tag);
                     return false;
                 }

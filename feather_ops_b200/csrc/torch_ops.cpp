@@ -137,10 +137,12 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
     STD_TORCH_CHECK(counters.numel() >= tickets, "counters must have one element per tile");
     if (scale.has_value()) {
         STD_TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == ScalarType::Float && scale->numel() == 1, "scale must be one float32 on the device");
+        STD_TORCH_CHECK(scale->get_device_index() == device, "scale must be on the same device as a");
     }
     if (bias.has_value()) {
         STD_TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == c.scalar_type() && bias->numel() == N && bias->is_contiguous(),
                         "bias must be N contiguous elements of c's dtype");
+        STD_TORCH_CHECK(bias->get_device_index() == device, "bias must be on the same device as a");
     }
     STD_TORCH_CHECK(aligned16(a.const_data_ptr()) && aligned16(b_prepacked.const_data_ptr()) && aligned16(c.mutable_data_ptr()) &&
                         aligned16(partials.mutable_data_ptr()),
@@ -194,15 +196,18 @@ void int8_scaled_mm(const Tensor& a, const Tensor& b_prepacked, const Tensor& a_
     STD_TORCH_CHECK(c.stride(0) == N_out && c.stride(1) == 1, "c must be contiguous");
     STD_TORCH_CHECK(b_prepacked.is_contiguous(), "b_prepacked must be contiguous");
     STD_TORCH_CHECK(a_scale.is_cuda() && a_scale.scalar_type() == ScalarType::Float, "a_scale must be float32");
+    STD_TORCH_CHECK(a_scale.get_device_index() == device, "a_scale must be on the same device as a");
     STD_TORCH_CHECK(a_scale.numel() == M, "a_scale must have M elements");
     STD_TORCH_CHECK(a_scale.is_contiguous(), "a_scale must be contiguous");
     if (b_scale.has_value()) {
         STD_TORCH_CHECK(b_scale->is_cuda() && b_scale->scalar_type() == ScalarType::Float, "b_scale must be float32");
+        STD_TORCH_CHECK(b_scale->get_device_index() == device, "b_scale must be on the same device as a");
         STD_TORCH_CHECK(b_scale->numel() == N_out, "b_scale must have N elements");
         STD_TORCH_CHECK(b_scale->is_contiguous(), "b_scale must be contiguous");
     }
     if (bias.has_value()) {
         STD_TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == c.scalar_type(), "bias must have the same dtype as c");
+        STD_TORCH_CHECK(bias->get_device_index() == device, "bias must be on the same device as a");
         STD_TORCH_CHECK(bias->numel() == N_out, "bias must have N elements");
         STD_TORCH_CHECK(bias->is_contiguous(), "bias must be contiguous");
     }
@@ -281,6 +286,8 @@ void conv2d_3x3(const Tensor& x, const Tensor& w_prepacked, const std::optional<
     const int64_t H = x.size(2);
     const int64_t W = x.size(3);
     const int64_t C_out = out.size(1);
+    constexpr int64_t kIntMax = 2147483647;
+    STD_TORCH_CHECK(B <= kIntMax && C_in <= kIntMax && C_out <= kIntMax && H <= kIntMax && W <= kIntMax, "conv2d_3x3: a dimension exceeds the 32-bit range");
     STD_TORCH_CHECK(out.size(0) == B && out.size(2) == H && out.size(3) == W, "out must be [B, C_out, H, W]");
     STD_TORCH_CHECK(w_prepacked.size(1) == C_out, "w_prepacked.shape[1] must equal C_out");
     STD_TORCH_CHECK(w_prepacked.size(2) == 8, "w_prepacked.shape[2] must be 8");

@@ -13,6 +13,7 @@ Function names, arguments and error behaviour follow the reference module (`feat
 import torch
 from torch.library import custom_op
 
+from .scaled_mm import sm_count
 from .tiles import INT8_UMMA
 
 CONVROT_GROUP = 256  # the quantizer implements the regular Hadamard over 256 channels only
@@ -20,8 +21,6 @@ CONVROT_GROUP = 256  # the quantizer implements the regular Hadamard over 256 ch
 _TILE_N256 = (4, 4, 2, 4, 4)
 _TILE_N128 = (2, 4, 2, 4, 2)
 _TILE_N64 = (2, 2, 2, 2, 2)
-_SM_COUNT = 148
-_PAIR_COUNT = _SM_COUNT // 2
 # Measured time of one wave of tiles per 128-deep k block, in microseconds (N = K = 3072 sweeps over M): 256-wide
 # tiles run as 256 x 256 tiles on CTA pairs (also for a single row tile), the others as 128-row tiles on single
 # CTAs, whose weight re-layout is much slower.
@@ -35,12 +34,13 @@ def select_int8_config(M: int, N: int, K: int, transposed_b: bool):
     waves of tiles times the measured cost of a wave, CTA pairs (74) for the 256-wide tile, single CTAs (148)
     for the others."""
     out = K if transposed_b else N
+    sms = sm_count()
     best = None
     for width in (256, 128, 64):
         if width == 256:
-            cost = -(-(-(-M // 256) * -(-out // 256)) // _PAIR_COUNT) * _WAVE_COST_US[256]
+            cost = -(-(-(-M // 256) * -(-out // 256)) // (sms // 2)) * _WAVE_COST_US[256]
         else:
-            cost = -(-(-(-M // 128) * -(-out // width)) // _SM_COUNT) * _WAVE_COST_US[width]
+            cost = -(-(-(-M // 128) * -(-out // width)) // sms) * _WAVE_COST_US[width]
         if best is None or cost < best[0] - 1e-9:
             best = (cost, width)
     return _TILE_OF_WIDTH[best[1]]

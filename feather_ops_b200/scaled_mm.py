@@ -17,8 +17,20 @@ _TILE_N256 = (1, 8, 4, 8, 2, 0)
 _TILE_N128 = (2, 2, 2, 4, 4, 0)
 _TILE_N64 = (1, 2, 4, 1, 2, 1)
 
-_SM_COUNT = 148
-_PAIR_COUNT = _SM_COUNT // 2
+_DEFAULT_SM_COUNT = 148   # a B200; used only when no CUDA device is visible (the heuristics are also exercised on CPU)
+_SM_COUNTS: dict = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current CUDA device (the number the launchers size their grids by)."""
+    if not torch.cuda.is_available():
+        return _DEFAULT_SM_COUNT
+    index = torch.cuda.current_device()
+    if index not in _SM_COUNTS:
+        _SM_COUNTS[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _SM_COUNTS[index]
+
+
 # Measured time of one wave of tiles per 64-deep k block, in microseconds (M > 128, N = 12288, K = 3072 sweeps):
 # 256-wide tiles run as 256 x 256 tiles on CTA pairs, the narrower ones as 128-row tiles on single CTAs.
 _WAVE_COST_US = {256: 0.40, 128: 0.42, 64: 0.35}
@@ -37,14 +49,15 @@ def select_scaled_mm_config(M: int, N: int, K: int, a_dtype=torch.float16, b_dty
     more SMs.
     """
     del a_dtype, b_dtype, out_dtype
+    sms = sm_count()
     k_blocks = -(-K // 64)
     best = None
     for width in (256, 128, 64):
         if width == 256 and M > 128:
-            waves = -(-(-(-M // 256) * -(-N // 256)) // _PAIR_COUNT)
+            waves = -(-(-(-M // 256) * -(-N // 256)) // (sms // 2))
             fixed = _FIXED_COST_US[256]
         else:
-            waves = -(-(-(-M // 128) * -(-N // width)) // _SM_COUNT)
+            waves = -(-(-(-M // 128) * -(-N // width)) // sms)
             fixed = _FIXED_COST_US[width if width != 256 else 128]
         cost = fixed + waves * k_blocks * _WAVE_COST_US[width] * (1.4 if width == 256 and M <= 128 else 1.0)
         if best is None or cost < best[0] - 1e-9:
@@ -58,7 +71,6 @@ _WARP_MMA_GRID_MAX_K = 8192
 _SKINNY_MAX_M = 128      # one row tile: the weight stream is the cost, a 64-wide tile per CTA, two CTAs per SM
 _SKINNY_WIDE_M = 64      # above this the activation re-reads of 64-wide tiles cost more than 128-wide tiles save
 _SPLIT_MAX_M = 32        # below this the fp32 partials are small against the weight and K is split as well
-_RESIDENT_SKINNY_CTAS = 2 * _SM_COUNT
 
 
 def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
@@ -70,7 +82,7 @@ def select_scaled_mm_splits(M: int, N: int, K: int) -> int:
         return 1
     tiles = -(-N // 64)
     k_blocks = -(-K // 64)
-    return max(1, min(4, _RESIDENT_SKINNY_CTAS // tiles, k_blocks // 16))
+    return max(1, min(4, 2 * sm_count() // tiles, k_blocks // 16))
 
 
 _WIDE_SPLIT_MIN_K_BLOCKS = 128   # 64-deep k blocks: below this the fp32 partials cost more than the idle SMs
@@ -84,7 +96,7 @@ def warp_mma_takes(M: int, N: int, K: int) -> bool:
         return False
     if M <= _WARP_MMA_MAX_M:
         return True
-    return M <= _SKINNY_MAX_M and -(-N // 32) * -(-M // 16) <= 3 * _SM_COUNT and K <= _WARP_MMA_GRID_MAX_K
+    return M <= _SKINNY_MAX_M and -(-N // 32) * -(-M // 16) <= 3 * sm_count() and K <= _WARP_MMA_GRID_MAX_K
 
 
 def select_wide_splits(M: int, N: int, K: int) -> int:
@@ -102,13 +114,14 @@ def select_wide_splits(M: int, N: int, K: int) -> int:
     256 x 3072 x 3072 18.7 -> 16.9, 256 x 3072 x 8192 41 -> 25, 384 x 3072 x 12288 58 -> 42."""
     tiles = -(-M // 128) * -(-N // 128)
     k_blocks = -(-K // 64)
-    if M <= 32 or tiles > _PAIR_COUNT:
+    sms = sm_count()
+    if M <= 32 or tiles > sms // 2:
         return 1
     if M > _SKINNY_MAX_M:
         if k_blocks < 48:
             return 1
-        return max(1, min(3, _SM_COUNT // tiles, k_blocks // 16))
-    splits = max(1, min(6 if k_blocks >= _WIDE_SPLIT_MIN_K_BLOCKS else 4, _SM_COUNT // tiles, k_blocks // 8))
+        return max(1, min(3, sms // tiles, k_blocks // 16))
+    splits = max(1, min(6 if k_blocks >= _WIDE_SPLIT_MIN_K_BLOCKS else 4, sms // tiles, k_blocks // 8))
     if M <= 64 and splits < 3:
         return 1
     return splits
@@ -127,6 +140,13 @@ def _ticket_counters(device: torch.device, n: int) -> torch.Tensor:
         buf = torch.zeros(max(need, 1024), device=device, dtype=torch.int32)
         _TICKETS[key] = buf
     return buf
+
+
+def reset_split_k_state() -> None:
+    """Forget the cached ticket counters. A split-K launch whose bounded device wait ran out (reported by
+    `feather_scaled_mm_status`) can leave its tickets non-zero; after such a failure the next launch must start
+    from fresh zeroed counters, which this guarantees. `_lib.read_status` calls it when it sees a failure."""
+    _TICKETS.clear()
 
 
 def _launch(a, b_prepacked, scale, bias, out, tile) -> None:
@@ -150,7 +170,7 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
         return
     if 0 < m <= _SKINNY_MAX_M:
         splits = select_scaled_mm_splits(m, n, k)
-        if m > _SKINNY_WIDE_M and -(-n // 128) >= _PAIR_COUNT:
+        if m > _SKINNY_WIDE_M and -(-n // 128) >= sm_count() // 2:
             # enough 128-wide tiles to occupy half the SMs: every activation byte is fetched half as often
             _launch(a, b_prepacked, scale, bias, out, _TILE_N128)
             return

@@ -2,8 +2,22 @@
 
 The path shards on the token dimension M: every rank multiplies its own rows of A against a replicated
 prepacked weight and owns the same rows of C, with no collective. The optional N-sharded variant keeps one
-column slab of the weight per rank and all-gathers the output slabs with one NCCL collective. The compute
-function is a parameter so the partition logic can be exercised on CPU ranks (gloo) with a stand-in.
+column slab of the weight per rank and all-gathers the output slabs over NVLink with NCCL (plain NCCL
+collectives on this rank's own buffers; no kernel here reads a peer's memory). The compute function is a
+parameter so the partition logic can be exercised on CPU ranks (gloo) with a stand-in.
+
+N-sharded variants, all returning the same numbers:
+
+* `layout="row_major"`, `chunks=1`: local product, one blocking all-gather into `[world, M, N / world]`, one
+  permute copy to row-major `[M, N]`.
+* `layout="row_major"`, `chunks > 1`: the rows are cut into chunks; the all-gather of chunk i runs on the
+  collective's own stream while the compute stream multiplies chunk i + 1 and permutes chunk i - 1. The
+  all-gather moves `(world - 1) / world` of the output through every GPU's links and is several times longer
+  than the product, so the pipeline hides the product and the copies behind it, not the other way round.
+* `layout="slabs"`: the result stays `[world, M, N / world]` (slab g holds columns `[g N / world, (g + 1) N / world)`),
+  for callers that can consume it that way. Every rank computes straight into its own slab and the all-gather
+  runs in place, so there is no copy at all; with `chunks > 1` each chunk's blocks are gathered into their final
+  position.
 """
 
 from collections.abc import Callable
@@ -39,12 +53,86 @@ def scaled_mm_token_sharded(a: torch.Tensor, b_prepacked, scale, bias, out_dtype
     return matmul(a[start:stop].contiguous(), b_prepacked, scale, bias, out_dtype)
 
 
-def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, matmul: Callable, group=None) -> torch.Tensor:
-    """Full `C[M, N]` on every rank from per-rank weight slabs: local product, then one all-gather of the
-    `[M, N / world]` slabs (`[world, M, N / world]` on the wire, permuted to row-major `[M, N]` afterwards)."""
+def _kernel_into(a, b_slab, scale, bias_slab, out) -> None:
+    """The library's own operator writing into a caller-provided output (tile and split choice included)."""
+    from .scaled_mm import _scaled_mm_auto
+
+    _scaled_mm_auto(a, b_slab, scale, bias_slab, out)
+
+
+def row_chunks(rows: int, chunks: int) -> list[tuple[int, int]]:
+    """`chunks` contiguous row ranges covering `rows` (fewer when there are fewer rows), balanced to within one row."""
+    chunks = max(1, min(chunks, rows)) if rows > 0 else 1
+    return [token_shard(rows, i, chunks) for i in range(chunks)]
+
+
+def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, matmul: Callable | None = None, group=None, *, chunks: int = 1,
+                        layout: str = "row_major", matmul_into: Callable | None = None) -> torch.Tensor:
+    """Full `C` on every rank from per-rank weight slabs: local product, then an all-gather of the `[M, N / world]` slabs.
+
+    `matmul(a, b, scale, bias, out_dtype) -> Tensor` or `matmul_into(a, b, scale, bias, out) -> None` computes the local
+    product (default: this library's kernel, writing in place). `layout` is `"row_major"` (`[M, N]`) or `"slabs"`
+    (`[world, M, N / world]`); `chunks > 1` pipelines the all-gather of one row chunk against the product of the next.
+    """
+    if layout not in ("row_major", "slabs"):
+        raise ValueError(f"layout must be 'row_major' or 'slabs', got {layout!r}")
     world = dist.get_world_size(group)
-    local = matmul(a, b_slab, scale, bias_slab, out_dtype).contiguous()
-    rows, width = local.shape
-    gathered = torch.empty((world * rows, width), device=local.device, dtype=local.dtype)
-    dist.all_gather_into_tensor(gathered, local, group=group)
-    return gathered.view(world, rows, width).permute(1, 0, 2).reshape(rows, world * width)
+    rank = dist.get_rank(group)
+    rows = a.shape[0]
+    width = b_slab.shape[1]
+    if matmul is None and matmul_into is None:
+        matmul_into = _kernel_into
+
+    def compute(a_rows: torch.Tensor, out: torch.Tensor) -> None:
+        if matmul_into is not None:
+            matmul_into(a_rows, b_slab, scale, bias_slab, out)
+        else:
+            out.copy_(matmul(a_rows, b_slab, scale, bias_slab, out_dtype))
+
+    spans = row_chunks(rows, chunks)
+    if layout == "slabs":
+        slabs = torch.empty((world, rows, width), device=a.device, dtype=out_dtype)
+        if len(spans) == 1:
+            # the local product lands in this rank's slab and the all-gather runs in place: no copy anywhere
+            compute(a, slabs[rank])
+            # NCCL gathers in place when the send buffer is this rank's block of the receive buffer; other backends get a copy
+            mine = slabs[rank] if dist.get_backend(group) == "nccl" else slabs[rank].clone()
+            dist.all_gather_into_tensor(slabs.view(world * rows, width), mine, group=group)
+            return slabs
+        works = []
+        for start, stop in spans:
+            mine = slabs[rank, start:stop]
+            compute(a[start:stop], mine)
+            # block (g, chunk) of the result is contiguous inside slab g: gather every rank's block into its final place
+            send = mine if dist.get_backend(group) == "nccl" else mine.clone()
+            works.append(dist.all_gather([slabs[g, start:stop] for g in range(world)], send, group=group, async_op=True))
+        for work in works:
+            work.wait()
+        return slabs
+
+    if len(spans) == 1:
+        local = torch.empty((rows, width), device=a.device, dtype=out_dtype)
+        compute(a, local)
+        gathered = torch.empty((world * rows, width), device=a.device, dtype=out_dtype)
+        dist.all_gather_into_tensor(gathered, local, group=group)
+        return gathered.view(world, rows, width).permute(1, 0, 2).reshape(rows, world * width)
+
+    out = torch.empty((rows, world * width), device=a.device, dtype=out_dtype)
+    pending = None   # (work, gathered chunk, start, stop) of the chunk whose all-gather is in flight
+
+    def finish(item) -> None:
+        work, gathered, start, stop = item
+        work.wait()   # the compute stream waits for the collective's stream; the host does not block
+        out[start:stop].view(stop - start, world, width).copy_(gathered.view(world, stop - start, width).permute(1, 0, 2))
+
+    for start, stop in spans:
+        local = torch.empty((stop - start, width), device=a.device, dtype=out_dtype)
+        compute(a[start:stop], local)
+        gathered = torch.empty((world * (stop - start), width), device=a.device, dtype=out_dtype)
+        work = dist.all_gather_into_tensor(gathered, local, group=group, async_op=True)
+        if pending is not None:
+            finish(pending)   # issued after this chunk's all-gather, so the collective does not wait for the copy
+        pending = (work, gathered, start, stop)
+    if pending is not None:
+        finish(pending)
+    return out

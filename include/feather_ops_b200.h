@@ -108,6 +108,15 @@ int feather_conv3x3_launch(const void* x, const void* wp, const void* bias, void
 /* Diagnostic for the conv kernel's bounded waits, as feather_scaled_mm_status. No counterpart in the reference. */
 int feather_conv3x3_status(uint32_t* out);
 
+/* Self-test of the bounded device waits every tcgen05 kernel here is built on: one warp waits, for at most limit_cycles
+ * SM clocks (clamped to [1e5, 4e9]), on a barrier that nothing arrives on, gives up, records it and the kernel ends
+ * normally; a second waiter with a 64 times longer limit must leave through the abort flag. Synchronizes `stream`.
+ * scratch: device memory for three uint32 (caller-owned). out (host, five uint32): [0] recorded wait site | tag << 8
+ * (expected 2 | 5 << 8), [1] recorded block (0), [2] 1 if the first wait "completed" (expected 0), [3] the abort flag
+ * (expected 1), [4] 1 if the second wait "completed" (expected 0). Returns 0 on success. Neither traps nor faults.
+ * No counterpart in the reference (its kernels have no device-side waits). */
+int feather_selftest_wait_runs_out(long long limit_cycles, uint32_t* scratch, uint32_t* out, feather_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

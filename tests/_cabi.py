@@ -9,6 +9,36 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+# Guard bands: every output buffer handed to a launcher sits between two bands of a sentinel byte, and
+# `assert_clean` (called after the launches of a test) checks that no band was written. A store one row or a few
+# bytes past a ragged tile would otherwise land in a neighbouring live tensor and pass every parity check.
+GUARD_BYTES = 4096
+_SENTINEL = 0xA5
+_guards: list = []
+
+
+def guarded_empty(shape, device, dtype) -> torch.Tensor:
+    """An uninitialized tensor of `shape` with sentinel bands before and after it (checked by `check_guards`)."""
+    count = 1
+    for extent in shape:
+        count *= int(extent)
+    nbytes = count * torch.empty((), dtype=dtype).element_size()
+    padded = (nbytes + 15) // 16 * 16
+    buffer = torch.full((2 * GUARD_BYTES + padded,), _SENTINEL, device=device, dtype=torch.uint8)
+    _guards.append((buffer, nbytes))
+    return buffer[GUARD_BYTES : GUARD_BYTES + nbytes].view(dtype).view(*shape)
+
+
+def check_guards() -> None:
+    """Every sentinel band registered since the last check is intact (synchronizes)."""
+    pending, _guards[:] = list(_guards), []
+    for buffer, nbytes in pending:
+        before = buffer[:GUARD_BYTES]
+        after = buffer[GUARD_BYTES + nbytes :]
+        assert bool((before == _SENTINEL).all().item()), "a launch wrote before the start of its output buffer"
+        assert bool((after == _SENTINEL).all().item()), "a launch wrote past the end of its output buffer"
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -16,7 +46,7 @@ def _stream():
 def scaled_mm(a, b_prepacked, scale, bias, out_dtype, tile=(1, 8, 4, 8, 2, 0)):
     m, k = a.shape
     n = b_prepacked.shape[1]
-    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    c = guarded_empty((m, n), a.device, out_dtype)
     ok = _lib.load().launch_scaled_mm(
         _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), m, n, k, int(scale is not None), int(bias is not None),
         b_prepacked.dtype == torch.float8_e5m2, a.dtype == torch.bfloat16, out_dtype == torch.bfloat16, *tile[:5], bool(tile[5]), _stream(),
@@ -27,8 +57,8 @@ def scaled_mm(a, b_prepacked, scale, bias, out_dtype, tile=(1, 8, 4, 8, 2, 0)):
 
 def convrot_quantize(x, rotate=True, col_scale=None):
     m, k = x.shape
-    q = torch.empty((m, k), device=x.device, dtype=torch.int8)
-    scale = torch.empty((m,), device=x.device, dtype=torch.float32)
+    q = guarded_empty((m, k), x.device, torch.int8)
+    scale = guarded_empty((m,), x.device, torch.float32)
     ok = _lib.load().launch_convrot_quantize(_ptr(x), _ptr(col_scale), _ptr(q), _ptr(scale), m, k, int(x.dtype == torch.float16), rotate, _stream())
     assert ok, "launch_convrot_quantize refused the call"
     return q, scale
@@ -36,7 +66,7 @@ def convrot_quantize(x, rotate=True, col_scale=None):
 
 def int8_scaled_mm(a, w_prepacked, a_scale, w_scale, bias, out_dtype, transposed_b, n_out, tile=(4, 4, 2, 4, 4)):
     m, kc = a.shape
-    c = torch.empty((m, n_out), device=a.device, dtype=out_dtype)
+    c = guarded_empty((m, n_out), a.device, out_dtype)
     weight_out = kc if transposed_b else n_out
     inner = weight_out // 4
     stride_kc, stride_out = (1, inner) if transposed_b else (inner, 1)
@@ -51,7 +81,7 @@ def int8_scaled_mm(a, w_prepacked, a_scale, w_scale, bias, out_dtype, transposed
 def conv3x3(x, w_prepacked, bias, tile=(4, 4, 2, 4, 1)):
     b, c_in, h, w = x.shape
     c_out = w_prepacked.shape[1]
-    y = torch.empty((b, c_out, h, w), device=x.device, dtype=x.dtype)
+    y = guarded_empty((b, c_out, h, w), x.device, x.dtype)
     rc = _lib.load().feather_conv3x3_launch(
         _ptr(x), _ptr(w_prepacked), _ptr(bias), _ptr(y), b, c_in, c_out, h, w, int(bias is not None), *tile, int(x.dtype == torch.bfloat16), 0, _stream()
     )
@@ -60,8 +90,9 @@ def conv3x3(x, w_prepacked, bias, tile=(4, 4, 2, 4, 1)):
 
 
 def assert_clean(symbol):
-    """No bounded device wait ran out (also synchronizes)."""
+    """No bounded device wait ran out and no launch wrote outside its output buffer (also synchronizes)."""
     assert _lib.read_status(symbol) == (0, 0)
+    check_guards()
 
 
 def scaled_mm_splitk_wide(a, b_prepacked, scale, bias, out_dtype, block_n, splits, partials=None, counters=None):
@@ -71,11 +102,11 @@ def scaled_mm_splitk_wide(a, b_prepacked, scale, bias, out_dtype, block_n, split
     lib = _lib.load()
     floats = lib.feather_scaled_mm_splitk_wide_partial_floats(m, n, k, block_n, splits)
     if partials is None:
-        partials = torch.empty(max(int(floats), 1), device=a.device, dtype=torch.float32)
+        partials = guarded_empty((max(int(floats), 1),), a.device, torch.float32)
     if counters is None:
         counters = torch.zeros(-(-m // 128) * -(-n // block_n), device=a.device, dtype=torch.int32)
     assert partials.numel() >= floats
-    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    c = guarded_empty((m, n), a.device, out_dtype)
     ok = lib.launch_scaled_mm_splitk_wide(
         _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), m, n, k, int(scale is not None), int(bias is not None),
         b_prepacked.dtype == torch.float8_e5m2, a.dtype == torch.bfloat16, out_dtype == torch.bfloat16, block_n, splits, _ptr(partials), _ptr(counters),
@@ -92,11 +123,11 @@ def scaled_mm_splitk(a, b_prepacked, scale, bias, out_dtype, splits, partials=No
     lib = _lib.load()
     floats = lib.feather_scaled_mm_splitk_partial_floats(m, n, k, splits)
     if partials is None:
-        partials = torch.empty(max(int(floats), 1), device=a.device, dtype=torch.float32)
+        partials = guarded_empty((max(int(floats), 1),), a.device, torch.float32)
     if counters is None:
         counters = torch.zeros(-(-n // 64), device=a.device, dtype=torch.int32)
     assert partials.numel() >= floats
-    c = torch.empty((m, n), device=a.device, dtype=out_dtype)
+    c = guarded_empty((m, n), a.device, out_dtype)
     ok = lib.launch_scaled_mm_splitk(
         _ptr(a), _ptr(b_prepacked), _ptr(scale), _ptr(bias), _ptr(c), m, n, k, int(scale is not None), int(bias is not None),
         b_prepacked.dtype == torch.float8_e5m2, a.dtype == torch.bfloat16, out_dtype == torch.bfloat16, splits, _ptr(partials), _ptr(counters), _stream(),

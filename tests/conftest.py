@@ -16,7 +16,7 @@ def pytest_configure(config):
 def golden():
     import torch
 
-    return torch.load(ROOT / "tests" / "golden" / "reference_vectors.pt", weights_only=False)
+    return torch.load(ROOT / "tests" / "golden" / "reference_vectors.pt", weights_only=True)
 
 
 @pytest.fixture(scope="session")

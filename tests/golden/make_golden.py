@@ -24,8 +24,28 @@ def load_reference(root: str):
     return {name: importlib.import_module(f"feather_ops.{name}") for name in names}
 
 
+ACTIVATION_SHAPES = [(1, 256), (4, 512), (512, 1024), (1024, 2048), (300, 4096), (16, 8192), (8, 16384)]
+ACTIVATION_ROWS = 16
+
+
+def reference_activation(m: int, k: int, dtype: torch.dtype) -> torch.Tensor:
+    """The first ACTIVATION_ROWS rows of the reference test's activation for one shape (seed 0, N(0, 2))."""
+    torch.manual_seed(0)
+    return (torch.randn(m, k, dtype=torch.float32) * 2.0)[:ACTIVATION_ROWS].to(dtype).contiguous()
+
+
+def checksum(x: torch.Tensor) -> int:
+    """Order-dependent 63-bit checksum of a 16-bit tensor's bit patterns."""
+    bits = x.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+    weights = torch.arange(1, bits.numel() + 1, dtype=torch.int64) % 1000003
+    return int((bits.reshape(-1) * weights).sum().item() & 0x7FFFFFFFFFFFFFFF)
+
+
 def main() -> None:
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FEATHER_OPS_REFERENCE", "/root/reference"))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FEATHER_OPS_REFERENCE")
+    if not root:
+        raise SystemExit("usage: make_golden.py /path/to/feather-ops (or set FEATHER_OPS_REFERENCE)")
+    ref = load_reference(root)
     gen = torch.Generator().manual_seed(20240607)
     out: dict = {}
 
@@ -60,6 +80,17 @@ def main() -> None:
         q, s = i8.quantize_rowwise_int8(i8.rotate(x, i8.build_hadamard(256)))
         acts.append({"x": x, "q_recipe": q, "scale_recipe": s})
     out["activation"] = acts
+    # The seven shapes and the input distribution of the reference's own recipe test (tests/test_int8_convrot.py:270-286
+    # there: `torch.manual_seed(0); randn(M, K) * 2`), both dtypes, through the reference's rotate + row-wise quantize.
+    # Rows are independent, so only the first ACTIVATION_ROWS rows of each shape are kept; the inputs are not stored but
+    # re-made from the seed by the tests, which check them against the stored checksum first.
+    shaped = []
+    for dtype in (torch.bfloat16, torch.float16):
+        for m, k in ACTIVATION_SHAPES:
+            x = reference_activation(m, k, dtype)
+            q, s = i8.quantize_rowwise_int8(i8.rotate(x, i8.build_hadamard(256)))
+            shaped.append({"shape": (m, k), "dtype": str(dtype), "x_checksum": checksum(x), "q_recipe": q, "scale_recipe": s})
+    out["activation_reference_shapes"] = shaped
     codes = torch.tensor([[-300.0, -127.4, -0.5, 0.5, 1.5, 126.6, 500.0, 0.0]])
     q, s = i8.quantize_rowwise_int8(codes, scale=1.0)
     out["rowwise_stored_scale"] = {"x": codes, "q": q, "scale": s}

@@ -111,21 +111,45 @@ def test_operator_errors(cuda_device):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("channels,size", [(512, 128), (256, 256), (128, 512)])
-def test_benchmark_shapes_by_properties(cuda_device, channels, size, dtype):
-    # VAE-decoder shapes. The fp64 oracle is run on a slice of the output channels (a conv's output channels
-    # are independent), plus: a sub-image computed alone equals the same pixels of the whole image away from
-    # its border rows, and a zero input gives exactly the bias.
+def test_benchmark_shapes_whole_output(cuda_device, channels, size, dtype):
+    # VAE-decoder shapes: every output element against the fp64 oracle (under a second on the host cores), per output
+    # channel as well as over the whole tensor; then a sub-image computed alone equals the same pixels of the whole
+    # image away from its border rows, and a zero input gives exactly the bias.
     import feather_ops_b200 as fo
 
     x, weight, bias = oc.make_inputs(1, channels, channels, size, size, dtype)
     xg, bg = x.to(cuda_device), bias.to(cuda_device)
     packed = fo.prepack_conv2d_weight_3x3(weight.to(cuda_device))
-    y = fo.conv3x3_prepacked(xg, packed, bg)
+    y = _cabi.conv3x3(xg, packed, bg, fo.conv2d.select_conv3x3_config(channels, size))
     _cabi.assert_clean(STATUS)
-    picked = torch.arange(5, channels, channels // 8)
-    ref = oc.conv3x3_fp64(x, weight[picked], bias[picked])
-    assert _rel(y[:, picked.to(cuda_device)], ref) < TOL[dtype]
+    assert torch.equal(y, fo.conv3x3_prepacked(xg, packed, bg))
+    ref = oc.conv3x3_fp64(x, weight, bias)
+    assert _rel(y, ref) < TOL[dtype]
+    per_channel = (y.double().cpu() - ref).flatten(2).norm(dim=2) / ref.flatten(2).norm(dim=2)
+    assert per_channel.max().item() < 2 * TOL[dtype]
     band = fo.conv3x3_prepacked(xg[:, :, 16:48].contiguous(), packed, bg)
     assert torch.equal(band[:, :, 1:-1], y[:, :, 17:47])
     zero = fo.conv3x3_prepacked(torch.zeros_like(xg[:, :, :4]), packed, bg)
     assert torch.equal(zero, bg.reshape(1, -1, 1, 1).expand_as(zero))
+
+
+def test_compiled_caller_matches_the_oracle(cuda_device):
+    # tests/test_conv3x3.py:276-291 of the reference: the prepacked op under torch.compile with the default backend
+    import feather_ops_b200 as fo
+    from feather_ops_b200.conv2d import select_conv3x3_config
+
+    x, weight, _ = oc.make_inputs(1, 96, 96, 64, 64, torch.bfloat16, seed=3, with_bias=False)
+    packed = fo.prepack_conv2d_weight_3x3(weight.to(cuda_device))
+    tile = select_conv3x3_config(96, 64)
+    assert tile is not None
+
+    def run(inp, wk):
+        return fo.conv3x3_prepacked(inp, wk, None, tile=tile)
+
+    torch._dynamo.reset()
+    out = torch.compile(run, fullgraph=True)(x.to(cuda_device), packed)
+    assert _rel(out, oc.conv3x3_fp64(x, weight, None)) < 4e-3
+    assert torch.equal(out, run(x.to(cuda_device), packed))
+    auto = torch.compile(lambda inp, wk: fo.conv3x3_prepacked(inp, wk, None), fullgraph=True, dynamic=True)(x.to(cuda_device), packed)
+    assert torch.equal(auto, out)
+    _cabi.assert_clean(STATUS)

@@ -29,15 +29,87 @@ def test_quantizer_codes_and_scales_are_bit_exact(cuda_device, shape, rotate, dt
     assert torch.equal(s.cpu(), s_ref)
 
 
+def _recipe_bounds(q, s, q_recipe, s_recipe):
+    # the reference's own bounds (tests/test_int8_convrot.py:280-286 there): the kernel sums in another order than the
+    # matmul recipe, so codes on a .5 boundary may flip by one; fewer than one in a thousand may
+    assert (q != q_recipe).float().mean().item() < 1e-3
+    assert (q.int() - q_recipe.int()).abs().max().item() <= 1
+    assert ((s - s_recipe).abs() / s_recipe.abs()).max().item() < 1e-2
+    dq, ref_dq = q.float() * s[:, None], q_recipe.float() * s_recipe[:, None]
+    assert ((dq - ref_dq).norm() / ref_dq.norm()).item() < 1e-3
+
+
 def test_quantizer_against_the_reference_recipe(cuda_device, golden):
-    # the matmul rotation + row-wise quantize recipe, with the reference's own bounds
+    # fixtures produced by the reference's rotate + quantize_rowwise_int8 (see tests/golden/make_golden.py)
     for case in golden["activation"]:
         q, s = _cabi.convrot_quantize(case["x"].to(cuda_device), True)
-        q, s = q.cpu(), s.cpu()
-        assert (q != case["q_recipe"]).float().mean().item() < 2e-3
-        assert (q.int() - case["q_recipe"].int()).abs().max().item() <= 1
-        assert ((s - case["scale_recipe"]).abs() / case["scale_recipe"]).max().item() < 1e-2
+        _recipe_bounds(q.cpu(), s.cpu(), case["q_recipe"], case["scale_recipe"])
         assert q.abs().max().item() == 127  # the row maximum maps to +-127
+    from tests.golden import make_golden as mg
+
+    for case in golden["activation_reference_shapes"]:
+        dtype = torch.bfloat16 if "bfloat16" in case["dtype"] else torch.float16
+        x = mg.reference_activation(*case["shape"], dtype)
+        assert mg.checksum(x) == case["x_checksum"], "the seeded activation is not the one the fixture was made from"
+        q, s = _cabi.convrot_quantize(x.to(cuda_device), True)
+        _recipe_bounds(q.cpu(), s.cpu(), case["q_recipe"], case["scale_recipe"])
+    _cabi.check_guards()
+
+
+def _recipe(x, rotate, col_scale=None):
+    """The matmul rotation + row-wise quantize recipe of the reference's tests (tests/test_int8_convrot.py:256-266)."""
+    if col_scale is not None:
+        x = (x.float() * col_scale.float()).to(x.dtype)
+    y = o8.rotate(x, o8.build_hadamard(256)) if rotate else x
+    return o8.quantize_rowwise_int8(y)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("shape", [(1, 256), (4, 512), (512, 1024), (1024, 2048), (300, 4096), (16, 8192), (8, 16384)])
+def test_quantizer_matches_the_reference_recipe_on_the_reference_shapes(cuda_device, shape, rotate, dtype):
+    # the reference's seven shapes at full size and its distribution, recipe computed on the host cores
+    m, k = shape
+    torch.manual_seed(0)
+    x = (torch.randn(m, k, dtype=torch.float32) * 2.0).to(dtype)
+    q, s = _cabi.convrot_quantize(x.to(cuda_device), rotate)
+    _cabi.check_guards()
+    q_ref, s_ref = _recipe(x, rotate)
+    _recipe_bounds(q.cpu(), s.cpu(), q_ref, s_ref)
+    q_exact, s_exact = o8.convrot_quantize(x, rotate)
+    assert torch.equal(q.cpu(), q_exact) and torch.equal(s.cpu(), s_exact)
+
+
+# every group-256 activation width of the reference's model plan (tests/test_int8_convrot.py:293-315 there)
+PLAN_PRODUCER_WIDTHS = [1024, 2048, 3072, 3840, 4096, 5120, 5376, 6144, 7168, 8192, 10240, 11520, 12288, 14336, 16384, 21504, 24576, 25600, 28672,
+                        36864, 248320]
+
+
+@pytest.mark.parametrize("rotate", [True, False])
+@pytest.mark.parametrize("k", PLAN_PRODUCER_WIDTHS)
+def test_quantizer_every_plan_width(cuda_device, k, rotate):
+    torch.manual_seed(k)
+    x = (torch.randn(3, k, dtype=torch.float32) * 2.0).to(torch.bfloat16)
+    q, s = _cabi.convrot_quantize(x.to(cuda_device), rotate)
+    _cabi.check_guards()
+    q_exact, s_exact = o8.convrot_quantize(x, rotate)
+    assert torch.equal(q.cpu(), q_exact) and torch.equal(s.cpu(), s_exact)
+    _recipe_bounds(q.cpu(), s.cpu(), *_recipe(x, rotate))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("k", [16384, 16640, 32768, 248320])
+def test_quantizer_wide_rows_fold_the_column_scale(cuda_device, k, dtype):
+    # the input gradient's producer (no rotation, weight scale folded in) on wide rows (tests/test_int8_convrot.py:334-346)
+    torch.manual_seed(k)
+    x = (torch.randn(5, k, dtype=torch.float32) * 2.0).to(dtype)
+    col = torch.rand(k, dtype=torch.float32) * 0.5 + 0.5
+    q, s = _cabi.convrot_quantize(x.to(cuda_device), False, col.to(cuda_device))
+    _cabi.check_guards()
+    q_exact, s_exact = o8.convrot_quantize(x, False, col)
+    assert torch.equal(q.cpu(), q_exact) and torch.equal(s.cpu(), s_exact)
+    q_ref, s_ref = _recipe(x, False, col)
+    assert (q.cpu() != q_ref).float().mean().item() < 1e-3
 
 
 def test_quantizer_edge_cases(cuda_device):
@@ -172,8 +244,8 @@ def test_operator_errors(cuda_device):
         op(a, w, s[:4], None, None, c, False, *tile)
 
 
-def test_benchmark_shape_by_properties(cuda_device):
-    # 4096 x 3072 x 3072: quantize -> GEMM with the offline weight recipe; row sample against the fp64 oracle
+def test_benchmark_shape_whole_output(cuda_device):
+    # 4096 x 3072 x 3072: quantize -> GEMM with the offline weight recipe; every element against the fp64 oracle
     import feather_ops_b200 as fo
 
     x = o8.make_activation(4096, 3072, torch.bfloat16)
@@ -182,11 +254,79 @@ def test_benchmark_shape_by_properties(cuda_device):
     q_ref, s_ref = o8.convrot_quantize(x, True)
     y = fo.convrot_int8_linear(x.to(cuda_device), wq.to(cuda_device), ws.to(cuda_device))
     _cabi.assert_clean(STATUS)
-    rows = torch.randperm(4096, generator=torch.Generator().manual_seed(1))[:64]
-    ref = o8.int8_scaled_mm(q_ref[rows], wq, s_ref[rows], ws, None, torch.bfloat16)
-    assert _max_rel(y[rows.to(cuda_device)], ref) < 0.02
-    full = x.float()[rows] @ w.float().T
-    assert ((y[rows.to(cuda_device)].float().cpu() - full).norm() / full.norm()).item() < 2e-2
+    ref = o8.int8_scaled_mm(q_ref, wq, s_ref, ws, None, torch.bfloat16)
+    assert _max_rel(y, ref) < 0.02
+    # the GEMM alone through the C ABI, both directions, every element (guard bands around the outputs)
+    packed = o8.prepack_int8_weight(wq).to(cuda_device)
+    fwd = _cabi.int8_scaled_mm(q_ref.to(cuda_device), packed, s_ref.to(cuda_device), ws.to(cuda_device), None, torch.bfloat16, False, 3072)
+    assert torch.equal(fwd, y)
+    bwd = _cabi.int8_scaled_mm(q_ref.to(cuda_device), packed, s_ref.to(cuda_device), None, None, torch.bfloat16, True, 3072)
+    _cabi.assert_clean(STATUS)
+    assert _max_rel(bwd, o8.int8_scaled_mm(q_ref, wq, s_ref, None, None, torch.bfloat16, True)) < 0.02
+    full = x.float() @ w.float().T
+    assert ((y.float().cpu() - full).norm() / full.norm()).item() < 2e-2
+
+
+# the reference's model cells (tests/test_int8_convrot.py:25-39 there): (M, N_w, K_w), the weight's output / input axes
+MODEL_CELLS = [(512, 2048, 1024), (4096, 2048, 2048), (4096, 8192, 2048), (4096, 2048, 8192), (4112, 1536, 6144), (4112, 6144, 6144), (4128, 11520, 3840),
+               (5376, 21504, 5376), (4112, 3072, 8192), (2048, 4304, 1152), (1024, 3456, 1152), (1, 36864, 6144), (16, 128, 128)]
+
+
+def _exact_accumulators(a, w_t):
+    """`a [m, kc] int8 @ w_t [kc, n] int8` as exact integers held in fp64: fp32 products of 1024-deep slices are exact
+    (127 * 127 * 1024 < 2^24), their sum is taken in fp64."""
+    acc = torch.zeros((a.shape[0], w_t.shape[1]), dtype=torch.float64)
+    for k0 in range(0, a.shape[1], 1024):
+        acc += (a[:, k0 : k0 + 1024].float() @ w_t[k0 : k0 + 1024].float()).double()
+    return acc
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("cell", MODEL_CELLS)
+def test_model_cells_against_the_oracle(cuda_device, cell, transposed):
+    # both directions of every model cell of the reference's test, through the public API with its own tile choice;
+    # the oracle is evaluated in bands of 1024 rows on the host cores with exact integer accumulators
+    import feather_ops_b200 as fo
+
+    m, n_w, k_w = cell
+    contraction, out = (n_w, k_w) if transposed else (k_w, n_w)
+    gen = torch.Generator().manual_seed(m + n_w)
+    wq = torch.randint(-127, 128, (n_w, k_w), generator=gen, dtype=torch.int8)
+    a = torch.randint(-127, 128, (m, contraction), generator=gen, dtype=torch.int8)
+    a_scale = torch.rand(m, generator=gen) * 0.02 + 1e-4
+    w_scale = None if transposed else torch.rand(out, generator=gen) * 0.02 + 1e-4
+    packed = fo.prepack_int8_weight(wq.to(cuda_device))
+    got = fo.int8_scaled_mm(a.to(cuda_device), packed, a_scale.to(cuda_device), None if transposed else w_scale.to(cuda_device), None, torch.bfloat16, transposed)
+    _cabi.assert_clean(STATUS)
+    assert got.shape == (m, out)
+    got = got.cpu()
+    w_t = wq if transposed else wq.T.contiguous()
+    for r0 in range(0, m, 1024):
+        acc = _exact_accumulators(a[r0 : r0 + 1024], w_t) * a_scale[r0 : r0 + 1024].double()[:, None]
+        if not transposed:
+            acc = acc * w_scale.double()[None, :]
+        assert _max_rel(got[r0 : r0 + 1024], acc.to(torch.bfloat16)) < 0.02, (cell, transposed, r0)
+
+
+def test_compiled_caller_matches_eager(cuda_device):
+    # tests/test_int8_convrot.py:387-401 of the reference: dynamic shapes, default backend, one opaque node
+    import feather_ops_b200 as fo
+
+    gen = torch.Generator().manual_seed(0)
+    m, n_w, k_w = 4112, 1152, 1152
+    packed = fo.prepack_int8_weight(torch.randint(-127, 128, (n_w, k_w), generator=gen, dtype=torch.int8).to(cuda_device))
+    a = torch.randint(-127, 128, (m, k_w), generator=gen, dtype=torch.int8).to(cuda_device)
+    a_scale = (torch.rand(m, generator=gen) * 0.02).to(cuda_device)
+    w_scale = (torch.rand(n_w, generator=gen) * 0.02).to(cuda_device)
+
+    def run(a, a_scale):
+        return fo.int8_scaled_mm(a, packed, a_scale, w_scale, None, torch.bfloat16, False)
+
+    eager = run(a, a_scale)
+    torch._dynamo.reset()
+    compiled = torch.compile(run, fullgraph=True, dynamic=True)(a, a_scale)
+    assert torch.equal(compiled, eager)
+    _cabi.assert_clean(STATUS)
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])

@@ -15,7 +15,10 @@ from oracle import int8_convrot as o8
 from oracle import scaled_mm as osm
 
 # a checkout of woct0rdho/feather-ops, when one is at hand: the tests that import it skip otherwise
-REFERENCE = pathlib.Path(os.environ.get("FEATHER_OPS_REFERENCE", "/root/reference"))
+# FEATHER_OPS_REFERENCE, or a directory named `reference` beside this repository
+REFERENCE = pathlib.Path(os.environ["FEATHER_OPS_REFERENCE"]) if os.environ.get("FEATHER_OPS_REFERENCE") else pathlib.Path(__file__).resolve().parents[2] / "reference"
+if not (REFERENCE / "feather_ops" / "naive.py").exists():
+    REFERENCE = None
 
 
 def _fp8(raw: torch.Tensor, name: str) -> torch.Tensor:
@@ -84,17 +87,35 @@ def test_radix4_rotation_equals_the_hadamard_matrix_on_integers():
     assert torch.equal(o8.hadamard256_radix4(x), x @ h.T)
 
 
+def _within_recipe_bounds(q, scale, q_recipe, scale_recipe):
+    # tests/test_int8_convrot.py:280-286 of the reference: code mismatch rate < 1e-3 (differences of one code), scale
+    # rel < 1e-2, dequantized rel < 1e-3. The recipe rotates with a matmul in the input dtype, the kernel in fp32.
+    assert (q != q_recipe).float().mean().item() < 1e-3
+    assert (q.int() - q_recipe.int()).abs().max().item() <= 1
+    assert ((scale - scale_recipe).abs() / scale_recipe).max().item() < 1e-2
+    deq = q.float() * scale[:, None]
+    ref = q_recipe.float() * scale_recipe[:, None]
+    assert ((deq - ref).norm() / ref.norm()).item() < 1e-3
+
+
 def test_kernel_restatement_stays_within_the_reference_bounds_of_the_recipe(golden):
-    # tests/test_int8_convrot.py:280-286 of the reference: code mismatch rate < 1e-3 (differences of one
-    # code), scale rel < 1e-2, dequantized rel < 1e-3... the recipe rotates with a matmul, the kernel in fp32.
     for case in golden["activation"]:
-        q, scale = o8.convrot_quantize(case["x"], True)
-        assert (q != case["q_recipe"]).float().mean().item() < 2e-3
-        assert (q.int() - case["q_recipe"].int()).abs().max().item() <= 1
-        assert ((scale - case["scale_recipe"]).abs() / case["scale_recipe"]).max().item() < 1e-2
-        deq = q.float() * scale[:, None]
-        ref = case["q_recipe"].float() * case["scale_recipe"][:, None]
-        assert ((deq - ref).norm() / ref.norm()).item() < 1e-2
+        _within_recipe_bounds(*o8.convrot_quantize(case["x"], True), case["q_recipe"], case["scale_recipe"])
+
+
+def test_kernel_restatement_on_the_reference_recipe_shapes(golden):
+    # the reference test's seven shapes and distribution, both dtypes; the inputs are re-made from the seed
+    from tests.golden import make_golden as mg
+
+    assert [tuple(c["shape"]) for c in golden["activation_reference_shapes"][:7]] == mg.ACTIVATION_SHAPES
+    for case in golden["activation_reference_shapes"]:
+        dtype = torch.bfloat16 if "bfloat16" in case["dtype"] else torch.float16
+        x = mg.reference_activation(*case["shape"], dtype)
+        assert mg.checksum(x) == case["x_checksum"]
+        _within_recipe_bounds(*o8.convrot_quantize(x, True), case["q_recipe"], case["scale_recipe"])
+        # the oracle's own restatement of the recipe equals the reference's output bit for bit
+        q_port, s_port = o8.quantize_rowwise_int8(o8.rotate(x, o8.build_hadamard(256)))
+        assert torch.equal(q_port, case["q_recipe"]) and torch.equal(s_port, case["scale_recipe"])
 
 
 def test_quantizer_without_rotation_folds_the_column_scale():
@@ -125,7 +146,7 @@ def test_empty_inputs():
     assert osm.scaled_mm_f32(a, packed, s, b, torch.bfloat16, b_prepacked=True).shape == (0, 32)
 
 
-@pytest.mark.skipif(not REFERENCE.exists(), reason="the reference checkout is only present in the build container")
+@pytest.mark.skipif(REFERENCE is None, reason="set FEATHER_OPS_REFERENCE to a checkout of the reference to run this")
 def test_oracle_equals_the_reference_python_directly():
     pkg = types.ModuleType("feather_ops")
     pkg.__path__ = [str(REFERENCE / "feather_ops")]

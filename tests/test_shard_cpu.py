@@ -12,6 +12,12 @@ from feather_ops_b200 import shard
 from oracle import scaled_mm as osm
 
 
+def test_row_chunks_cover_the_rows():
+    assert shard.row_chunks(10, 3) == [(0, 4), (4, 7), (7, 10)]
+    assert shard.row_chunks(2, 8) == [(0, 1), (1, 2)]
+    assert shard.row_chunks(0, 4) == [(0, 0)]
+
+
 def test_token_shards_cover_the_batch():
     for m in (0, 1, 7, 4096, 65536, 65537):
         for world in (1, 2, 3, 8):
@@ -50,6 +56,13 @@ def _worker(rank, world, port, results):
         slab, bias_slab = shard.weight_column_shard(packed, rank, world, bias)
         gathered = shard.scaled_mm_n_sharded(a, slab, scale, bias_slab, torch.bfloat16, _oracle_mm)
         ok_cols = torch.equal(gathered, full)
+        # the pipelined variants (row chunks, ragged last chunk) and the slab layout give the same numbers
+        for chunks in (3, 64):
+            piped = shard.scaled_mm_n_sharded(a, slab, scale, bias_slab, torch.bfloat16, _oracle_mm, chunks=chunks)
+            ok_cols = ok_cols and torch.equal(piped, full)
+        for chunks in (1, 4):
+            slabs = shard.scaled_mm_n_sharded(a, slab, scale, bias_slab, torch.bfloat16, _oracle_mm, chunks=chunks, layout="slabs")
+            ok_cols = ok_cols and slabs.shape == (world, 37, 48) and torch.equal(slabs.permute(1, 0, 2).reshape(37, 96), full)
         results[rank] = (ok_rows, ok_cols)
     finally:
         dist.destroy_process_group()
