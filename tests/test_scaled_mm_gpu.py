@@ -269,8 +269,10 @@ def test_one_and_two_rows_take_the_vector_kernel(cuda_device, shape, a_dtype, b_
     first = _cabi.scaled_mm(*dev, out_dtype, (1, 2, 4, 1, 2, 1))
     _cabi.assert_clean(STATUS)
     _compare(first, ref, out_dtype, 1e-3)
-    again, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 2)
+    again, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 1)   # one split through the split-K entry point: the same kernel
     assert torch.equal(first, again)
+    split, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 2)   # an explicit K split runs the tcgen05 split-K kernel instead
+    _compare(split, ref, out_dtype, 1e-3)
     no_bias = _cabi.scaled_mm(dev[0], dev[1], None, None, out_dtype, (1, 2, 4, 1, 2, 1))
     _compare(no_bias, osm.scaled_mm_f32(a, packed, None, None, out_dtype, b_prepacked=True), out_dtype, 1e-3)
 
@@ -290,8 +292,11 @@ def test_few_rows_take_the_warp_mma_kernel(cuda_device, shape, a_dtype, b_dtype,
     first = _cabi.scaled_mm(*dev, out_dtype, (1, 2, 4, 1, 2, 1))
     _cabi.assert_clean(STATUS)
     _compare(first, ref, out_dtype, 1e-3)
-    again, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 3)
+    again, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 1)   # one split through the split-K entry point: the same kernel
     assert torch.equal(first, again)
+    split, _, _ = _cabi.scaled_mm_splitk(*dev, out_dtype, 3)   # an explicit K split runs the tcgen05 split-K kernel instead
+    _cabi.assert_clean(STATUS)
+    _compare(split, ref, out_dtype, 1e-3)
     no_scale = _cabi.scaled_mm(dev[0], dev[1], None, None, out_dtype, (1, 2, 4, 1, 2, 1))
     _compare(no_scale, osm.scaled_mm_f32(a, packed, None, None, out_dtype, b_prepacked=True), out_dtype, 1e-3)
 
