@@ -35,6 +35,8 @@ PROTOTYPES = {
         _c_int,
         [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _c_int, _c_int, _c_bool, _c_bool, _c_bool, _c_int, _ptr, ctypes.c_char_p, ctypes.c_size_t],
     ),
+    "feather_scaled_mm_set_sm_margin": (_c_int, [_c_int]),
+    "launch_interleave_slabs": (_c_bool, [_ptr, _ptr, _i64, _i64, _i64, _ptr]),
     "feather_scaled_mm_status": (_c_int, [_ptr]),
     "launch_convrot_quantize": (_c_bool, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _c_int, _c_bool, _ptr]),
     "launch_int8_scaled_mm": (

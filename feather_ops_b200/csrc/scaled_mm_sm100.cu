@@ -40,6 +40,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 namespace feather {
@@ -1106,6 +1107,10 @@ scaled_mm_skinny_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     }
 }
 
+// SMs that the persistent scaled_mm kernels leave free (feather_scaled_mm_set_sm_margin): a collective that runs beside
+// the product needs SMs of its own, because a persistent CTA holds its SM's shared memory until the kernel ends.
+std::atomic<int> g_sm_margin{0};
+
 struct LaunchArgs {
     const uint16_t* a;
     const uint8_t* b;
@@ -1175,7 +1180,8 @@ bool launch_instance(const LaunchArgs& args) {
     }
     const int64_t num_items = static_cast<int64_t>(p.tiles_m) * p.tiles_n * p.splits;
     if (num_items > (1 << 30)) return false;
-    const int sms = device_info().sm_count;
+    const int margin = g_sm_margin.load(std::memory_order_relaxed);
+    const int sms = device_info().sm_count - margin > 0 ? device_info().sm_count - margin : 1;
     const int grid = num_items < sms ? static_cast<int>(num_items) : sms;
     p.single_item = (split && num_items <= sms) ? 1 : 0;
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
@@ -1265,7 +1271,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
+    const int margin_pairs = (g_sm_margin.load(std::memory_order_relaxed) + 1) / 2;
+    const int usable = pairs - margin_pairs > 0 ? pairs - margin_pairs : 1;
+    const int grid = 2 * (num_tiles < usable ? num_tiles : usable);
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
 }
@@ -1940,6 +1948,50 @@ extern "C" int launch_scaled_mm_splitk_static(const uint16_t* a, const uint8_t* 
         return 3;
     }
     return 0;
+}
+
+// Leaves `sms` SMs free in every later launch of the persistent scaled_mm kernels (the CTA-pair kernel and the one-CTA
+// kernel size their grids by the SM count); 0 restores full grids. For a caller that overlaps the product with other
+// kernels that need SMs of their own, e.g. an NCCL collective on another stream. Returns the previous value.
+// Process-wide; takes effect at the next launch. No counterpart in the reference.
+extern "C" int feather_scaled_mm_set_sm_margin(int sms) {
+    if (sms < 0) sms = 0;
+    return feather::smm::g_sm_margin.exchange(sms, std::memory_order_relaxed);
+}
+
+// out[r][g][:] = slabs[g][r][:] for g < world, r < rows, rows of `width_bytes` bytes (a multiple of 16, pointers 16-byte
+// aligned): turns the [world][rows][width] result of an all-gather of column slabs into the row-major [rows][world * width]
+// matrix. A plain HBM-bound copy kernel with 16-byte accesses. Returns false for bad arguments. No counterpart in the
+// reference (it has no multi-GPU path).
+namespace feather {
+namespace smm {
+__global__ void __launch_bounds__(256) interleave_slabs_kernel(const uint4* __restrict__ slabs, uint4* __restrict__ out, int64_t world, int64_t rows,
+                                                                int64_t width16) {
+    const int64_t total = world * rows * width16;
+    const int64_t row16 = world * width16;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        // i indexes the output: row r, slab g, 16-byte unit w
+        const int64_t r = i / row16;
+        const int64_t rem = i - r * row16;
+        const int64_t g = rem / width16;
+        const int64_t w = rem - g * width16;
+        out[i] = __ldcs(slabs + (g * rows + r) * width16 + w);
+    }
+}
+}  // namespace smm
+}  // namespace feather
+
+extern "C" bool launch_interleave_slabs(const void* slabs, void* out, int64_t world, int64_t rows, int64_t width_bytes, cudaStream_t stream) {
+    if (world <= 0 || rows < 0 || width_bytes <= 0 || width_bytes % 16 != 0) return false;
+    if (((reinterpret_cast<uintptr_t>(slabs) | reinterpret_cast<uintptr_t>(out)) & 15u) != 0) return false;
+    if (rows == 0) return true;
+    const int64_t total = world * rows * (width_bytes / 16);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(feather::device_info().sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    feather::smm::interleave_slabs_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<const uint4*>(slabs), static_cast<uint4*>(out), world, rows,
+                                                                                             width_bytes / 16);
+    return cudaGetLastError() == cudaSuccess;
 }
 
 // Reads (and clears) the status record the kernel's bounded waits report into: out[0] = wait site

@@ -168,6 +168,22 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
     STD_TORCH_CHECK(launched, "scaled_mm_splitk: unsupported problem");
 }
 
+// out[r, g * width : (g + 1) * width] = slabs[g, r, :]: the row-major matrix from the [world, rows, width] all-gather of column slabs.
+void interleave_slabs(const Tensor& slabs, Tensor& out) {
+    STD_TORCH_CHECK(slabs.is_cuda() && out.is_cuda() && slabs.get_device_index() == out.get_device_index(), "slabs and out must be on one CUDA device");
+    STD_TORCH_CHECK(slabs.dim() == 3 && out.dim() == 2, "slabs must be [world, rows, width], out [rows, world * width]");
+    STD_TORCH_CHECK(slabs.scalar_type() == out.scalar_type(), "slabs and out must have the same dtype");
+    STD_TORCH_CHECK(is_half_or_bf16(out.scalar_type()), "slabs must be float16 or bfloat16");
+    const int64_t world = slabs.size(0), rows = slabs.size(1), width = slabs.size(2);
+    STD_TORCH_CHECK(out.size(0) == rows && out.size(1) == world * width, "out must be [rows, world * width]");
+    STD_TORCH_CHECK(slabs.is_contiguous() && out.is_contiguous(), "slabs and out must be contiguous");
+    STD_TORCH_CHECK(width % 8 == 0, "the slab width must be a multiple of 8 elements");
+    STD_TORCH_CHECK(aligned16(slabs.const_data_ptr()) && aligned16(out.mutable_data_ptr()), "data pointers must be 16-byte aligned");
+    const auto device = slabs.get_device_index();
+    torch::stable::accelerator::DeviceGuard guard(device);
+    STD_TORCH_CHECK(launch_interleave_slabs(slabs.const_data_ptr(), out.mutable_data_ptr(), world, rows, width * 2, current_stream(device)), "interleave_slabs launch failed");
+}
+
 void int8_scaled_mm(const Tensor& a, const Tensor& b_prepacked, const Tensor& a_scale, const std::optional<Tensor>& b_scale,
                     const std::optional<Tensor>& bias, Tensor& c, bool transposed_b, int64_t block_warps_m, int64_t block_warps_n,
                     int64_t unroll_k, int64_t repeat_m, int64_t repeat_n) {
@@ -332,6 +348,7 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
     m.def(
         "scaled_mm_splitk(Tensor a, Tensor b_prepacked, Tensor? scale, Tensor? bias, Tensor(a!) c, Tensor(b!) partials, Tensor(c!) counters, "
         "int splits, int block_n=64) -> ()");
+    m.def("interleave_slabs(Tensor slabs, Tensor(a!) out) -> ()");
     m.def(
         "int8_scaled_mm(Tensor a, Tensor b_prepacked, Tensor a_scale, Tensor? b_scale, Tensor? bias, Tensor(a!) c, bool transposed_b, "
         "int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n) -> ()");
@@ -344,6 +361,7 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
 STABLE_TORCH_LIBRARY_IMPL(feather_ops, CUDA, m) {
     m.impl("scaled_mm", TORCH_BOX(&scaled_mm));
     m.impl("scaled_mm_splitk", TORCH_BOX(&scaled_mm_splitk));
+    m.impl("interleave_slabs", TORCH_BOX(&interleave_slabs));
     m.impl("int8_scaled_mm", TORCH_BOX(&int8_scaled_mm));
     m.impl("convrot_quantize", TORCH_BOX(&convrot_quantize));
     m.impl("conv2d_3x3", TORCH_BOX(&conv2d_3x3));

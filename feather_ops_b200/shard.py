@@ -60,6 +60,37 @@ def _kernel_into(a, b_slab, scale, bias_slab, out) -> None:
     _scaled_mm_auto(a, b_slab, scale, bias_slab, out)
 
 
+def _interleave(gathered: torch.Tensor, out: torch.Tensor) -> None:
+    """`out[r, g * width : (g + 1) * width] = gathered[g, r, :]`: the library's copy kernel on CUDA, a strided torch copy elsewhere."""
+    world, rows, width = gathered.shape
+    if gathered.is_cuda and gathered.dtype in (torch.bfloat16, torch.float16) and width % 8 == 0:
+        torch.ops.feather_ops.interleave_slabs.default(gathered, out)
+    else:
+        out.view(rows, world, width).copy_(gathered.permute(1, 0, 2))
+
+
+class _SmMargin:
+    """Leave `sms` SMs free in the persistent scaled_mm kernels while a collective runs beside them (restored on exit).
+    A persistent CTA holds its SM's shared memory until the kernel ends, so without free SMs the collective's kernel
+    would only start when the product has finished, and nothing would overlap."""
+
+    def __init__(self, sms: int, active: bool) -> None:
+        self.sms, self.active, self.previous = sms, active and sms > 0, 0
+
+    def __enter__(self):
+        if self.active:
+            from . import _lib
+
+            self.previous = _lib.load().feather_scaled_mm_set_sm_margin(self.sms)
+        return self
+
+    def __exit__(self, *exc) -> None:
+        if self.active:
+            from . import _lib
+
+            _lib.load().feather_scaled_mm_set_sm_margin(self.previous)
+
+
 def row_chunks(rows: int, chunks: int) -> list[tuple[int, int]]:
     """`chunks` contiguous row ranges covering `rows` (fewer when there are fewer rows), balanced to within one row."""
     chunks = max(1, min(chunks, rows)) if rows > 0 else 1
@@ -67,12 +98,13 @@ def row_chunks(rows: int, chunks: int) -> list[tuple[int, int]]:
 
 
 def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, matmul: Callable | None = None, group=None, *, chunks: int = 1,
-                        layout: str = "row_major", matmul_into: Callable | None = None) -> torch.Tensor:
+                        layout: str = "row_major", matmul_into: Callable | None = None, sm_margin: int = 32) -> torch.Tensor:
     """Full `C` on every rank from per-rank weight slabs: local product, then an all-gather of the `[M, N / world]` slabs.
 
     `matmul(a, b, scale, bias, out_dtype) -> Tensor` or `matmul_into(a, b, scale, bias, out) -> None` computes the local
     product (default: this library's kernel, writing in place). `layout` is `"row_major"` (`[M, N]`) or `"slabs"`
-    (`[world, M, N / world]`); `chunks > 1` pipelines the all-gather of one row chunk against the product of the next.
+    (`[world, M, N / world]`); `chunks > 1` pipelines the all-gather of one row chunk against the product of the next,
+    with `sm_margin` SMs left free by the library's kernel for the collective's kernel to run on.
     """
     if layout not in ("row_major", "slabs"):
         raise ValueError(f"layout must be 'row_major' or 'slabs', got {layout!r}")
@@ -90,6 +122,11 @@ def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, ma
             out.copy_(matmul(a_rows, b_slab, scale, bias_slab, out_dtype))
 
     spans = row_chunks(rows, chunks)
+    with _SmMargin(sm_margin, a.is_cuda and len(spans) > 1 and matmul is None):
+        return _n_sharded(a, compute, spans, world, rank, rows, width, out_dtype, layout, group)
+
+
+def _n_sharded(a, compute, spans, world, rank, rows, width, out_dtype, layout, group) -> torch.Tensor:
     if layout == "slabs":
         slabs = torch.empty((world, rows, width), device=a.device, dtype=out_dtype)
         if len(spans) == 1:
@@ -115,7 +152,9 @@ def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, ma
         compute(a, local)
         gathered = torch.empty((world * rows, width), device=a.device, dtype=out_dtype)
         dist.all_gather_into_tensor(gathered, local, group=group)
-        return gathered.view(world, rows, width).permute(1, 0, 2).reshape(rows, world * width)
+        out = torch.empty((rows, world * width), device=a.device, dtype=out_dtype)
+        _interleave(gathered.view(world, rows, width), out)
+        return out
 
     out = torch.empty((rows, world * width), device=a.device, dtype=out_dtype)
     pending = None   # (work, gathered chunk, start, stop) of the chunk whose all-gather is in flight
@@ -123,7 +162,7 @@ def scaled_mm_n_sharded(a: torch.Tensor, b_slab, scale, bias_slab, out_dtype, ma
     def finish(item) -> None:
         work, gathered, start, stop = item
         work.wait()   # the compute stream waits for the collective's stream; the host does not block
-        out[start:stop].view(stop - start, world, width).copy_(gathered.view(world, stop - start, width).permute(1, 0, 2))
+        _interleave(gathered.view(world, stop - start, width), out[start:stop])
 
     for start, stop in spans:
         local = torch.empty((stop - start, width), device=a.device, dtype=out_dtype)

@@ -70,6 +70,17 @@ int launch_scaled_mm_splitk_static(const uint16_t* a, const uint8_t* b_prepacked
                                    int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
                                    bool output_bf16, int splits, feather_stream_t stream, char* error_message, size_t error_capacity);
 
+/* Leaves `sms` SMs free in every later launch of the persistent scaled_mm kernels (0 restores full grids): for a caller
+ * that overlaps the product with kernels that need SMs of their own, such as an NCCL collective on another stream (a
+ * persistent CTA holds its SM until the kernel ends). Process-wide, takes effect at the next launch. Returns the previous
+ * value. No counterpart in the reference (it has no multi-GPU path). */
+int feather_scaled_mm_set_sm_margin(int sms);
+
+/* out[r][g][:] = slabs[g][r][:] for g < world, r < rows, rows of width_bytes bytes (a multiple of 16; both pointers
+ * 16-byte aligned): turns the [world][rows][width] result of an all-gather of column slabs into the row-major
+ * [rows][world * width] matrix. Returns false for bad arguments. No counterpart in the reference. */
+bool launch_interleave_slabs(const void* slabs, void* out, int64_t world, int64_t rows, int64_t width_bytes, feather_stream_t stream);
+
 /* Diagnostic: reads and clears the record that the scaled_mm kernel's bounded device waits report into.
  * out[0] = 0 when every wait completed, else the wait site; out[1] = block index. Synchronizes the device.
  * Returns 0 on success. No counterpart in the reference (its kernels have no device-side waits). */

@@ -76,3 +76,32 @@ def test_n_sharded_all_gather_on_two_gpus_equals_one_gpu():
     for rank, verdicts in results.items():
         assert verdicts.pop("status") == (0, 0), rank
         assert all(verdicts.values()), (rank, verdicts)
+
+
+def test_interleave_slabs_kernel_equals_the_permute(cuda_device):
+    import feather_ops_b200  # noqa: F401
+    from feather_ops_b200 import shard
+
+    for world, rows, width, dtype in ((2, 7, 16, torch.bfloat16), (8, 1000, 1536, torch.bfloat16), (3, 129, 48, torch.float16), (4, 0, 64, torch.bfloat16)):
+        slabs = torch.randn((world, rows, width), device=cuda_device).to(dtype)
+        out = torch.full((rows, world * width), 3.0, device=cuda_device, dtype=dtype)
+        shard._interleave(slabs, out)
+        assert torch.equal(out, slabs.permute(1, 0, 2).reshape(rows, world * width))
+
+
+def test_sm_margin_shrinks_the_grid_and_keeps_the_result(cuda_device):
+    import feather_ops_b200 as fo
+    from feather_ops_b200 import _lib
+    from oracle import scaled_mm as osm
+
+    a, packed, scale, bias = (t.to(cuda_device) for t in osm.make_inputs(1500, 1024, 512, torch.bfloat16, torch.float8_e5m2, torch.bfloat16))
+    full = fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16)
+    lib = _lib.load()
+    assert lib.feather_scaled_mm_set_sm_margin(40) == 0
+    try:
+        for tile in ((1, 8, 4, 8, 2, 0), (2, 2, 2, 4, 4, 0)):   # the CTA-pair kernel and the one-CTA kernel
+            assert torch.equal(fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16, tile=tile), fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16, tile=tile))
+        assert torch.equal(fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16), full)   # which SM computes a tile does not change its value
+    finally:
+        assert lib.feather_scaled_mm_set_sm_margin(0) == 40
+    assert _lib.read_status("feather_scaled_mm_status") == (0, 0)
