@@ -63,6 +63,7 @@ struct Params {
     int act_stage_bytes;
     uint32_t idesc;
     int pairs;        // W is even: gather two pixels per 4-byte load
+    int staging_bytes;   // staged kernels: bytes of one slot's raw halo tile [16 channels][rows + 2][bn + 16] as TMA delivers it
 };
 
 template <bool kBf16>
@@ -100,13 +101,21 @@ __device__ __forceinline__ TileCoord tile_coord(const Params& p, int tile) {
     return t;
 }
 
-template <bool kBf16>
-__global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+// kStaged: the halo tile of a slot comes by TMA (a 4-D box over the NCHW input, channel-planar, zero filled outside the
+// image and past C_in) into a staging buffer of the slot, and the gather warps only re-lay it shared -> shared into
+// the pixel records. The copies then run slots ahead of the gather without holding registers; with loads from global
+// memory into registers the gather has one group per team in flight and runs at the pace of the memory latency.
+// A TMA box starts on a 16-byte boundary, so the box begins eight pixels left of the tile (w0 - 8, the halo's first
+// column is w0 - 1) and is sixteen pixels wider; it needs W % 8 == 0 (16-byte row pitch) and at most 128 pixels per row
+// segment (a box side is at most 256 elements).
+template <bool kBf16, bool kStaged>
+__global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* const weight_smem = smem;
     uint8_t* const act_smem = smem + kStages * kWeightStageBytes;
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(act_smem + kStages * p.act_stage_bytes);
+    uint8_t* const staging_smem = act_smem + kStages * p.act_stage_bytes;   // kStaged only (staging_bytes is 0 otherwise)
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(staging_smem + kStages * p.staging_bytes);
     uint64_t* const weight_full = bars;
     uint64_t* const act_full = weight_full + kStages;
     uint64_t* const stage_empty = act_full + kStages;
@@ -132,6 +141,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_w);
+        if constexpr (kStaged) tma_prefetch_desc(&map_x);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 2 * kAccColumns);
@@ -159,8 +169,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
                     const uint32_t phase = (it / kStages) & 1u;
                     ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes);
+                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes + (kStaged ? p.staging_bytes : 0));
                     tma_load_2d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], tc.m0 * 2, g * kWeightRows);
+                    if constexpr (kStaged) {
+                        tma_load_4d(staging_smem + s * p.staging_bytes, &map_x, &weight_full[s], tc.w0 - 8, tc.h0 - 1, g * 16, tc.b);
+                    }
                 }
             }
         }
@@ -271,7 +284,69 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
         const int items = 2 * halo_rows * per_row;
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+        if constexpr (kStaged) {
+            // The staging buffer is [16 channels][halo_rows][bn + 16 pixels]; halo column hc is staged pixel hc + 7. An item is
+            // a pixel pair (halo columns 1 + 2 e and 2 + 2 e: a 4-byte aligned load per channel) or one of the two edge
+            // pixels, for one 8-channel plane: eight loads, a byte permute, one or two 16-byte record stores. The geometry
+            // does not depend on the tile (the TMA unit has done the clipping and the zero fill), so it is decoded once.
+            const int staged_cols = p.bn + 16;
+            const int channel_pitch = halo_rows * staged_cols * 2;   // bytes between the same pixel of consecutive channels
+            int src_off[kMaxItems];
+            int dst_off[kMaxItems];
+            uint32_t pair_mask = 0;
+#pragma unroll
+            for (int j = 0; j < kMaxItems; ++j) {
+                const int item = t + j * kTeamThreads;
+                src_off[j] = 0;
+                dst_off[j] = -1;
+                if (item < items) {
+                    const int plane = item / (halo_rows * per_row);
+                    const int rem = item % (halo_rows * per_row);
+                    const int hr = rem / per_row;
+                    const int e = rem % per_row;
+                    const bool pair = e < p.bn / 2;
+                    const int hc = pair ? 1 + 2 * e : (e == p.bn / 2 ? 0 : p.bn + 1);
+                    src_off[j] = plane * 8 * channel_pitch + (hr * staged_cols + hc + 7) * 2;
+                    dst_off[j] = plane * plane_bytes + (hr * halo_cols + hc) * 16;
+                    if (pair) pair_mask |= 1u << j;
+                }
+            }
+            for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    if (static_cast<int>(it % kTeams) != team) continue;
+                    const uint32_t s = it % kStages;
+                    const uint32_t phase = (it / kStages) & 1u;
+                    // the slot's raw tile (and its weights) have landed; the records of the slot's previous use were read by
+                    // UMMAs that completed before the copy engine was allowed to refill the slot
+                    ok = guard.wait(&weight_full[s], phase, kSiteLoadFull, 3);
+                    if (!ok) break;
+                    const uint8_t* const src = staging_smem + s * p.staging_bytes;
+                    uint8_t* const dst = act_smem + s * p.act_stage_bytes;
+#pragma unroll
+                    for (int j = 0; j < kMaxItems; ++j) {
+                        if (dst_off[j] < 0) continue;
+                        uint32_t v[8];
+                        if ((pair_mask >> j) & 1u) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint32_t*>(src + src_off[j] + c * channel_pitch);
+                            *reinterpret_cast<uint4*>(dst + dst_off[j]) = make_uint4(__byte_perm(v[0], v[1], 0x5410u), __byte_perm(v[2], v[3], 0x5410u),
+                                                                                      __byte_perm(v[4], v[5], 0x5410u), __byte_perm(v[6], v[7], 0x5410u));
+                            *reinterpret_cast<uint4*>(dst + dst_off[j] + 16) = make_uint4(__byte_perm(v[0], v[1], 0x7632u), __byte_perm(v[2], v[3], 0x7632u),
+                                                                                           __byte_perm(v[4], v[5], 0x7632u), __byte_perm(v[6], v[7], 0x7632u));
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint16_t*>(src + src_off[j] + c * channel_pitch);
+                            *reinterpret_cast<uint4*>(dst + dst_off[j]) = make_uint4(__byte_perm(v[0], v[1], 0x5410u), __byte_perm(v[2], v[3], 0x5410u),
+                                                                                      __byte_perm(v[4], v[5], 0x5410u), __byte_perm(v[6], v[7], 0x5410u));
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&act_full[s]);
+                }
+            }
+        }
+        for (int tile = static_cast<int>(blockIdx.x); !kStaged && ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
             const TileCoord tc = tile_coord(p, tile);
             const uint16_t* const x_img = p.x + static_cast<int64_t>(tc.b) * p.C_in * hw;
             // The item geometry depends on the tile only: decode it once, so that the per-group work is loads,
@@ -379,6 +454,22 @@ inline bool encode_weight_map(CUtensorMap* map, const void* wp, int C_out, int g
     return encode_map(map, CU_TENSOR_MAP_DATA_TYPE_INT64, 2, wp, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+// The NCHW input as a 4-D tensor [W][H][C_in][B] with a box of `box_w` pixels x `box_h` rows x 16 channels of one image:
+// what the staged kernels fetch per 16-channel group. Coordinates outside the image (the padding ring, the rounded-up
+// box, channels past C_in) read as zero. Needs W % 8 == 0 (strides are multiples of 16 bytes).
+inline bool encode_input_map(CUtensorMap* map, const void* x, int B, int C_in, int H, int W, int box_w, int box_h, bool bf16) {
+    const uint64_t dims[4] = {static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(C_in), static_cast<uint64_t>(B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(W) * 2, static_cast<uint64_t>(H) * W * 2, static_cast<uint64_t>(C_in) * H * W * 2};
+    const uint32_t box[4] = {static_cast<uint32_t>(box_w), static_cast<uint32_t>(box_h), 16u, 1u};
+    return encode_map(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, x, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// FEATHER_CONV_STAGING_OFF=1 keeps the gather from global memory for every shape (A/B measurements). Read once per process.
+inline bool staging_off() {
+    static const bool off = env_switch("FEATHER_CONV_STAGING_OFF");
+    return off;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // CTA-pair version (tcgen05 cta_group::2) for C_out > 128: a cluster of two CTAs owns 256 output channels x
 // two output rows x 128 pixels. CTA r loads the weights of output channels [128 r, +128) and gathers the
@@ -389,26 +480,45 @@ inline bool encode_weight_map(CUtensorMap* map, const void* wp, int C_out, int g
 // memory per flop (the measured limiter of the one-CTA kernel), and the 256-wide UMMA spends a smaller share
 // of its time loading the weight operand (162 clocks per 128 x 256 x 16 against 2 x 98 for two 128-wide ones).
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kPairStages = 4;
 constexpr int kPairBN = 128;                       // pixels per CTA (one output row segment)
 constexpr int kPairHaloCols = kPairBN + 2;
 constexpr int kPairHaloRows = 3;
 constexpr int kPairPlaneBytes = kPairHaloRows * kPairHaloCols * 16;
 constexpr int kPairActStageBytes = (2 * kPairPlaneBytes + 127) / 128 * 128;
-constexpr int kPairTeams = 4;   // gather teams taking 16-channel groups in turn: that many groups' loads are in flight (2 teams: 1.19, 4: 1.24 PFLOP/s)
-constexpr int kPairTeamWarps = kGatherWarps / kPairTeams;
-constexpr int kPairItems = (2 * kPairHaloRows * (kPairBN / 2 + 2) + kPairTeamWarps * 32 - 1) / (kPairTeamWarps * 32);   // gather items per thread per slot
-static_assert(kPairStages % kPairTeams == 0, "ring depth must be a multiple of the team count");
-constexpr int kPairSmemBytes = kPairStages * (kWeightStageBytes + kPairActStageBytes) + (3 * kPairStages + 4) * 8 + 16 + 1024;
+constexpr int kPairStagedCols = kPairBN + 16;      // staged halo rows start eight pixels left of the tile (16-byte rule) and are sixteen wider
+constexpr int kPairStagingBytes = 16 * kPairHaloRows * kPairStagedCols * 2;
+static_assert(kPairStagingBytes % 128 == 0, "staging slots must keep the 128-byte alignment of TMA destinations");
 
-template <bool kBf16>
+// Pipeline shape of the two variants. Gathering from global memory: four slots, four teams of gather warps taking the
+// 16-channel groups in turn, so that four groups' loads are in flight (2 teams: 1.19, 4: 1.24 PFLOP/s). Staged by TMA:
+// three slots (a slot also holds the raw halo tile), one team: the re-layout reads shared memory and takes a fraction
+// of a group's UMMA time, and the copies run ahead by themselves.
+template <bool kStaged>
+struct PairShape {
+    static constexpr int kStages = kStaged ? 3 : 4;
+    static constexpr int kTeams = kStaged ? 1 : 4;
+    static constexpr int kTeamWarps = kGatherWarps / kTeams;
+    static constexpr int kItems = (2 * kPairHaloRows * (kPairBN / 2 + 2) + kTeamWarps * 32 - 1) / (kTeamWarps * 32);   // gather items per thread per slot
+    static constexpr int kStagingBytes = kStaged ? kPairStagingBytes : 0;
+    static constexpr int kSmemBytes = kStages * (kWeightStageBytes + kPairActStageBytes + kStagingBytes) + (3 * kStages + 4) * 8 + 16 + 1024;
+    static_assert(kStages % kTeams == 0, "ring depth must be a multiple of the team count");
+    static_assert(kSmemBytes <= 227 * 1024, "a CTA's shared memory");
+};
+
+template <bool kBf16, bool kStaged>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+    using S = PairShape<kStaged>;
+    constexpr int kPairStages = S::kStages;
+    constexpr int kPairTeams = S::kTeams;
+    constexpr int kPairTeamWarps = S::kTeamWarps;
+    constexpr int kPairItems = S::kItems;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* const weight_smem = smem;
     uint8_t* const act_smem = smem + kPairStages * kWeightStageBytes;
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(act_smem + kPairStages * kPairActStageBytes);
+    uint8_t* const staging_smem = act_smem + kPairStages * kPairActStageBytes;   // kStaged only
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(staging_smem + kPairStages * S::kStagingBytes);
     uint64_t* const weight_full = bars;                        // local: this CTA's weight rows have landed
     uint64_t* const act_full = weight_full + kPairStages;      // CTA 0 only: both CTAs' gather warps arrive here
     uint64_t* const stage_empty = act_full + kPairStages;      // signalled in both CTAs by CTA 0's commits
@@ -437,6 +547,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_w);
+        if constexpr (kStaged) tma_prefetch_desc(&map_x);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, 2 * kAccColumns);
@@ -478,8 +589,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
                     const uint32_t phase = (it / kPairStages) & 1u;
                     ok = guard.wait(&stage_empty[s], phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes);
+                    mbar_arrive_expect_tx(&weight_full[s], kWeightStageBytes + S::kStagingBytes);
                     tma_load_2d(weight_smem + s * kWeightStageBytes, &map_w, &weight_full[s], tc.m0 * 2, g * kWeightRows);
+                    if constexpr (kStaged) {
+                        // the three halo rows of this CTA's output row h0 + cta, eight pixels to the left for the 16-byte rule
+                        tma_load_4d(staging_smem + s * kPairStagingBytes, &map_x, &weight_full[s], tc.w0 - 8, tc.h0 + static_cast<int>(cta) - 1, g * 16, tc.b);
+                    }
                 }
             }
         }
@@ -588,7 +703,66 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
         const int64_t hw = static_cast<int64_t>(p.H) * p.W;
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+        if constexpr (kStaged) {
+            // Re-layout from the slot's staging buffer [16 channels][3 halo rows][144 pixels] (halo column hc is staged pixel
+            // hc + 7) into the pixel records; the geometry does not depend on the tile, the TMA unit has done the clipping.
+            constexpr int kChannelPitch = kPairHaloRows * kPairStagedCols * 2;
+            int src_off[kPairItems];
+            int dst_off[kPairItems];
+            uint32_t pair_mask = 0;
+#pragma unroll
+            for (int j = 0; j < kPairItems; ++j) {
+                const int item = t + j * kTeamThreads;
+                src_off[j] = 0;
+                dst_off[j] = -1;
+                if (item < kItems) {
+                    const int plane = item / (kPairHaloRows * kPerRow);
+                    const int rem = item % (kPairHaloRows * kPerRow);
+                    const int hr = rem / kPerRow;
+                    const int e = rem % kPerRow;
+                    const bool pair = e < kPairBN / 2;
+                    const int hc = pair ? 1 + 2 * e : (e == kPairBN / 2 ? 0 : kPairBN + 1);
+                    src_off[j] = plane * 8 * kChannelPitch + (hr * kPairStagedCols + hc + 7) * 2;
+                    dst_off[j] = plane * kPairPlaneBytes + (hr * kPairHaloCols + hc) * 16;
+                    if (pair) pair_mask |= 1u << j;
+                }
+            }
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                for (int g = 0; g < p.groups; ++g, ++it) {
+                    if (static_cast<int>(it % kPairTeams) != team) continue;
+                    const uint32_t s = it % kPairStages;
+                    const uint32_t phase = (it / kPairStages) & 1u;
+                    // this CTA's raw halo tile and weight rows of the slot have landed (the slot's records were last read by
+                    // UMMAs that completed before the copy engine was allowed to refill the slot)
+                    ok = guard.wait(&weight_full[s], phase, kSiteLoadFull, 3);
+                    if (!ok) break;
+                    const uint8_t* const src = staging_smem + s * kPairStagingBytes;
+                    uint8_t* const dst = act_smem + s * kPairActStageBytes;
+#pragma unroll
+                    for (int j = 0; j < kPairItems; ++j) {
+                        if (dst_off[j] < 0) continue;
+                        uint32_t v[8];
+                        if ((pair_mask >> j) & 1u) {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint32_t*>(src + src_off[j] + c * kChannelPitch);
+                            *reinterpret_cast<uint4*>(dst + dst_off[j]) = make_uint4(__byte_perm(v[0], v[1], 0x5410u), __byte_perm(v[2], v[3], 0x5410u),
+                                                                                      __byte_perm(v[4], v[5], 0x5410u), __byte_perm(v[6], v[7], 0x5410u));
+                            *reinterpret_cast<uint4*>(dst + dst_off[j] + 16) = make_uint4(__byte_perm(v[0], v[1], 0x7632u), __byte_perm(v[2], v[3], 0x7632u),
+                                                                                           __byte_perm(v[4], v[5], 0x7632u), __byte_perm(v[6], v[7], 0x7632u));
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint16_t*>(src + src_off[j] + c * kChannelPitch);
+                            *reinterpret_cast<uint4*>(dst + dst_off[j]) = make_uint4(__byte_perm(v[0], v[1], 0x5410u), __byte_perm(v[2], v[3], 0x5410u),
+                                                                                      __byte_perm(v[4], v[5], 0x5410u), __byte_perm(v[6], v[7], 0x5410u));
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&act_full[s]), 0));
+                }
+            }
+        }
+        for (int tile = first_tile; !kStaged && ok && tile < num_tiles; tile += tile_step) {
             const TileCoord tc = coord(tile);
             const uint16_t* const x_img = p.x + static_cast<int64_t>(tc.b) * p.C_in * hw;
             int64_t src_off[kPairItems];
@@ -677,7 +851,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
 
 template <bool kBf16>
 int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W, cudaStream_t stream) {
-    auto* kernel = &conv3x3_pair_kernel<kBf16>;
+    const bool staged = (W % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && !staging_off();
+    auto* kernel = staged ? &conv3x3_pair_kernel<kBf16, true> : &conv3x3_pair_kernel<kBf16, false>;
+    const int kPairSmemBytes = staged ? PairShape<true>::kSmemBytes : PairShape<false>::kSmemBytes;
     Params p{};
     p.x = static_cast<const uint16_t*>(x);
     p.bias = static_cast<const uint16_t*>(bias);
@@ -695,7 +871,8 @@ int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B,
 
     // once per device: the shared-memory limit and how many CTA pairs fit at once (a persistent grid must be resident as a
     // whole, and a pair needs both SMs of a TPC)
-    static PerDeviceState resident_pairs;
+    static PerDeviceState resident_pairs_of[2];
+    PerDeviceState& resident_pairs = resident_pairs_of[staged ? 1 : 0];
     const int pairs = resident_pairs.get([&] {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) return 0;
         cudaLaunchConfig_t config = {};
@@ -720,18 +897,23 @@ int launch_pair(const void* x, const void* wp, const void* bias, void* y, int B,
 
     CUtensorMap map_w;
     if (!encode_weight_map(&map_w, wp, C_out, p.groups)) return 1;
+    CUtensorMap map_x = map_w;   // unused by the kernel that gathers from global memory
+    if (staged && !encode_input_map(&map_x, x, B, C_in, H, W, kPairStagedCols, kPairHaloRows, kBf16)) return 1;
     const int64_t tiles_m = (C_out + 2 * kBlockM - 1) / (2 * kBlockM);
     const int64_t num_tiles = static_cast<int64_t>(B) * tiles_m * ((H + 1) / 2) * ((W + kPairBN - 1) / kPairBN);
     if (num_tiles > (1ll << 30)) return 1;
     const int grid = 2 * static_cast<int>(num_tiles < pairs ? num_tiles : pairs);
-    kernel<<<grid, kThreads, kPairSmemBytes, stream>>>(map_w, p);
+    kernel<<<grid, kThreads, kPairSmemBytes, stream>>>(map_w, map_x, p);
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
 template <bool kBf16>
 int launch(const void* x, const void* wp, const void* bias, void* y, int B, int C_in, int C_out, int H, int W, int bn, int rows,
            cudaStream_t stream) {
-    auto* kernel = &conv3x3_kernel<kBf16>;
+    // staged halo tiles need a 16-byte row pitch, at most 128 pixels per segment (a TMA box side is at most 256 elements)
+    // and a 16-byte aligned input
+    const bool staged = (W % 8) == 0 && bn <= 128 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && !staging_off();
+    auto* kernel = staged ? &conv3x3_kernel<kBf16, true> : &conv3x3_kernel<kBf16, false>;
     Params p{};
     p.x = static_cast<const uint16_t*>(x);
     p.bias = static_cast<const uint16_t*>(bias);
@@ -753,19 +935,22 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
     const int per_row = p.pairs ? bn / 2 + 2 : bn + 2;
     if (2 * (rows + 2) * per_row > kMaxItems * kTeamWarps * 32) return 1;
 
-    const int smem_bytes = kStages * (kWeightStageBytes + p.act_stage_bytes) + (3 * kStages + 4) * 8 + 16 + 1024;
-    static PerDeviceState smem_limit;
-    if (!smem_limit.at_least(smem_bytes, [&](int need) { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, need) == cudaSuccess; })) {
+    p.staging_bytes = staged ? (16 * (rows + 2) * (bn + 16) * 2 + 127) / 128 * 128 : 0;
+    const int smem_bytes = kStages * (kWeightStageBytes + p.act_stage_bytes + p.staging_bytes) + (3 * kStages + 4) * 8 + 16 + 1024;
+    static PerDeviceState smem_limit[2];
+    if (!smem_limit[staged ? 1 : 0].at_least(smem_bytes, [&](int need) { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, need) == cudaSuccess; })) {
         return 1;
     }
 
     CUtensorMap map_w;
     if (!encode_weight_map(&map_w, wp, C_out, p.groups)) return 1;
+    CUtensorMap map_x = map_w;   // unused by the kernel that gathers from global memory
+    if (staged && !encode_input_map(&map_x, x, B, C_in, H, W, bn + 16, rows + 2, kBf16)) return 1;
     const int64_t num_tiles = static_cast<int64_t>(B) * p.tiles_m * p.tiles_h * p.tiles_w;
     if (num_tiles > (1ll << 30)) return 1;
     const int sms = device_info().sm_count;
     const int grid = num_tiles < sms ? static_cast<int>(num_tiles) : sms;
-    kernel<<<grid, kThreads, smem_bytes, stream>>>(map_w, p);
+    kernel<<<grid, kThreads, smem_bytes, stream>>>(map_w, map_x, p);
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

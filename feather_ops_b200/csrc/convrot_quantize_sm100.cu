@@ -285,32 +285,168 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_kernel(
     }
 }
 
-// Rows up to 2 * 256 * blockDim.y wide (one round: every half warp has at most one group per row). A fixed number of
-// resident CTAs walk the rows, and a CTA asks for its next row's values before it works on the current one: with
-// one row per CTA lifetime the pass ran at the pace of one HBM latency per wave of CTAs, not at the HBM rate.
+// ---------------------------------------------------------------------------------------------------------
+// Streaming kernel for rows up to 4 * 256 * blockDim.y wide (one round: every half warp has at most one PAIR of
+// groups per row). A fixed number of resident CTAs walk the rows, and a CTA asks for its next row's values before it
+// works on the current one: with one row per CTA lifetime the pass ran at the pace of one HBM latency per wave of
+// CTAs, not at the HBM rate.
 //
-// The pass is bound by instruction issue, so the per-row bookkeeping is kept short: the warp maximum is one
-// `redux` on the bit pattern (magnitudes are non-negative, so they order like unsigned integers), the row maximum
-// one shared-memory atomic per warp and one load per thread, and the two row buffers swap roles by unrolling.
+// The pass is bound by instruction issue, so this kernel halves the instructions of the arithmetic: a half warp
+// rotates TWO adjacent groups (A and B) of its row at once, value i of A and value i of B sitting in one 64-bit
+// register pair, and every butterfly runs on the packed fp32 pair instructions of sm_100a (add.f32x2, fma.rn.f32x2:
+// two independent IEEE fp32 results per instruction, so every bit is what the scalar instruction gives). A pair
+// never holds two members of one butterfly (its halves belong to different groups), and both halves always have the
+// same member index, so the reference's operation order holds in each half. The pair also travels as a unit through
+// the transposes: 8 bytes forward (16-byte stores, 8-byte column loads), and as one 32-bit word of two rounded
+// 16-bit values back (4-byte stores, 16-byte row loads), so both transposes move twice the values per instruction.
+// The per-row bookkeeping is kept short: the warp maximum is one `redux` on the bit pattern (magnitudes are
+// non-negative, so they order like unsigned integers), the row maximum one shared-memory atomic per warp and one
+// load per thread, and the two row buffers swap roles by unrolling.
+// ---------------------------------------------------------------------------------------------------------
 constexpr int kMaxRowsPerCta = 8;
+constexpr int kPairPitchBytes = 16 * 8 + 16;           // forward transpose: a lane's sixteen 8-byte pairs + 16 bytes, so that the
+                                                       // 16-byte stores of eight lanes fall into eight different bank groups
+constexpr int kPairRegionBytes = 16 * kPairPitchBytes + 64;   // per half warp; the + 64 puts the two half warps of a warp 16 banks apart
+constexpr int kBackPitchWords = 20;                    // backward transpose: rows of sixteen words, pitch 20 (16-byte row loads conflict free)
+static_assert(16 * kBackPitchWords * 4 <= kPairRegionBytes, "the backward transpose reuses the forward buffer");
+
+using f32x2 = unsigned long long;   // two fp32 values in one 64-bit register pair: low = group A, high = group B
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(f32x2 p, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// butterfly4 on both halves of four pairs
+__device__ __forceinline__ void butterfly4_pair(f32x2& a0, f32x2& a1, f32x2& a2, f32x2& a3, f32x2 minus_two) {
+    const f32x2 sum = add2(add2(add2(a0, a1), a2), a3);
+    const f32x2 r0 = fma2(minus_two, a3, sum);
+    const f32x2 r1 = fma2(minus_two, a2, sum);
+    const f32x2 r2 = fma2(minus_two, a1, sum);
+    const f32x2 r3 = fma2(minus_two, a0, sum);
+    a0 = r0;
+    a1 = r1;
+    a2 = r2;
+    a3 = r3;
+}
+
+__device__ __forceinline__ void two_stages_pair(f32x2 (&v)[kPerLane], f32x2 minus_two) {
+#pragma unroll
+    for (int b = 0; b < kPerLane; b += 4) butterfly4_pair(v[b], v[b + 1], v[b + 2], v[b + 3], minus_two);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) butterfly4_pair(v[q], v[q + 4], v[q + 8], v[q + 12], minus_two);
+}
+
+// Both halves of a pair rounded to the input dtype: group A in the low 16 bits, group B in the high 16 bits.
+template <bool kFp16>
+__device__ __forceinline__ uint32_t round_pair(f32x2 p) {
+    float a, b;
+    unpack2(p, a, b);
+    return to_bits2<kFp16>(a, b);
+}
 
 template <bool kFp16, bool kRotate>
 struct StreamRow {
     const float* col_scale;
-    float* region;
+    uint8_t* region;         // this half warp's transpose buffer
     uint32_t* row_max_bits;  // [3][kMaxRowsPerCta]: slot t % 3 collects row t, slot (t + 1) % 3 is cleared meanwhile
     float* row_scale;
     int l;
-    int base;
+    int base_a;              // first element of this lane's sixteen values in group A; group B is kGroup further
     int local_row;
-    bool group_live;
+    bool a_live;
+    bool b_live;
     bool writes_scale;
 
-    // One row: `raw` holds its values, `q_row` / `row` say where the codes and the scale go.
-    __device__ __forceinline__ void run(const uint4 (&raw)[2], bool row_live, int8_t* q_row, int64_t row, uint32_t turn) const {
-        uint32_t packed[8];
+    // The lane's sixteen values of A and of B, paired: v[i] = (A[base_a + i], B[base_a + kGroup + i]) as fp32.
+    __device__ __forceinline__ void load_pairs(const uint4 (&raw_a)[2], const uint4 (&raw_b)[2], f32x2 (&v)[kPerLane]) const {
+        const uint32_t wa[8] = {raw_a[0].x, raw_a[0].y, raw_a[0].z, raw_a[0].w, raw_a[1].x, raw_a[1].y, raw_a[1].z, raw_a[1].w};
+        const uint32_t wb[8] = {raw_b[0].x, raw_b[0].y, raw_b[0].z, raw_b[0].w, raw_b[1].x, raw_b[1].y, raw_b[1].z, raw_b[1].w};
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+            v[i] = pack2(to_float<kFp16>(static_cast<uint16_t>(wa[i / 2] >> (16 * (i % 2)))), to_float<kFp16>(static_cast<uint16_t>(wb[i / 2] >> (16 * (i % 2)))));
+        }
+    }
+
+    // One row: `raw_a` / `raw_b` hold its values, `q_row` / `row` say where the codes and the scale go.
+    __device__ __forceinline__ void run(const uint4 (&raw_a)[2], const uint4 (&raw_b)[2], bool row_live, int8_t* q_row, int64_t row, uint32_t turn) const {
+        f32x2 v[kPerLane];
+        load_pairs(raw_a, raw_b, v);
+        uint32_t words[kPerLane];   // element i of the lane's sixteen consecutive outputs: A in the low half, B in the high half
         float amax = 0.0f;
-        produce_from<kFp16>(raw, col_scale, base, l, row_live && group_live, kRotate, region, packed, amax);
+        if constexpr (kRotate) {
+            const f32x2 minus_two = pack2(-2.0f, -2.0f);
+            two_stages_pair(v, minus_two);   // digits 0 and 1: element index = l * 16 + i
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                *reinterpret_cast<ulonglong2*>(region + l * kPairPitchBytes + 16 * c) = make_ulonglong2(v[2 * c], v[2 * c + 1]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) v[i] = *reinterpret_cast<const f32x2*>(region + i * kPairPitchBytes + 8 * l);   // now element index = i * 16 + l
+            __syncwarp();
+            two_stages_pair(v, minus_two);   // digits 2 and 3
+            uint32_t* const back = reinterpret_cast<uint32_t*>(region);
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                float a, b;
+                unpack2(v[i], a, b);
+                amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+                back[i * kBackPitchWords + l] = to_bits2<kFp16>(a, b);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 w4 = *reinterpret_cast<const uint4*>(back + l * kBackPitchWords + 4 * c);
+                words[4 * c] = w4.x;
+                words[4 * c + 1] = w4.y;
+                words[4 * c + 2] = w4.z;
+                words[4 * c + 3] = w4.w;
+            }
+            __syncwarp();
+        } else {
+            if (col_scale != nullptr) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float4 sa = a_live ? __ldg(reinterpret_cast<const float4*>(col_scale + base_a + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 sb = b_live ? __ldg(reinterpret_cast<const float4*>(col_scale + base_a + kGroup + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[4 * c] = mul2(v[4 * c], pack2(sa.x, sb.x));
+                    v[4 * c + 1] = mul2(v[4 * c + 1], pack2(sa.y, sb.y));
+                    v[4 * c + 2] = mul2(v[4 * c + 2], pack2(sa.z, sb.z));
+                    v[4 * c + 3] = mul2(v[4 * c + 3], pack2(sa.w, sb.w));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kPerLane; ++i) {
+                float a, b;
+                unpack2(v[i], a, b);
+                amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+                words[i] = to_bits2<kFp16>(a, b);
+            }
+        }
         const uint32_t warp_bits = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
         uint32_t* const slot = row_max_bits + turn * kMaxRowsPerCta + local_row;
         if (threadIdx.x == 0) atomicMax(slot, warp_bits);
@@ -320,32 +456,65 @@ struct StreamRow {
         const float row_max = round_to_input<kFp16>(__uint_as_float(*slot));
         const float divisor = fmaxf(row_max / 127.0f, 1e-30f);
         if (row_live && writes_scale) row_scale[row] = kRotate ? divisor * 0.0625f : divisor;
-        if (row_live && group_live) store_codes<kFp16>(q_row, base, packed, 1.0f / divisor);
+        if (!row_live) return;
+        // codes: clamp(rint(v / divisor)) for both halves of every word (see code_of); four words give four codes of A and four of B
+        const float inv = 1.0f / divisor;
+        const f32x2 inv2 = pack2(inv, inv);
+        const f32x2 magic2 = pack2(12582912.0f, 12582912.0f);
+        uint32_t out_a[4], out_b[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t ca[4], cb[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t word = words[4 * w + j];
+                float a, b;
+                if constexpr (kFp16) {
+                    const float2 ab = __half22float2(*reinterpret_cast<const __half2*>(&word));
+                    a = ab.x;
+                    b = ab.y;
+                } else {
+                    a = __uint_as_float(word << 16);
+                    b = __uint_as_float(word & 0xffff0000u);
+                }
+                float pa, pb;
+                unpack2(mul2(pack2(a, b), inv2), pa, pb);
+                unpack2(add2(pack2(fmaxf(pa, -127.0f), fmaxf(pb, -127.0f)), magic2), pa, pb);
+                ca[j] = __float_as_uint(pa);
+                cb[j] = __float_as_uint(pb);
+            }
+            out_a[w] = __byte_perm(__byte_perm(ca[0], ca[1], 0x0040u), __byte_perm(ca[2], ca[3], 0x0040u), 0x5410u);
+            out_b[w] = __byte_perm(__byte_perm(cb[0], cb[1], 0x0040u), __byte_perm(cb[2], cb[3], 0x0040u), 0x5410u);
+        }
+        if (a_live) *reinterpret_cast<uint4*>(q_row + base_a) = make_uint4(out_a[0], out_a[1], out_a[2], out_a[3]);
+        if (b_live) *reinterpret_cast<uint4*>(q_row + base_a + kGroup) = make_uint4(out_b[0], out_b[1], out_b[2], out_b[3]);
     }
 };
 
+// blockDim = (32, warps_per_row, rows_per_cta); half warp h of warp w owns groups 4 w + 2 h (A) and 4 w + 2 h + 1 (B) of its row.
 template <bool kFp16, bool kRotate>
 __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_stream_kernel(const uint16_t* __restrict__ x, const float* __restrict__ col_scale,
                                                                                       int8_t* __restrict__ q, float* __restrict__ row_scale, int64_t M, int K,
                                                                                       int groups) {
-    extern __shared__ __align__(16) float regions[];  // 2 * kRegionWords per warp of the CTA
+    extern __shared__ __align__(16) uint8_t pair_regions[];  // kPairRegionBytes per half warp of the CTA
     __shared__ uint32_t row_max_bits[3 * kMaxRowsPerCta];
     const int lane = static_cast<int>(threadIdx.x);
     const int half = lane >> 4;
     const int warp = static_cast<int>(threadIdx.y);
     const int warps = static_cast<int>(blockDim.y);
     const int local_row = static_cast<int>(threadIdx.z);
-    const int g = 2 * warp + half;
+    const int group_a = 4 * warp + 2 * half;
 
     StreamRow<kFp16, kRotate> ctx;
     ctx.col_scale = col_scale;
-    ctx.region = regions + ((local_row * warps + warp) * 2 + half) * kRegionWords;
+    ctx.region = pair_regions + ((local_row * warps + warp) * 2 + half) * kPairRegionBytes;
     ctx.row_max_bits = row_max_bits;
     ctx.row_scale = row_scale;
     ctx.l = lane & 15;
-    ctx.base = g * kGroup + ctx.l * kPerLane;
+    ctx.base_a = group_a * kGroup + ctx.l * kPerLane;
     ctx.local_row = local_row;
-    ctx.group_live = g < groups;
+    ctx.a_live = group_a < groups;
+    ctx.b_live = group_a + 1 < groups;
     ctx.writes_scale = warp == 0 && lane == 0;
 
     const int flat = (local_row * warps + warp) * 32 + lane;
@@ -358,21 +527,23 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_stream_
     int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.z;   // the CTA's lowest row: the same for all its threads
     const uint16_t* x_row = x + (row < M ? row : 0) * K;
     int8_t* q_row = q + (row < M ? row : 0) * K;
-    uint4 raw_a[2];
-    uint4 raw_b[2];
-    load_raw(x_row, ctx.base, ctx.group_live && row < M, raw_a);
+    uint4 raw_a0[2], raw_b0[2], raw_a1[2], raw_b1[2];
+    load_raw(x_row, ctx.base_a, ctx.a_live && row < M, raw_a0);
+    load_raw(x_row, ctx.base_a + kGroup, ctx.b_live && row < M, raw_b0);
     uint32_t turn = 0;
     while (first < M) {
-        load_raw(x_row + step_elems, ctx.base, ctx.group_live && row + row_step < M, raw_b);
-        ctx.run(raw_a, row < M, q_row, row, turn);
+        load_raw(x_row + step_elems, ctx.base_a, ctx.a_live && row + row_step < M, raw_a1);
+        load_raw(x_row + step_elems, ctx.base_a + kGroup, ctx.b_live && row + row_step < M, raw_b1);
+        ctx.run(raw_a0, raw_b0, row < M, q_row, row, turn);
         turn = turn == 2u ? 0u : turn + 1u;
         first += row_step;
         row += row_step;
         x_row += step_elems;
         q_row += step_elems;
         if (first >= M) break;
-        load_raw(x_row + step_elems, ctx.base, ctx.group_live && row + row_step < M, raw_a);
-        ctx.run(raw_b, row < M, q_row, row, turn);
+        load_raw(x_row + step_elems, ctx.base_a, ctx.a_live && row + row_step < M, raw_a0);
+        load_raw(x_row + step_elems, ctx.base_a + kGroup, ctx.b_live && row + row_step < M, raw_b0);
+        ctx.run(raw_a1, raw_b1, row < M, q_row, row, turn);
         turn = turn == 2u ? 0u : turn + 1u;
         first += row_step;
         row += row_step;
@@ -394,47 +565,47 @@ extern "C" bool launch_convrot_quantize(const void* x, const float* col_scale, i
     if (K <= 0 || K % kGroup != 0 || K > (1ll << 30) || M < 0) return false;
     if (M == 0) return true;
     const int groups = static_cast<int>(K / kGroup);
-    const int pairs = (groups + 1) / 2;
-    const int warps = pairs < kMaxWarpsPerRow ? pairs : kMaxWarpsPerRow;
-    // short rows share a CTA so that a CTA is at least eight warps
-    int rows_per_cta = 8 / warps;
-    if (rows_per_cta < 1) rows_per_cta = 1;
-    const bool cache = groups <= 2 * warps * kCachedRounds;
-    const dim3 block(32, warps, rows_per_cta);
-    const dim3 grid(static_cast<unsigned>((M + rows_per_cta - 1) / rows_per_cta));
     const uint16_t* const xp = static_cast<const uint16_t*>(x);
     const int k = static_cast<int>(K);
-    const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kRegionWords * sizeof(float);
-    if (groups <= 2 * warps) {
-        // one round per row: resident CTAs walk the rows and prefetch the next one
-        // CTAs resident per SM for this block shape (the shared-memory size follows from it), asked once per device
-        static int resident_per_sm[2][64][kMaxWarpsPerCta + 1] = {};
+    if (groups <= 4 * kMaxWarpsPerRow) {
+        // One round per row (a half warp takes two adjacent groups): resident CTAs walk the rows and prefetch the next one.
+        const int warps = (groups + 3) / 4;
+        // Small CTAs: every row costs its CTA one barrier (the row maximum), and many small CTAs per SM hide it better than
+        // few large ones (4096 x 3072: 10.6 us with one row = three warps per CTA, 11.7 with three rows, 12.6 with four).
+        // Rows narrower than three warps share a CTA so that a CTA is at least four warps.
+        const int rows_per_cta = warps >= 3 ? 1 : 4 / warps;
+        const dim3 block(32, warps, rows_per_cta);
         const int threads = 32 * warps * rows_per_cta;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev < 0 || dev >= 64) dev = 0;
-        int& per_sm = resident_per_sm[input_fp16 != 0 ? 1 : 0][dev][threads / 32];
+        const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kPairRegionBytes;
         using StreamKernel = void (*)(const uint16_t*, const float*, int8_t*, float*, int64_t, int, int);
         const StreamKernel kernel = input_fp16 != 0 ? (rotate ? convrot_quantize_stream_kernel<true, true> : convrot_quantize_stream_kernel<true, false>)
                                                     : (rotate ? convrot_quantize_stream_kernel<false, true> : convrot_quantize_stream_kernel<false, false>);
-        if (per_sm == 0) {
+        // CTAs resident per SM for this block shape (the shared-memory size follows from it), asked once per device and shape
+        static feather::PerDeviceState resident_per_sm[2][2][kMaxWarpsPerCta + 1];
+        const int per_sm = resident_per_sm[input_fp16 != 0 ? 1 : 0][rotate ? 1 : 0][threads / 32].get([&] {
+            if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess) return 0;
             int value = 0;
-            // asked for the rotating variant, the one with more registers
-            const cudaError_t occ = input_fp16 != 0
-                                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<true, true>, threads, smem)
-                                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, convrot_quantize_stream_kernel<false, true>, threads, smem);
-            if (occ != cudaSuccess || value < 1) {
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&value, kernel, threads, smem) != cudaSuccess || value < 1) {
                 (void)cudaGetLastError();
                 value = 1;
             }
-            per_sm = value;
-        }
+            return value;
+        });
+        if (per_sm <= 0) return false;
         const int64_t resident = static_cast<int64_t>(per_sm) * feather::device_info().sm_count;
         const int64_t wanted = (M + rows_per_cta - 1) / rows_per_cta;
         const dim3 stream_grid(static_cast<unsigned>(wanted < resident ? wanted : resident));
         kernel<<<stream_grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups);
         return cudaGetLastError() == cudaSuccess;
     }
+    // wider rows: several rounds per row, a half warp takes one group per round
+    const int pairs = (groups + 1) / 2;
+    const int warps = pairs < kMaxWarpsPerRow ? pairs : kMaxWarpsPerRow;
+    const int rows_per_cta = 1;
+    const bool cache = groups <= 2 * warps * kCachedRounds;
+    const dim3 block(32, warps, rows_per_cta);
+    const dim3 grid(static_cast<unsigned>((M + rows_per_cta - 1) / rows_per_cta));
+    const size_t smem = static_cast<size_t>(warps) * rows_per_cta * 2 * kRegionWords * sizeof(float);
     if (input_fp16 != 0) {
         if (cache) {
             convrot_quantize_kernel<true, true><<<grid, block, smem, stream>>>(xp, col_scale, q, row_scale, M, k, groups, rotate);
