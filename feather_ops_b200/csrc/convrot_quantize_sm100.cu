@@ -478,6 +478,9 @@ struct StreamRow {
                     b = __uint_as_float(word & 0xffff0000u);
                 }
                 float pa, pb;
+                // The clamp sits between the multiplication and the addition on purpose: with the two packed instructions back
+                // to back the assembler contracts them into one fused multiply-add, which rounds once and flips the codes
+                // whose product rounds onto a .5 boundary (measured: 4382 of 12.6 M codes of the benchmark activation).
                 unpack2(mul2(pack2(a, b), inv2), pa, pb);
                 unpack2(add2(pack2(fmaxf(pa, -127.0f), fmaxf(pb, -127.0f)), magic2), pa, pb);
                 ca[j] = __float_as_uint(pa);
