@@ -57,7 +57,7 @@ def shared_config(world: int) -> dict:
 
 
 def measured_peaks() -> dict:
-    """The driver-measured peaks of this pool (`MEASURED_PEAKS.json` beside this file), or the stated fallback."""
+    """The measured peaks of the device (`MEASURED_PEAKS.json` beside this file: copy bandwidth, cuBLAS bf16 burst and sustained), or the stated fallback."""
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             peaks = json.load(f)
@@ -156,8 +156,10 @@ def host_threads() -> int:
         try:
             os.sched_setaffinity(0, ORIGINAL_AFFINITY)
             import ctypes
+            import platform
 
-            ctypes.CDLL(None, use_errno=True).syscall(238, 0, None, 0)   # set_mempolicy(MPOL_DEFAULT)
+            if platform.machine() == "x86_64":
+                ctypes.CDLL(None, use_errno=True).syscall(238, 0, None, 0)   # set_mempolicy(MPOL_DEFAULT)
         except OSError:
             pass
         cores = len(os.sched_getaffinity(0))
@@ -340,7 +342,9 @@ def numa_local_setup(device_index: int) -> dict:
             os.sched_setaffinity(0, pick)
             info["affinity_set"] = True
         info["cpus_allowed"] = len(allowed)
-        if node >= 0:
+        import platform
+
+        if node >= 0 and platform.machine() == "x86_64":   # the system-call number below is the x86-64 one
             import ctypes
 
             libc = ctypes.CDLL(None, use_errno=True)
@@ -582,9 +586,8 @@ def run_library(args):
                 "peak": peaks["bf16_tflops"],
                 "unit": "TFLOP/s",
                 "frac": achieved / peaks["bf16_tflops"],
-                # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarized in
-                # profiles/scaled_mm_pair_4096x12288x3072_ncu.md (launches 3 and 4 of a loop over the same four rotating buffer
-                # sets: 64.24 MB read + 61.07 / 63.67 MB written). Reads are the algorithmic A + B; the writes fall short of the
+                # dram__bytes_read.sum + dram__bytes_write.sum per launch from an ncu capture of this kernel at this shape (launches
+                # 3 and 4 of a loop over the same four rotating buffer sets: 64.24 MB read + 61.07 / 63.67 MB written). Reads are the algorithmic A + B; the writes fall short of the
                 # 100.7 MB of C because the profiler flushes the L2 before the captured launch and part of C is still dirty
                 # in L2 when it ends. In the back-to-back timed region those lines are written back during the next launch, so
                 # the steady-state traffic is at least the algorithmic bytes.
@@ -623,6 +626,7 @@ def run_library(args):
             line["cpu_baseline"] = cpu_baseline_headline()
             if not args.skip_kernels:
                 bench_peaks = {"bf16_tflops": peaks["bf16_tflops"], "hbm_gbs": peaks["hbm_gbs"]}
+                benchmarks.set_device_limits(device)
                 records = benchmarks.bench_scaled_mm(device, bench_peaks)
                 records += benchmarks.bench_msweep(device, bench_peaks, include_65536=False)   # M = 65536 is the strong_m65536 object
                 records += benchmarks.bench_int8(device, bench_peaks)

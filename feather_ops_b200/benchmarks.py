@@ -19,7 +19,7 @@ import sys
 
 import torch
 
-L2_BYTES = 126 * 1024 * 1024
+L2_BYTES = 126 * 1024 * 1024   # replaced by the device's own figure in `main` / `set_device_limits`
 NOMINAL = {"bf16_tflops": 2250.0, "int8_tops": 4500.0, "hbm_gbs": 8000.0}   # B200 dense peaks
 ROUND_MS = 50.0
 ROUNDS = 5
@@ -78,6 +78,14 @@ def time_launches(launch, sets: int, rounds: int = ROUNDS, round_ms: float = ROU
         samples.append(start.elapsed_time(stop) * 1e3 / (per_graph * replays))
     return {"us": statistics.median(samples), "p20_us": _percentile(samples, 0.2), "p80_us": _percentile(samples, 0.8),
             "launches_per_round": per_graph * replays, "rounds": rounds}
+
+
+def set_device_limits(device) -> None:
+    """Take the L2 size from the device, so that "cold" means larger than twice THIS part's L2."""
+    global L2_BYTES
+    size = getattr(torch.cuda.get_device_properties(device), "L2_cache_size", 0)
+    if size:
+        L2_BYTES = int(size)
 
 
 def sets_for(bytes_per_set: int, cold: bool, cap: int = 8) -> int:
@@ -443,6 +451,7 @@ def main(argv):
         with open(argv[argv.index("--peaks") + 1]) as f:
             peaks = json.load(f)
     device = torch.device("cuda")
+    set_device_limits(device)
     chosen = [a for a in argv if a in GROUPS] or [g for g in GROUPS if g != "cells"]
     for name in chosen:
         for record in GROUPS[name](device, peaks):

@@ -533,6 +533,9 @@ __global__ void __launch_bounds__(32 * kMaxWarpsPerCta) convrot_quantize_stream_
     uint4 raw_a0[2], raw_b0[2], raw_a1[2], raw_b1[2];
     load_raw(x_row, ctx.base_a, ctx.a_live && row < M, raw_a0);
     load_raw(x_row, ctx.base_a + kGroup, ctx.b_live && row < M, raw_b0);
+    // The GEMM that consumes the codes may be launched as a programmatic dependent: let it set itself up (barriers, tensor
+    // memory, descriptors) on SMs as they fall free; it waits for this grid to complete before it reads a code or a scale.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint32_t turn = 0;
     while (first < M) {
         load_raw(x_row + step_elems, ctx.base_a, ctx.a_live && row + row_step < M, raw_a1);

@@ -527,6 +527,9 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (this CTA's halves)
         if (elect_one()) {
+            // Launched as a programmatic dependent of the quantizer, everything above (barriers, tensor memory, descriptor
+            // prefetch) has overlapped its tail; the activation codes are only read from here on.
+            grid_dependency_wait();
             Ring slot;
             bool ok = true;
             for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
@@ -596,6 +599,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool has_bias = !kTransposedB && p.bias != nullptr;
         Ring acc;
         bool ok = true;
+        grid_dependency_wait();   // the row scales come from the kernel before this one
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
             int tile_m, tile_n;
             banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
@@ -808,6 +812,12 @@ bool launch_instance(const LaunchArgs& args) {
     return cudaGetLastError() == cudaSuccess;
 }
 
+// FEATHER_INT8_PDL_OFF=1 launches the pair kernel without programmatic dependent launch (A/B measurements). Read once per process.
+inline bool pdl_off() {
+    static const bool off = env_switch("FEATHER_INT8_PDL_OFF");
+    return off;
+}
+
 template <bool kTransposedB, bool kOutBf16>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
@@ -875,8 +885,20 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
-    kernel<<<grid, kPairThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
-    return cudaGetLastError() == cudaSuccess;
+    // Programmatic dependent launch: the kernel may start while the one before it in the stream (in the ConvRot linear
+    // layer: the activation quantizer) is still running, and waits for it (griddepcontrol.wait) before it reads the
+    // activations or the row scales. After a kernel that never signals its dependents this is an ordinary launch.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(grid));
+    config.blockDim = dim3(kPairThreads);
+    config.dynamicSmemBytes = L::kDynamic;
+    config.stream = args.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_off() ? 0 : 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, map_a, map_b, p) == cudaSuccess;
 }
 
 // ---------------------------------------------------------------------------------------------------------

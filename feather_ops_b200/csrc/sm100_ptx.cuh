@@ -117,6 +117,13 @@ struct WaitGuard {
     }
 };
 
+// Programmatic dependent launch. A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running; `grid_dependency_wait` returns once that kernel has completed and its
+// memory is visible (at once when the launch carries no such attribute). `grid_launch_dependents` tells the scheduler that
+// the kernel after this one may start as soon as every CTA of this one has called it or exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Generic-proxy writes to shared memory (st.shared) -> visible to the async proxy (UMMA, TMA stores).
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -18,6 +18,9 @@ SHAPES = [
     (1, 16, 16, 8, 32), (1, 8, 32, 9, 40), (2, 24, 48, 13, 50), (1, 64, 128, 32, 128), (1, 32, 64, 17, 33), (2, 128, 256, 16, 256),
     (1, 40, 144, 7, 300), (1, 8, 8, 1, 1), (1, 16, 320, 5, 64), (3, 48, 96, 31, 96), (1, 128, 128, 64, 64), (1, 256, 128, 3, 513),
     (1, 72, 200, 11, 130), (1, 512, 512, 8, 128),
+    # widths that are multiples of 8 take their halo tiles through the copy engine: a tile narrower than the box, channels that end
+    # inside a 16-channel group, a ragged second segment, a ragged channel tile on the CTA-pair kernel, batch > 1, one row
+    (2, 24, 40, 5, 8), (1, 8, 136, 3, 16), (2, 40, 272, 9, 136), (1, 24, 130, 2, 264), (1, 136, 264, 1, 392),
 ]
 TILES = [(4, 4, 2, 4, 1), (4, 4, 2, 2, 1), (2, 2, 2, 2, 1), (4, 4, 2, 2, 2)]
 
