@@ -30,6 +30,7 @@ PROTOTYPES = {
         [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _c_int, _c_int, _c_bool, _c_bool, _c_bool, _c_int, _c_int, _ptr, _ptr, _ptr],
     ),
     "feather_scaled_mm_splitk_wide_partial_floats": (_i64, [_i64, _i64, _i64, _c_int, _c_int]),
+    "feather_scaled_mm_splitk_wide_counters": (_i64, [_i64, _i64, _c_int]),
     "feather_scaled_mm_splitk_partial_floats": (_i64, [_i64, _i64, _i64, _c_int]),
     "launch_scaled_mm_splitk_static": (
         _c_int,

@@ -131,6 +131,8 @@ def _scaled_mm_path(m, n, k):
 
     if m <= 128 and smm.warp_mma_takes(m, n, k):
         return "vector kernel" if m <= 2 and n >= 64 * smm.sm_count() else "warp-MMA kernel"
+    if smm.select_pair_splits(m, n, k) > 1:
+        return f"CTA-pair kernel, 256x256 tiles, {smm.select_pair_splits(m, n, k)} K splits"
     splits = smm.select_wide_splits(m, n, k)
     if splits > 1:
         return f"one-CTA kernel, 128x128 tiles, {splits} K splits"

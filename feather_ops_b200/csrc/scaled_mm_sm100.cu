@@ -582,7 +582,14 @@ struct PairSmem {
     static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+// kSplitK: every pair has exactly ONE work item (tile, K split) instead of walking tiles; compiled apart so that the plain
+// kernel keeps its registers. A pair writes its fp32 partial tile to scratch and counts itself in; then every CTA of the tile
+// (two per split) waits, with a limit, until all splits of its half of the rows are in, and adds the partials of ITS share
+// of the 32-column chunks in split order: the reduction is spread over all the CTAs that worked on the tile instead of one
+// CTA reading every partial through its own L2 port. All pairs of the grid are resident at once (the launcher checks), so the
+// wait cannot starve. Scratch: [tile][row half][split][chunk][4-column group][row][4] fp32; tickets: two "in" counters per tile
+// (one per row half) and one "done" counter, whose last arriver puts all three back to zero for the next launch.
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
     using L = PairSmem;
@@ -635,8 +642,13 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int tiles_n = (p.N + kPairN - 1) / kPairN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + kBlockK - 1) / kBlockK;
-    const int first_tile = static_cast<int>(blockIdx.x) / 2;
-    const int tile_step = static_cast<int>(gridDim.x) / 2;
+    // plain: pair i walks tiles i, i + pairs, ...; split K: pair i has the one item (tile i / splits, split i % splits)
+    const int item = static_cast<int>(blockIdx.x) / 2;
+    const int my_split = kSplitK ? item % p.splits : 0;
+    const int first_tile = kSplitK ? item / p.splits : item;
+    const int tile_step = kSplitK ? num_tiles : static_cast<int>(gridDim.x) / 2;
+    const int kb_begin = kSplitK ? my_split * p.kb_per_split : 0;
+    const int kb_end = kSplitK ? (kb_begin + p.kb_per_split < num_kb ? kb_begin + p.kb_per_split : num_kb) : num_kb;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (this CTA's halves)
@@ -648,7 +660,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
                 const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
                 const int n0 = tile_n * kPairN + static_cast<int>(cta) * kPairHalfN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
                     mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
@@ -669,7 +681,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc.idx * kPairN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 1) &&
                          guard.wait(&operand_full[operand.idx], operand.phase, kSiteOperandFull);
                     if (!ok) break;
@@ -679,7 +691,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k) {
                         umma_f16_pair(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
-                                      (kb | k) != 0 ? 1u : 0u);
+                                      (kb != kb_begin || k != 0) ? 1u : 0u);
                     }
 #pragma unroll
                     for (uint32_t dst = 0; dst < 2; ++dst) {
@@ -712,6 +724,27 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
             uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+            if constexpr (kSplitK) {
+                // this pair's partial of the tile goes to scratch; a warp writes 512 consecutive bytes per instruction
+                float* const part = p.partials + ((static_cast<int64_t>(tile) * 2 + cta) * p.splits + my_split) * (kBlockM * kPairN) + (quarter * 32 + lane) * 4;
+#pragma unroll 1
+                for (int c = 0; c < kPairN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        __stcg(reinterpret_cast<uint4*>(part + (c * 8 + g) * (kBlockM * 4)), make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]));
+                    }
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: this CTA's half of the partial is out
+                if (threadIdx.x == kFirstEpilogueWarp * 32) {
+                    __threadfence();
+                    atomicAdd(p.counters + tile * 2 + static_cast<int>(cta), 1u);
+                }
+                break;   // one item per pair
+            }
 #pragma unroll 1
             for (int c = 0; c < kPairN / 32; ++c) {
                 uint32_t v[32];
@@ -775,7 +808,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         bool ok = true;
         uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
                 if (turn == static_cast<uint32_t>(team)) {
                     ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2) &&
                          guard.wait(&operand_empty[operand.idx], operand.phase ^ 1u, kSiteOperandEmpty);
@@ -810,6 +843,75 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 turn = turn + 1 == kPairTeams ? 0 : turn + 1;
                 slot.advance(kPairLoadStages);
                 operand.advance(kPairOperandStages);
+            }
+        }
+    }
+
+    if constexpr (kSplitK) {
+        // Every role loop has ended. Wait until all splits of this CTA's half of the tile are in (bounded), then add the
+        // partials of this CTA's share of the chunks: chunk c belongs to split c % splits. Twenty warps, one row per thread.
+        __syncthreads();
+        const int tile = first_tile;
+        if (threadIdx.x == 0 && !guard.aborted()) {
+            const uint32_t* const in_counter = p.counters + tile * 2 + static_cast<int>(cta);
+            const long long start = clock64();
+            while (true) {
+                uint32_t seen;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(in_counter) : "memory");
+                if (seen >= static_cast<uint32_t>(p.splits)) break;
+                if (clock64() - start > kWaitLimitCycles) {
+                    guard.give_up(kSiteStore, 7);
+                    break;
+                }
+                __nanosleep(64);
+            }
+            __threadfence();
+        }
+        __syncthreads();
+        if (!guard.aborted() && threadIdx.x >= kFirstEpilogueWarp * 32) {
+            constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
+            const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
+            const int group = t / kBlockM;
+            const int r = t % kBlockM;
+            int tile_m, tile_n;
+            banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+            const int row = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM + r;
+            const int n0 = tile_n * kPairN;
+            const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+            const float* const half_base = p.partials + (static_cast<int64_t>(tile) * 2 + cta) * p.splits * (kBlockM * kPairN) + r * 4;
+            int owned = 0;
+            for (int c = my_split; c < kPairN / 32; c += p.splits, ++owned) {
+                if (group >= kGroups || owned % kGroups != group) continue;
+                float sum[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                for (int sp = 0; sp < p.splits; ++sp) {   // split order: the sum does not depend on who adds it
+                    const float* const src = half_base + static_cast<int64_t>(sp) * (kBlockM * kPairN);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + g) * (kBlockM * 4)));
+                        sum[4 * g] += x.x;
+                        sum[4 * g + 1] += x.y;
+                        sum[4 * g + 2] += x.z;
+                        sum[4 * g + 3] += x.w;
+                    }
+                }
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
+                finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // this CTA has read every partial it needs: the last of the tile's 2 x splits CTAs resets the tickets
+            __threadfence();
+            uint32_t* const done = p.counters + 2 * num_tiles + tile;
+            if (atomicAdd(done, 1u) == static_cast<uint32_t>(2 * p.splits - 1)) {
+                p.counters[tile * 2] = 0u;
+                p.counters[tile * 2 + 1] = 0u;
+                *done = 0u;
             }
         }
     }
@@ -1212,10 +1314,15 @@ inline bool skinny_wmma_off() {
     return off;
 }
 
-template <bool kE5M2, bool kOperandBf16, bool kOutBf16>
+// Pair tiles (256 x 256) of a problem, and whether a K split of the pair kernel fits: every (tile, split) item needs a pair
+// of its own, all resident at once, because the CTAs of a tile wait for one another's partials.
+inline int64_t pair_tiles(int64_t M, int64_t N) { return ((M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((N + kPairN - 1) / kPairN); }
+constexpr int kPairMaxSplits = kPairN / 32;   // a split owns at least one 32-column chunk of the reduction
+
+template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
-    auto* kernel = &scaled_mm_pair_kernel<kE5M2, kOperandBf16, kOutBf16>;
+    auto* kernel = &scaled_mm_pair_kernel<kE5M2, kOperandBf16, kOutBf16, kSplitK>;
     // Set-up once per device: the shared-memory limit, and how many CTA pairs can be resident at once. A persistent
     // grid must not exceed that: pairs need both SMs of a TPC, and parts with an odd number of enabled SMs in some
     // TPCs hold fewer pairs than sm_count / 2.
@@ -1273,16 +1380,29 @@ bool launch_pair_instance(const LaunchArgs& args) {
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int margin_pairs = (g_sm_margin.load(std::memory_order_relaxed) + 1) / 2;
     const int usable = pairs - margin_pairs > 0 ? pairs - margin_pairs : 1;
+    if constexpr (kSplitK) {
+        const int num_kb = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
+        p.splits = effective_splits(args.K, args.splits < kPairMaxSplits ? args.splits : kPairMaxSplits);
+        p.kb_per_split = (num_kb + p.splits - 1) / p.splits;
+        p.partials = args.partials;
+        p.counters = args.counters;
+        p.band = p.tiles_m;   // one item per pair: no walk to order
+        const int64_t items = static_cast<int64_t>(num_tiles) * p.splits;
+        if (p.splits < 2 || items > usable) return false;   // the caller falls back to the one-CTA split kernel
+        kernel<<<static_cast<unsigned>(2 * items), kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
+        return cudaGetLastError() == cudaSuccess;
+    }
     const int grid = 2 * (num_tiles < usable ? num_tiles : usable);
     kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
     return cudaGetLastError() == cudaSuccess;
 }
 
-bool launch_pair(const LaunchArgs& args) {
+// `split`: the K-split variant (one (tile, split) item per pair); false when the items do not fit the resident pairs.
+bool launch_pair(const LaunchArgs& args, bool split = false) {
     const bool operand_bf16 = args.a_bf16;
 #define FEATHER_SMM_PAIR_CASE(E5, OB, OUT)                                 \
     if (args.e5m2 == E5 && operand_bf16 == OB && args.out_bf16 == OUT) {    \
-        return launch_pair_instance<E5, OB, OUT>(args);                     \
+        return split ? launch_pair_instance<E5, OB, OUT, true>(args) : launch_pair_instance<E5, OB, OUT, false>(args); \
     }
     FEATHER_SMM_PAIR_CASE(true, false, true)
     FEATHER_SMM_PAIR_CASE(true, false, false)
@@ -1824,7 +1944,20 @@ extern "C" bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b
     args.splits = splits;
     args.partials = partials;
     args.counters = counters;
+    if (block_n == 256 && M > smm::kBlockM && smm::pair_kernel_enabled() && smm::effective_splits(K, splits) > 1) {
+        // more than one row tile: CTA pairs, one (256 x 256 tile, split) item per pair, when all items fit the device at once
+        if (smm::launch_pair(args, true)) return true;
+        (void)cudaGetLastError();
+    }
     return block_n == 256 ? smm::launch_for_block_n<256>(args) : smm::launch_for_block_n<128>(args);
+}
+
+// Number of uint32 tickets `launch_scaled_mm_splitk_wide` needs in `counters` (zero before the first launch).
+extern "C" int64_t feather_scaled_mm_splitk_wide_counters(int64_t M, int64_t N, int block_n) {
+    if (M <= 0 || N <= 0 || (block_n != 128 && block_n != 256)) return 0;
+    const int64_t one_cta = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
+    const int64_t pair = block_n == 256 ? 3 * feather::smm::pair_tiles(M, N) : 0;   // two "in" counters and one "done" counter per pair tile
+    return one_cta > pair ? one_cta : pair;
 }
 
 // Floats of `partials` scratch that `launch_scaled_mm_splitk_wide` needs: whole 128 x block_n tiles per split
@@ -1832,7 +1965,9 @@ extern "C" bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b
 extern "C" int64_t feather_scaled_mm_splitk_wide_partial_floats(int64_t M, int64_t N, int64_t K, int block_n, int splits) {
     if (M <= 0 || N <= 0 || K <= 0 || (block_n != 128 && block_n != 256)) return 0;
     const int effective = feather::smm::effective_splits(K, splits);
-    const int64_t tiles = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
+    int64_t tiles = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
+    // the CTA-pair kernel (block_n 256, more than one row tile) keeps whole 256 x 256 tiles: two 128-row halves per pair tile
+    if (block_n == 256 && 2 * feather::smm::pair_tiles(M, N) > tiles) tiles = 2 * feather::smm::pair_tiles(M, N);
     return effective > 1 ? static_cast<int64_t>(effective) * tiles * feather::smm::kBlockM * block_n : 0;
 }
 

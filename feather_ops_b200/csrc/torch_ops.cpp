@@ -133,7 +133,7 @@ void scaled_mm_splitk(const Tensor& a, const Tensor& b_prepacked, const std::opt
     const int64_t scratch = block_n == 64 ? feather_scaled_mm_splitk_partial_floats(M, N, K, static_cast<int>(splits))
                                           : feather_scaled_mm_splitk_wide_partial_floats(M, N, K, static_cast<int>(block_n), static_cast<int>(splits));
     STD_TORCH_CHECK(partials.numel() >= scratch, "partials is too small");
-    const int64_t tickets = block_n == 64 ? (N + 63) / 64 : ((M + 127) / 128) * ((N + block_n - 1) / block_n);
+    const int64_t tickets = block_n == 64 ? (N + 63) / 64 : feather_scaled_mm_splitk_wide_counters(M, N, static_cast<int>(block_n));
     STD_TORCH_CHECK(counters.numel() >= tickets, "counters must have one element per tile");
     if (scale.has_value()) {
         STD_TORCH_CHECK(scale->is_cuda() && scale->scalar_type() == ScalarType::Float && scale->numel() == 1, "scale must be one float32 on the device");

@@ -127,6 +127,32 @@ def select_wide_splits(M: int, N: int, K: int) -> int:
     return splits
 
 
+_PAIR_SPLIT_MAX = 8          # a split owns at least one 32-column chunk of a 256-wide tile's reduction
+_PAIR_SPLIT_MIN_K_BLOCKS = 64   # 64-deep k blocks (K >= 4096); from 48 (K >= 3072) with more than 256 rows
+
+
+def select_pair_splits(M: int, N: int, K: int) -> int:
+    """K splits of the CTA-pair kernel (1 = none), for more than 128 rows and so few 256 x 256 tiles that at least half of
+    the CTA pairs would idle. Every (tile, split) item gets a pair of its own, all resident at once, and every CTA of a tile
+    adds its share of the columns, so the reduction is spread over the SMs that worked on the tile. A pair tile pulls half
+    as many bytes per flop through an SM's L2 port as a 128 x 128 tile, which is what bounds these shapes; the price is
+    a fixed cost of about 14 us per launch, so short contractions stay on the one-CTA kernels. Measured against the
+    choice before (us): 256 x 4096 x 4096 23.3 -> 20.1, 512 x 4096 x 4096 29.8 -> 24.8, 256 x 5120 x 5120 37.1 -> 24.0,
+    1024 x 1536 x 6144 42.2 -> 25.6, 512 x 3072 x 12288 69.6 -> 38.5, 768 x 2048 x 8192 46.7 -> 30.4; level at K = 3072
+    with at most 256 rows (18.3 / 18.5) and slower below K = 3072 (256 x 2560 x 2560 16.4 -> 17.0, 512 x 1280 x 1280 9.5 -> 16.1)."""
+    if M <= 128:
+        return 1
+    pairs = sm_count() // 2
+    tiles = -(-M // 256) * -(-N // 256)
+    k_blocks = -(-K // 64)
+    splits = max(1, min(_PAIR_SPLIT_MAX, pairs // tiles if tiles else 1, k_blocks // 8))
+    if splits < 2:
+        return 1
+    if k_blocks < _PAIR_SPLIT_MIN_K_BLOCKS and not (k_blocks >= 48 and M > 256):
+        return 1
+    return splits
+
+
 _TICKETS: dict = {}
 
 
@@ -161,6 +187,12 @@ def _scaled_mm_auto(a: torch.Tensor, b_prepacked: torch.Tensor, scale: torch.Ten
     if 0 < m <= _SKINNY_MAX_M and warp_mma_takes(m, n, k):
         # the launcher runs these on the vector or the warp-MMA kernel when the tile is 64 wide: no scratch to allocate
         _launch(a, b_prepacked, scale, bias, out, _TILE_N64)
+        return
+    splits = select_pair_splits(m, n, k)
+    if splits > 1:
+        pair_tiles = -(-m // 256) * -(-n // 256)
+        partials = torch.empty(splits * pair_tiles * 256 * 256, device=a.device, dtype=torch.float32)
+        torch.ops.feather_ops.scaled_mm_splitk.default(a, b_prepacked, scale, bias, out, partials, _ticket_counters(a.device, 64 * 3 * pair_tiles), splits, 256)
         return
     splits = select_wide_splits(m, n, k)
     if splits > 1:

@@ -43,10 +43,12 @@ bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prepacked, cons
 
 /* launch_scaled_mm_splitk for taller problems: the persistent one-CTA kernel with 128 x block_n tiles (block_n = 128 or
  * 256) walks (tile, K split) work items, so a product with fewer tiles than SMs (a few hundred rows) still uses all of
- * them; the CTA that draws a tile's last ticket adds the partials in split order. Any M.
+ * them; the CTA that draws a tile's last ticket adds the partials in split order. Any M. With block_n = 256, more than
+ * 128 rows and at most as many (256 x 256 tile, split) items as CTA pairs fit the device at once, the CTA-pair kernel runs
+ * instead, one item per pair, and every CTA of a tile adds its share of the columns (at most 8 splits).
  * partials: scratch of feather_scaled_mm_splitk_wide_partial_floats(M, N, K, block_n, splits) floats.
- * counters: ceil(M / 128) * ceil(N / block_n) uint32, zero before the first launch, left zero by every launch.
- * No counterpart in the reference's C ABI. */
+ * counters: feather_scaled_mm_splitk_wide_counters(M, N, block_n) uint32, zero before the first launch, left zero by every
+ * launch. The result does not depend on the order in which the CTAs finish. No counterpart in the reference's C ABI. */
 bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b_prepacked, const float* scale, const uint16_t* bias, uint16_t* c,
                                   int64_t M, int64_t N, int64_t K, int has_scale, int has_bias, bool use_fp8_e5m2, bool a_bf16,
                                   bool output_bf16, int block_n, int splits, float* partials, uint32_t* counters, feather_stream_t stream);
@@ -54,6 +56,9 @@ bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b_prepacked,
 /* Number of floats of `partials` scratch launch_scaled_mm_splitk_wide needs: whole tiles per split (0 when the request
  * collapses to one split). No counterpart in the reference. */
 int64_t feather_scaled_mm_splitk_wide_partial_floats(int64_t M, int64_t N, int64_t K, int block_n, int splits);
+
+/* Number of uint32 tickets launch_scaled_mm_splitk_wide needs in `counters`. No counterpart in the reference. */
+int64_t feather_scaled_mm_splitk_wide_counters(int64_t M, int64_t N, int block_n);
 
 /* Number of floats of `partials` scratch launch_scaled_mm_splitk needs (0 when the request collapses to one split).
  * No counterpart in the reference. */

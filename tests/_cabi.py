@@ -104,7 +104,7 @@ def scaled_mm_splitk_wide(a, b_prepacked, scale, bias, out_dtype, block_n, split
     if partials is None:
         partials = guarded_empty((max(int(floats), 1),), a.device, torch.float32)
     if counters is None:
-        counters = torch.zeros(-(-m // 128) * -(-n // block_n), device=a.device, dtype=torch.int32)
+        counters = torch.zeros(max(int(lib.feather_scaled_mm_splitk_wide_counters(m, n, block_n)), 1), device=a.device, dtype=torch.int32)
     assert partials.numel() >= floats
     c = guarded_empty((m, n), a.device, out_dtype)
     ok = lib.launch_scaled_mm_splitk_wide(

@@ -237,9 +237,13 @@ def test_split_k_of_the_one_cta_kernel_is_what_the_heuristic_picks_for_few_tiles
     assert sm.select_wide_splits(512, 2560, 2560) == 1 and sm.select_wide_splits(128, 12288, 3072) == 1
     assert sm.select_wide_splits(128, 3072, 12288) == 6 and sm.select_wide_splits(100, 5120, 5120) == 3 and sm.select_wide_splits(128, 4096, 4096) == 4
     assert sm.select_wide_splits(48, 8192, 3072) == 1 and sm.select_wide_splits(64, 5120, 5120) == 3
+    # more than 128 rows and few 256 x 256 tiles: K splits on CTA pairs, from K = 4096 (K = 3072 with more than 256 rows)
+    assert sm.select_pair_splits(256, 4096, 4096) == 4 and sm.select_pair_splits(512, 3072, 12288) == 3 and sm.select_pair_splits(768, 2048, 8192) == 3
+    assert sm.select_pair_splits(256, 3072, 3072) == 1 and sm.select_pair_splits(512, 3072, 3072) == 3 and sm.select_pair_splits(512, 1280, 1280) == 1
+    assert sm.select_pair_splits(128, 4096, 4096) == 1 and sm.select_pair_splits(4096, 12288, 3072) == 1 and sm.select_pair_splits(1024, 4096, 4096) == 1
     assert sm.warp_mma_takes(16, 4096, 4096) and sm.warp_mma_takes(64, 3072, 3072) and not sm.warp_mma_takes(64, 12288, 3072)
     assert not sm.warp_mma_takes(32, 3072, 12288) and not sm.warp_mma_takes(8, 256, 4096)
-    for m, n, k in [(100, 2064, 1040), (65, 528, 4096), (48, 1040, 528), (128, 1296, 272), (33, 3072, 8192 + 64)]:
+    for m, n, k in [(100, 2064, 1040), (65, 528, 4096), (48, 1040, 528), (128, 1296, 272), (33, 3072, 8192 + 64), (300, 1040, 4112), (513, 272, 8192)]:
         a, packed, scale, bias = osm.make_inputs(m, n, k, torch.float16, torch.float8_e4m3fn, torch.float16, seed=m + n)
         ref = osm.scaled_mm_f32(a, packed, scale, bias, torch.float16, b_prepacked=True)
         dev = [t.to(cuda_device) for t in (a, packed, scale, bias)]
