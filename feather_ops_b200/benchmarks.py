@@ -36,6 +36,19 @@ def _percentile(samples, q):
     return ordered[lo] + (ordered[hi] - ordered[lo]) * (pos - lo)
 
 
+def wait_records() -> dict:
+    """The records of the kernels' bounded waits that are not `(0, 0)`: `{}` in a healthy run. A wait that ran out costs
+    seconds, so a time measured over it is not a kernel time; every timed case carries this beside its number."""
+    from . import _lib
+
+    found = {}
+    for symbol in ("feather_scaled_mm_status", "feather_int8_mm_status", "feather_conv3x3_status"):
+        site, block = _lib.read_status(symbol)
+        if site or block:
+            found[symbol] = [site, block]
+    return found
+
+
 def time_launches(launch, sets: int, rounds: int = ROUNDS, round_ms: float = ROUND_MS) -> dict:
     """`{"us": median, "p20_us", "p80_us", "launches_per_round", "rounds"}` for `launch(i)`, which enqueues one launch
     on buffer set `i % sets`. A round replays a CUDA graph of up to GRAPH_LAUNCHES_MAX launches (a multiple of `sets`)
@@ -77,7 +90,7 @@ def time_launches(launch, sets: int, rounds: int = ROUNDS, round_ms: float = ROU
         torch.cuda.synchronize()
         samples.append(start.elapsed_time(stop) * 1e3 / (per_graph * replays))
     return {"us": statistics.median(samples), "p20_us": _percentile(samples, 0.2), "p80_us": _percentile(samples, 0.8),
-            "launches_per_round": per_graph * replays, "rounds": rounds}
+            "launches_per_round": per_graph * replays, "rounds": rounds, "wait_status": wait_records()}
 
 
 def set_device_limits(device) -> None:
@@ -103,6 +116,8 @@ def _rates(record: dict, timing: dict, *, flop: float | None, algorithmic_bytes:
     us = timing["us"]
     record.update(us=_round(us, 2), p20_us=_round(timing["p20_us"], 2), p80_us=_round(timing["p80_us"], 2), launches_per_round=timing["launches_per_round"],
                   rounds=timing["rounds"], bound=bound, flop=flop, algorithmic_bytes=algorithmic_bytes)
+    if timing.get("wait_status"):
+        record["wait_status"] = timing["wait_status"]
     if us is None:
         return record
     if flop is not None:
@@ -133,6 +148,8 @@ def _scaled_mm_path(m, n, k):
         return "vector kernel" if m <= 2 and n >= 64 * smm.sm_count() else "warp-MMA kernel"
     if smm.select_pair_splits(m, n, k) > 1:
         return f"CTA-pair kernel, 256x256 tiles, {smm.select_pair_splits(m, n, k)} K splits"
+    if smm.select_row_tile_splits_256(m, n, k) > 1:
+        return f"one-CTA kernel, 128x256 tiles, {smm.select_row_tile_splits_256(m, n, k)} K splits"
     splits = smm.select_wide_splits(m, n, k)
     if splits > 1:
         return f"one-CTA kernel, 128x128 tiles, {splits} K splits"

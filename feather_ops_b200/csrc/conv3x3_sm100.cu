@@ -127,12 +127,20 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
     const WaitGuard guard{abort_flag, g_status};
+    // A parity wait tells "the phase I need has completed" from "the phase before it has not" only for a waiter that
+    // visits every use of a slot, or whose barriers complete in the order of the uses. The staged gather waits on the
+    // copy engine's barriers, which complete in any order across slots: a team that skipped a use of a slot (two teams
+    // over three slots) could run a whole ring ahead of a late copy and take the slot's previous phase for its own. So
+    // the staged gather is one team that visits every use. The gather from global memory waits on the MMA commits, which
+    // arrive in issue order, and keeps two teams.
+    constexpr int kMyTeams = kStaged ? 1 : kTeams;
+    constexpr int kMyTeamWarps = kGatherWarps / kMyTeams;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&weight_full[s], 1);
-            mbar_init(&act_full[s], kTeamWarps);
+            mbar_init(&act_full[s], kMyTeamWarps);
             mbar_init(&stage_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -274,9 +282,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
         }
     } else {
         // ------------------------------------------------------------------ activation gather warps
-        const int team = (warp - kFirstGatherWarp) / kTeamWarps;
-        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kTeamWarps) * 32;
-        constexpr int kTeamThreads = kTeamWarps * 32;
+        const int team = (warp - kFirstGatherWarp) / kMyTeamWarps;
+        const int t = static_cast<int>(threadIdx.x) - (kFirstGatherWarp + team * kMyTeamWarps) * 32;
+        constexpr int kTeamThreads = kMyTeamWarps * 32;
         const int64_t hw = static_cast<int64_t>(p.H) * p.W;
         // Work items of one slot. With `pairs`: per (plane, halo row) the halo columns 1..BN as BN / 2 aligned
         // pixel pairs, then the two edge columns 0 and BN + 1 as single pixels. Without: every column alone.
@@ -313,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
             }
             for (int tile = static_cast<int>(blockIdx.x); ok && tile < num_tiles; tile += static_cast<int>(gridDim.x)) {
                 for (int g = 0; g < p.groups; ++g, ++it) {
-                    if (static_cast<int>(it % kTeams) != team) continue;
+                    static_assert(kMyTeams == 1, "the staged gather visits every use of a slot");
                     const uint32_t s = it % kStages;
                     const uint32_t phase = (it / kStages) & 1u;
                     // the slot's raw tile (and its weights) have landed; the records of the slot's previous use were read by

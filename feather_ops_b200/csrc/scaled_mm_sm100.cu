@@ -374,10 +374,18 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == kFirstEpilogueWarp * 32) {
-                    const uint32_t ticket = atomicAdd(p.counters + tile, 1u);
-                    const bool last = ticket == static_cast<uint32_t>(splits - 1);
-                    if (last) p.counters[tile] = 0u;  // every other split has drawn its ticket: ready for the next launch
-                    *last_flag = last ? 1u : 0u;
+                    if (p.single_item != 0) {
+                        // one item per CTA: count this split in; the tile's CTAs share the reduction after the role loops
+                        if (got) {
+                            __threadfence();
+                            atomicAdd(p.counters + tile, 1u);
+                        }
+                    } else {
+                        const uint32_t ticket = atomicAdd(p.counters + tile, 1u);
+                        const bool last = ticket == static_cast<uint32_t>(splits - 1);
+                        if (last) p.counters[tile] = 0u;  // every other split has drawn its ticket: ready for the next launch
+                        *last_flag = last ? 1u : 0u;
+                    }
                 }
                 uint32_t any_failed;
                 asm volatile(
@@ -491,43 +499,71 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     if constexpr (kSplitK) {
         if (p.single_item != 0 && splits > 1) {
-            // One item per CTA: every role loop has ended, so all warps but the first two add the partials of the tile
-            // whose last ticket this CTA drew. Four epilogue warps alone keep too few loads in flight (about 16 GB/s).
+            // One item per CTA, all of them resident at once: every role loop has ended. Wait (bounded) until every split of the
+            // tile is in, then add the partials of THIS CTA's share of the 32-column chunks (chunk c belongs to split c % splits)
+            // in split order, twenty warps at work. One CTA adding a whole tile reads all its partials through its own L2 port
+            // (six splits of a 128 x 128 tile: 384 KB, 6 us); spread over the tile's CTAs it is a sixth of that each.
             __syncthreads();
-            if (!guard.aborted() && *last_flag != 0u && threadIdx.x >= kFirstEpilogueWarp * 32) {
+            const int tile = static_cast<int>(blockIdx.x) / splits;
+            const int split = static_cast<int>(blockIdx.x) - tile * splits;
+            if (threadIdx.x == 0 && !guard.aborted()) {
+                const uint32_t* const in_counter = p.counters + tile;
+                const long long start = clock64();
+                while (true) {
+                    uint32_t seen;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(in_counter) : "memory");
+                    if (seen >= static_cast<uint32_t>(splits)) break;
+                    if (clock64() - start > kWaitLimitCycles) {
+                        guard.give_up(kSiteStore, 7);
+                        break;
+                    }
+                    __nanosleep(64);
+                }
+                __threadfence();
+            }
+            __syncthreads();
+            if (!guard.aborted() && threadIdx.x >= kFirstEpilogueWarp * 32) {
                 constexpr int kTileFloats = kBlockM * BN;
                 constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
                 const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
                 const int group = t / kBlockM;
                 const int r = t % kBlockM;
-                const int tile = static_cast<int>(blockIdx.x) / splits;
                 const int row = (tile % p.tiles_m) * kBlockM + r;
                 const int n0 = (tile / p.tiles_m) * BN;
                 const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
                 uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
-                __threadfence();
-                if (group < kGroups) {
+                int owned = 0;
 #pragma unroll 1
-                    for (int c = group; c < BN / 32; c += kGroups) {
-                        float sum[32];
+                for (int c = split; c < BN / 32; c += splits, ++owned) {
+                    if (group >= kGroups || owned % kGroups != group) continue;
+                    float sum[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
-                        for (int sp = 0; sp < splits; ++sp) {  // split order: the sum does not depend on which CTA came last
-                            const float* const src = p.partials + (static_cast<int64_t>(sp) * num_tiles + tile) * kTileFloats + r * 4;
+                    for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                    for (int sp = 0; sp < splits; ++sp) {  // split order: the sum does not depend on who adds it
+                        const float* const src = p.partials + (static_cast<int64_t>(sp) * num_tiles + tile) * kTileFloats + r * 4;
 #pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + g) * (kBlockM * 4)));
-                                sum[4 * g] += x.x;
-                                sum[4 * g + 1] += x.y;
-                                sum[4 * g + 2] += x.z;
-                                sum[4 * g + 3] += x.w;
-                            }
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (c * 8 + g) * (kBlockM * 4)));
+                            sum[4 * g] += x.x;
+                            sum[4 * g + 1] += x.y;
+                            sum[4 * g + 2] += x.z;
+                            sum[4 * g + 3] += x.w;
                         }
-                        uint32_t v[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
-                        finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
                     }
+                    uint32_t v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
+                    finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
+                }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                // this CTA has read what it needs: the last of the tile's CTAs puts both tickets back to zero
+                __threadfence();
+                uint32_t* const done = p.counters + num_tiles + tile;
+                if (atomicAdd(done, 1u) == static_cast<uint32_t>(splits - 1)) {
+                    p.counters[tile] = 0u;
+                    *done = 0u;
                 }
             }
         }
@@ -1955,8 +1991,9 @@ extern "C" bool launch_scaled_mm_splitk_wide(const uint16_t* a, const uint8_t* b
 // Number of uint32 tickets `launch_scaled_mm_splitk_wide` needs in `counters` (zero before the first launch).
 extern "C" int64_t feather_scaled_mm_splitk_wide_counters(int64_t M, int64_t N, int block_n) {
     if (M <= 0 || N <= 0 || (block_n != 128 && block_n != 256)) return 0;
-    const int64_t one_cta = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
-    const int64_t pair = block_n == 256 ? 3 * feather::smm::pair_tiles(M, N) : 0;   // two "in" counters and one "done" counter per pair tile
+    // the one-CTA kernel: an "in" and a "done" counter per 128 x block_n tile; the CTA-pair kernel: two "in" counters (one per row half) and a "done" counter per 256 x 256 tile
+    const int64_t one_cta = 2 * ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
+    const int64_t pair = (block_n == 256 && M > feather::smm::kBlockM) ? 3 * feather::smm::pair_tiles(M, N) : 0;
     return one_cta > pair ? one_cta : pair;
 }
 
@@ -1967,7 +2004,7 @@ extern "C" int64_t feather_scaled_mm_splitk_wide_partial_floats(int64_t M, int64
     const int effective = feather::smm::effective_splits(K, splits);
     int64_t tiles = ((M + feather::smm::kBlockM - 1) / feather::smm::kBlockM) * ((N + block_n - 1) / block_n);
     // the CTA-pair kernel (block_n 256, more than one row tile) keeps whole 256 x 256 tiles: two 128-row halves per pair tile
-    if (block_n == 256 && 2 * feather::smm::pair_tiles(M, N) > tiles) tiles = 2 * feather::smm::pair_tiles(M, N);
+    if (block_n == 256 && M > feather::smm::kBlockM && 2 * feather::smm::pair_tiles(M, N) > tiles) tiles = 2 * feather::smm::pair_tiles(M, N);
     return effective > 1 ? static_cast<int64_t>(effective) * tiles * feather::smm::kBlockM * block_n : 0;
 }
 

@@ -43,7 +43,8 @@ bool launch_scaled_mm_splitk(const uint16_t* a, const uint8_t* b_prepacked, cons
 
 /* launch_scaled_mm_splitk for taller problems: the persistent one-CTA kernel with 128 x block_n tiles (block_n = 128 or
  * 256) walks (tile, K split) work items, so a product with fewer tiles than SMs (a few hundred rows) still uses all of
- * them; the CTA that draws a tile's last ticket adds the partials in split order. Any M. With block_n = 256, more than
+ * them; with more items than SMs the CTA that draws a tile's last ticket adds the partials in split order, with at most
+ * one item per SM every CTA of a tile adds its share of the columns after a bounded wait for the others. Any M. With block_n = 256, more than
  * 128 rows and at most as many (256 x 256 tile, split) items as CTA pairs fit the device at once, the CTA-pair kernel runs
  * instead, one item per pair, and every CTA of a tile adds its share of the columns (at most 8 splits).
  * partials: scratch of feather_scaled_mm_splitk_wide_partial_floats(M, N, K, block_n, splits) floats.

@@ -136,6 +136,29 @@ def test_benchmark_shapes_whole_output(cuda_device, channels, size, dtype):
     assert torch.equal(zero, bg.reshape(1, -1, 1, 1).expand_as(zero))
 
 
+@pytest.mark.parametrize("channels,size", [(128, 512), (256, 256), (64, 264)])
+def test_back_to_back_launches_repeat_the_same_bits(cuda_device, channels, size):
+    # The copy engine fills the slots of the halo ring in any order; a gather that mistook an older phase of a slot's
+    # barrier for its own would show as a launch that differs from the first one or as a wait that ran out. 300 launches
+    # in a row over rotating inputs (so that the tiles come from DRAM with scattered latencies), every output compared.
+    import feather_ops_b200 as fo
+
+    x, weight, bias = oc.make_inputs(1, channels, channels, size, size, torch.bfloat16, seed=channels)
+    packed = fo.prepack_conv2d_weight_3x3(weight.to(cuda_device))
+    bg = bias.to(cuda_device)
+    xs = [x.to(cuda_device).clone() for _ in range(6)]
+    ys = [torch.empty_like(xs[0]) for _ in range(6)]
+    tile = fo.conv2d.select_conv3x3_config(channels, size)
+    first = _cabi.conv3x3(xs[0], packed, bg, tile)
+    op = torch.ops.feather_ops.conv2d_3x3.default
+    for rounds in range(50):
+        for i in range(6):
+            op(xs[i], packed, bg, ys[i], *tile, False)
+        for i in range(6):
+            assert torch.equal(ys[i], first), (rounds, i)
+    _cabi.assert_clean(STATUS)
+
+
 def test_compiled_caller_matches_the_oracle(cuda_device):
     # tests/test_conv3x3.py:276-291 of the reference: the prepacked op under torch.compile with the default backend
     import feather_ops_b200 as fo

@@ -241,6 +241,9 @@ def test_split_k_of_the_one_cta_kernel_is_what_the_heuristic_picks_for_few_tiles
     assert sm.select_pair_splits(256, 4096, 4096) == 4 and sm.select_pair_splits(512, 3072, 12288) == 3 and sm.select_pair_splits(768, 2048, 8192) == 3
     assert sm.select_pair_splits(256, 3072, 3072) == 1 and sm.select_pair_splits(512, 3072, 3072) == 3 and sm.select_pair_splits(512, 1280, 1280) == 1
     assert sm.select_pair_splits(128, 4096, 4096) == 1 and sm.select_pair_splits(4096, 12288, 3072) == 1 and sm.select_pair_splits(1024, 4096, 4096) == 1
+    # one row tile of 64..128 rows and 32..74 column tiles of 256: three or more K splits of the one-CTA kernel with 128 x 256 tiles
+    assert sm.select_row_tile_splits_256(128, 12288, 3072) == 3 and sm.select_row_tile_splits_256(64, 8192, 3072) == 4 and sm.select_row_tile_splits_256(48, 12288, 3072) == 1
+    assert sm.select_row_tile_splits_256(128, 4096, 4096) == 1 and sm.select_row_tile_splits_256(129, 12288, 3072) == 1
     assert sm.warp_mma_takes(16, 4096, 4096) and sm.warp_mma_takes(64, 3072, 3072) and not sm.warp_mma_takes(64, 12288, 3072)
     assert not sm.warp_mma_takes(32, 3072, 12288) and not sm.warp_mma_takes(8, 256, 4096)
     for m, n, k in [(100, 2064, 1040), (65, 528, 4096), (48, 1040, 528), (128, 1296, 272), (33, 3072, 8192 + 64), (300, 1040, 4112), (513, 272, 8192)]:
@@ -310,7 +313,7 @@ def test_skinny_shapes_through_the_python_api(cuda_device):
     from feather_ops_b200.scaled_mm import select_scaled_mm_splits
 
     assert select_scaled_mm_splits(1, 3072, 12288) > 1 and select_scaled_mm_splits(64, 3072, 12288) == 1
-    for m, n, k in ((1, 12288, 3072), (16, 3072, 12288), (100, 12288, 3072), (128, 3072, 1024)):
+    for m, n, k in ((1, 12288, 3072), (16, 3072, 12288), (100, 12288, 3072), (128, 3072, 1024), (77, 8208, 3088)):
         a, packed, scale, bias = osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, weight_std=0.02, with_bias=False)
         out = fo.scaled_mm_hip(a.to(cuda_device), packed.to(cuda_device), scale.to(cuda_device), None, torch.bfloat16)
         _cabi.assert_clean(STATUS)
