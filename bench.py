@@ -477,8 +477,19 @@ def run_library(args):
     fastest_step_ms = max_over_ranks(min(step_ms))
 
     # ------------------------------------------------------------------ end to end: host buffers, public API
+    # every rank with all ranks copying at once (what the end-to-end loop meets), then every rank in turn with the others idle
+    # (what one GPU's link gives): the gap between the two is the share of the host side (root complex, memory) in the limit
+    barrier()
     copy_gbs = copy_bandwidth(device, M, N, K)
     copy_gbs_per_rank = {key: [round(v, 1) for v in gather_over_ranks(val)] for key, val in copy_gbs.items()}
+    copy_gbs_alone = copy_gbs
+    if distributed:
+        for turn in range(world):
+            barrier()
+            if turn == rank:
+                copy_gbs_alone = copy_bandwidth(device, M, N, K)
+        barrier()
+    copy_gbs_per_rank_alone = {key: [round(v, 1) for v in gather_over_ranks(val)] for key, val in copy_gbs_alone.items()}
 
     def e2e_run(m_rows, batches, a_rows_host):
         """`batches` passes of `fo.scaled_mm_hip` over `m_rows` host rows each: H2D of the activations, the product,
@@ -613,8 +624,10 @@ def run_library(args):
                 "batches_timed": e2e_batches,
                 "ms_per_batch": e2e_s / e2e_batches * 1e3,
                 "copy_gbs_per_rank": copy_gbs_per_rank,
+                "copy_gbs_per_rank_alone": copy_gbs_per_rank_alone,
+                "copy_gbs_all_ranks_together": round(sum(copy_gbs_per_rank["both"]), 1),
                 "copy_floor_ms_per_batch": d2h_floor_ms,
-                "limiter": "the device -> host copy of the 100.7 MB result per batch: ms_per_batch is the copy floor (both directions in flight), the product itself takes us_per_launch",
+                "limiter": "the device -> host copy of the 100.7 MB result per batch: ms_per_batch follows the copy floor (both directions in flight, all ranks copying at once: copy_gbs_per_rank; copy_gbs_per_rank_alone is each rank with the others idle), the product itself takes us_per_launch",
                 "numa": numa,
                 "how": "feather_ops_b200.scaled_mm_hip per batch; activations copied from pinned host memory and the bf16 result copied back to pinned host memory every batch, on copy streams double-buffered against the compute stream; wall clock, max over ranks",
             },
