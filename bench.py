@@ -531,7 +531,8 @@ def run_library(args):
     e2e_batches = max(4, min(args.steps * LAUNCHES_PER_STEP, 24))
     e2e_s = e2e_run(M, e2e_batches, a_host)
     e2e_value = FLOP_PER_LAUNCH * world * e2e_batches / e2e_s / 1e12
-    d2h_floor_ms = M * N * 2 / (min(copy_gbs_per_rank["both"]) * 1e9) * 1e3 if min(copy_gbs_per_rank["both"]) > 0 else None
+    # a batch moves its activations in and its result out; `both` is the rate with the two directions in flight together
+    d2h_floor_ms = (M * K * 2 + M * N * 2) / (min(copy_gbs_per_rank["both"]) * 1e9) * 1e3 if min(copy_gbs_per_rank["both"]) > 0 else None
 
     # ------------------------------------------------------------------ strong scaling: M = 65536 split over the ranks
     start_row, stop_row = shard.token_shard(STRONG_M, rank, world)

@@ -222,15 +222,16 @@ def bench_msweep(device, peaks, include_65536: bool = True) -> list[dict]:
 
 
 # ------------------------------------------------------------------------------------------------------------- int8
-def measure_vendor_int8(device, m=8192, n=8192, k=8192) -> float | None:
-    """TOP/s of the vendor library's int8 GEMM (`torch._int_mm`) at a large square: the measured int8 denominator (the
-    driver-measured peaks have no int8 figure). None if the private entry point is missing or refuses the layout."""
+def measure_vendor_int8(device, m=8192, n=8192, k=8192, sets=1) -> float | None:
+    """TOP/s of the vendor library's int8 GEMM (`torch._int_mm`, int32 output, no scales) over `sets` rotating operand sets. At a
+    large square it is the measured int8 denominator (the driver-measured peaks have no int8 figure); at a case's own shape it is
+    the comparator beside the case. None if the private entry point is missing or refuses the layout."""
     if PROFILE_MODE:
         return None
     try:
-        a = torch.randint(-127, 128, (m, k), device=device, dtype=torch.int8)
-        w_t = torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8).t()  # [K, N] column-major, as the library wants
-        timing = time_launches(lambda i: torch._int_mm(a, w_t), 1)
+        a = [torch.randint(-127, 128, (m, k), device=device, dtype=torch.int8) for _ in range(sets)]
+        w_t = [torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8).t() for _ in range(sets)]  # [K, N] column-major, as the library wants
+        timing = time_launches(lambda i: torch._int_mm(a[i % sets], w_t[i % sets]), sets)   # the result comes from the graph's private pool
         return 2.0 * m * n * k / timing["us"] / 1e6
     except Exception:  # noqa: BLE001
         return None
@@ -275,9 +276,12 @@ def bench_int8(device, peaks) -> list[dict]:
                       time_launches(quant, sets), flop=None, algorithmic_bytes=q_bytes, bound="hbm", peaks=peaks))
     flop = 2.0 * m * n * k
     gemm_bytes = float(m * k + n * k + m * n * 2)
+    vendor_here = measure_vendor_int8(device, m, n, k, sets)
     for transposed in (False, True):
-        record = {"case": f"cfg3 int8_scaled_mm 4096x3072x3072 {'backward (transposed_b)' if transposed else 'forward'}", "op": "int8_scaled_mm", "M": m, "N": n,
-                  "K": k, "tile": list(tile), "cold": True, "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
+        record = {"vendor_same_shape_tops": _round(vendor_here, 1), "vendor_same_shape_us": None if not vendor_here else _round(flop / vendor_here / 1e6, 2),
+                  "vendor_same_shape": "torch._int_mm at this shape over the same number of rotating operand sets: int32 output, no scales, no rounding",
+                  **{"case": f"cfg3 int8_scaled_mm 4096x3072x3072 {'backward (transposed_b)' if transposed else 'forward'}", "op": "int8_scaled_mm", "M": m, "N": n,
+                  "K": k, "tile": list(tile), "cold": True, "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}}
         out.append(_rates(record, time_launches(lambda i, t=transposed: gemm(i, t), sets), flop=flop, algorithmic_bytes=gemm_bytes, bound="tensor", peaks=peaks, int8=True))
     record = {"case": "cfg3 convrot_int8_linear 4096x3072x3072 (quantize + GEMM, the public call)", "op": "convrot_int8_linear", "M": m, "N": n, "K": k, "cold": True,
               "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}

@@ -21,6 +21,10 @@ SHAPES = [
     # widths that are multiples of 8 take their halo tiles through the copy engine: a tile narrower than the box, channels that end
     # inside a 16-channel group, a ragged second segment, a ragged channel tile on the CTA-pair kernel, batch > 1, one row
     (2, 24, 40, 5, 8), (1, 8, 136, 3, 16), (2, 40, 272, 9, 136), (1, 24, 130, 2, 264), (1, 136, 264, 1, 392),
+    # more tiles than SMs, so that a CTA walks a range of tiles and consecutive tiles share their weight slots: ranges of two and
+    # three tiles over two images; a range that straddles two output-channel tiles on the one-CTA kernel (3 x 75 tiles of one row)
+    # and on the CTA-pair kernel (3 x 40 tiles of two rows), where the tile before the boundary must run alone
+    (2, 24, 96, 90, 136), (1, 16, 272, 75, 128), (1, 16, 520, 80, 128),
 ]
 TILES = [(4, 4, 2, 4, 1), (4, 4, 2, 2, 1), (2, 2, 2, 2, 1), (4, 4, 2, 2, 2)]
 
