@@ -1500,7 +1500,7 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
         if (ring_bytes() + p.staging_bytes <= budget) p.raw_slots = 4;
         if (ring_bytes() + p.act_stage_bytes <= budget) p.rec_slots = 3;
         const int smem_bytes = ring_bytes() + fixed_bytes;
-        auto* kernel = &conv3x3_staged_kernel<kBf16>;
+            auto* kernel = &conv3x3_staged_kernel<kBf16>;
         if (!smem_limit[1].at_least(smem_bytes, [&](int need) { return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, need) == cudaSuccess; })) {
             return 1;
         }

@@ -52,6 +52,8 @@ def test_heuristics_return_table_rows():
     assert conv2d.select_conv3x3_config(128, 0) is None
     assert conv2d.select_conv3x3_config(512, 128)[4] == 2
     assert conv2d.select_conv3x3_config(512, 129)[4] == 1  # two-row tiles need an even width
+    assert conv2d.select_conv3x3_config(128, 512) == (4, 4, 2, 4, 1) and conv2d.select_conv3x3_config(128, 264)[4] == 2  # one row of 256 pixels only without much padding
+    assert conv2d.select_conv3x3_config(256, 512)[4] == 2  # more than 128 output channels: the CTA-pair kernel's tile
 
 
 def test_prepacks_equal_the_oracle(golden):
