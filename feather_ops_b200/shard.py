@@ -69,6 +69,17 @@ def _interleave(gathered: torch.Tensor, out: torch.Tensor) -> None:
         out.view(rows, world, width).copy_(gathered.permute(1, 0, 2))
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device: torch.device):
+    """One extra stream per device for the copies that run beside the products."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[key]
+
+
 class _SmMargin:
     """Leave `sms` SMs free in the persistent scaled_mm kernels while a collective runs beside them (restored on exit).
     A persistent CTA holds its SM's shared memory until the kernel ends, so without free SMs the collective's kernel
@@ -158,20 +169,40 @@ def _n_sharded(a, compute, spans, world, rank, rows, width, out_dtype, layout, g
 
     out = torch.empty((rows, world * width), device=a.device, dtype=out_dtype)
     pending = None   # (work, gathered chunk, start, stop) of the chunk whose all-gather is in flight
+    # The copies into place run on a stream of their own: on the compute stream they would sit between two products and
+    # lengthen its chain (product + copy per chunk) past the all-gather's; beside it they use the SMs the margin leaves free.
+    on_gpu = a.is_cuda
+    main = torch.cuda.current_stream(a.device) if on_gpu else None
+    side = _side_stream(a.device) if on_gpu else None
+    if on_gpu:
+        side.wait_stream(main)   # `out` and the chunks are allocated in the compute stream's order
 
     def finish(item) -> None:
         work, gathered, start, stop = item
-        work.wait()   # the compute stream waits for the collective's stream; the host does not block
-        _interleave(gathered.view(world, stop - start, width), out[start:stop])
+        if on_gpu:
+            with torch.cuda.stream(side):
+                work.wait()   # the side stream waits for the collective's stream; the host does not block
+                _interleave(gathered.view(world, stop - start, width), out[start:stop])
+        else:
+            work.wait()
+            _interleave(gathered.view(world, stop - start, width), out[start:stop])
 
+    # The chunk buffers are allocated on the compute stream, which never waits for a collective here (the side stream
+    # does): they stay referenced until the compute stream has joined the side stream, or the allocator could hand a block
+    # to the next chunk while the collective still reads it.
+    keep = []
     for start, stop in spans:
         local = torch.empty((stop - start, width), device=a.device, dtype=out_dtype)
         compute(a[start:stop], local)
         gathered = torch.empty((world * (stop - start), width), device=a.device, dtype=out_dtype)
         work = dist.all_gather_into_tensor(gathered, local, group=group, async_op=True)
+        keep.append((local, gathered))
         if pending is not None:
             finish(pending)   # issued after this chunk's all-gather, so the collective does not wait for the copy
         pending = (work, gathered, start, stop)
     if pending is not None:
         finish(pending)
+    if on_gpu:
+        main.wait_stream(side)   # the caller's stream sees the whole result, and every collective has finished before it
+    del keep
     return out
