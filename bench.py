@@ -139,7 +139,8 @@ class ClockSampler:
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": max_clock, "reasons": [], "samples": 0}
         return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks),
-                "reasons_mask": hex(mask), "power_w": statistics.median(watts) if watts else None}
+                "reasons_mask": hex(mask), "power_w": statistics.median(watts) if watts else None,
+                "sm_mhz_samples": clocks[:32], "power_w_samples": watts[:32]}
 
 
 try:
