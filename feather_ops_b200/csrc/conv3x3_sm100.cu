@@ -419,6 +419,7 @@ constexpr int kStagedEpilogueWarps = 8;
 constexpr int kStagedFirstGatherWarp = kFirstEpilogueWarp + kStagedEpilogueWarps;
 constexpr int kStagedThreads = 32 * (kStagedFirstGatherWarp + kGatherWarps);
 constexpr int kOutImageBytes = 128 * 64;   // 128 output channels x 32 pixels of 16 bits: what one bulk tensor store writes
+constexpr int kOutImages = 2;              // per half of the epilogue warps: one is written while the copy engine reads the other
 
 struct TileRange {
     int begin, end;
@@ -479,8 +480,8 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* const weight_smem = smem;
-    uint8_t* const out_smem = smem + p.weight_slots * kWeightStageBytes;   // two images of 128 channels x 32 pixels, one per half of the epilogue warps
-    uint8_t* const act_smem = out_smem + 2 * kOutImageBytes;
+    uint8_t* const out_smem = smem + p.weight_slots * kWeightStageBytes;   // images of 128 channels x 32 pixels, kOutImages per half of the epilogue warps
+    uint8_t* const act_smem = out_smem + 2 * kOutImages * kOutImageBytes;
     uint8_t* const staging_smem = act_smem + p.rec_slots * p.act_stage_bytes;
     uint64_t* const bars = reinterpret_cast<uint64_t*>(staging_smem + p.raw_slots * p.staging_bytes);
     uint64_t* const weight_full = bars;                        // TMA: a group's weights have landed
@@ -491,9 +492,9 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
     uint64_t* const rec_empty = rec_full + kMaxSlots;          // MMA commit: the records have been read
     uint64_t* const tmem_full = rec_empty + kMaxSlots;
     uint64_t* const tmem_empty = tmem_full + 2;
-    uint64_t* const image_ready = tmem_empty + 2;              // per half of the epilogue warps: its four warps have written the output image
-    uint64_t* const image_free = image_ready + 2;              // the copy engine has read it
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2);
+    uint64_t* const image_ready = tmem_empty + 2;              // [half][image]: the half's four warps have written the output image
+    uint64_t* const image_free = image_ready + 2 * kOutImages;  // [half][image]: the copy engine has read it
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2 * kOutImages);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
@@ -516,6 +517,8 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], kStagedEpilogueWarps);
+        }
+        for (int s = 0; s < 2 * kOutImages; ++s) {
             mbar_init(&image_ready[s], kStagedEpilogueWarps / 2);
             mbar_init(&image_free[s], 1);
         }
@@ -638,8 +641,7 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
             const int chunks = p.bn / 32;                       // per output row; rows * chunks is even
             const int mine = p.rows * chunks / 2;
             const int row = quarter * 32 + lane;                 // this lane's output channel inside the tile
-            uint8_t* const image = out_smem + half * kOutImageBytes;
-            uint8_t* const image_row = image + row * 64;
+            uint8_t* const images = out_smem + half * kOutImages * kOutImageBytes;
             const int twist = (row >> 1) & 3;                    // the 64-byte swizzle of the tensor map: 16-byte chunk ^= bits 7..8 of the offset
 #pragma unroll 1
             for (int i = half * mine; i < (half + 1) * mine; ++i) {
@@ -660,12 +662,18 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
                 // rows, swizzled so that a quarter warp covers all banks) and one thread hands it to the copy engine, which
                 // also clips at the image edge and at C_out. The hand-offs are mbarriers with bounded waits, like every
                 // other wait of the kernel.
-                if (leader && stores != 0) {
-                    tma_store_wait_read<0>();                     // the copy engine has read the image of the store before
-                    mbar_arrive(&image_free[half]);
+                const uint32_t img = stores % kOutImages;       // this store's image and which use of it this is
+                const uint32_t use = stores / kOutImages;
+                uint64_t* const ready = &image_ready[half * kOutImages + img];
+                uint64_t* const freed = &image_free[half * kOutImages + img];
+                if (leader && use != 0) {
+                    tma_store_wait_read<kOutImages - 1>();        // all but the newest stores have been read: this image's last one too
+                    mbar_arrive(freed);
                 }
-                ok = guard.wait(&image_free[half], (stores & 1u) ^ 1u, kSiteStore);
+                ok = guard.wait(freed, (use & 1u) ^ 1u, kSiteStore);
                 if (!ok) break;
+                uint8_t* const image = images + img * kOutImageBytes;
+                uint8_t* const image_row = image + row * 64;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
@@ -677,9 +685,9 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&image_ready[half]);
+                if (lane == 0) mbar_arrive(ready);
                 if (leader) {
-                    ok = guard.wait(&image_ready[half], stores & 1u, kSiteStore, 1);
+                    ok = guard.wait(ready, use & 1u, kSiteStore, 1);
                     if (ok) {
                         tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0, tc.b);
                         tma_store_commit();
@@ -1090,8 +1098,8 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
 constexpr int kPairWeightSlots = 3;
 constexpr int kPairActSlots = 3;
 constexpr int kPairStagedItems = (2 * kPairHaloRows * (kPairBN / 2 + 2) + kGatherWarps * 32 - 1) / (kGatherWarps * 32);
-constexpr int kPairStagedSmemBytes = kPairWeightSlots * kWeightStageBytes + 2 * kOutImageBytes + kPairActSlots * (kPairActStageBytes + kPairStagingBytes) +
-                                     (2 * kPairWeightSlots + 3 * kPairActSlots + 8) * 8 + 16 + 1024;
+constexpr int kPairStagedSmemBytes = kPairWeightSlots * kWeightStageBytes + 2 * kOutImages * kOutImageBytes + kPairActSlots * (kPairActStageBytes + kPairStagingBytes) +
+                                     (2 * kPairWeightSlots + 3 * kPairActSlots + 4 + 4 * kOutImages) * 8 + 16 + 1024;
 static_assert(kPairStagedSmemBytes <= 227 * 1024, "a CTA's shared memory");
 
 template <bool kBf16>
@@ -1100,8 +1108,8 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* const weight_smem = smem;
-    uint8_t* const out_smem = smem + kPairWeightSlots * kWeightStageBytes;   // two images of 128 channels x 32 pixels, one per output row
-    uint8_t* const act_smem = out_smem + 2 * kOutImageBytes;
+    uint8_t* const out_smem = smem + kPairWeightSlots * kWeightStageBytes;   // images of 128 channels x 32 pixels, kOutImages per output row
+    uint8_t* const act_smem = out_smem + 2 * kOutImages * kOutImageBytes;
     uint8_t* const staging_smem = act_smem + kPairActSlots * kPairActStageBytes;
     uint64_t* const bars = reinterpret_cast<uint64_t*>(staging_smem + kPairActSlots * kPairStagingBytes);
     uint64_t* const weight_full = bars;                             // local: this CTA's weight rows have landed
@@ -1111,9 +1119,9 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     uint64_t* const act_empty = act_full + kPairActSlots;           // signalled in both CTAs by CTA 0's commits
     uint64_t* const tmem_full = act_empty + kPairActSlots;
     uint64_t* const tmem_empty = tmem_full + 2;                     // CTA 0 only
-    uint64_t* const image_ready = tmem_empty + 2;                   // local, per output row: its four warps have written the output image
-    uint64_t* const image_free = image_ready + 2;                   // local: the copy engine has read it
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2);
+    uint64_t* const image_ready = tmem_empty + 2;                   // local, [row][image]: the row's four warps have written the output image
+    uint64_t* const image_free = image_ready + 2 * kOutImages;       // local: the copy engine has read it
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2 * kOutImages);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
@@ -1135,6 +1143,8 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kStagedEpilogueWarps);
+        }
+        for (int s = 0; s < 2 * kOutImages; ++s) {
             mbar_init(&image_ready[s], kStagedEpilogueWarps / 2);
             mbar_init(&image_free[s], 1);
         }
@@ -1247,8 +1257,7 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         const int r = (warp - kFirstEpilogueWarp) / 4;
         const bool leader = quarter == 0 && lane == 0;           // issues this row's bulk stores and waits for them
         const int row = quarter * 32 + lane;                     // this lane's output channel inside the CTA's 128
-        uint8_t* const image = out_smem + r * kOutImageBytes;
-        uint8_t* const image_row = image + row * 64;
+        uint8_t* const images = out_smem + r * kOutImages * kOutImageBytes;
         const int twist = (row >> 1) & 3;                        // the 64-byte swizzle of the tensor map
         uint32_t stores = 0;                                     // bulk stores of this row's warps so far
         uint32_t q = 0;
@@ -1277,12 +1286,18 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 }
                 if (h >= p.H || tc.w0 + c * 32 >= p.W) continue;   // uniform over the four warps of this row
                 // the output goes through a shared-memory image and a bulk tensor store, as in conv3x3_staged_kernel
-                if (leader && stores != 0) {
-                    tma_store_wait_read<0>();
-                    mbar_arrive(&image_free[r]);
+                const uint32_t img = stores % kOutImages;
+                const uint32_t use = stores / kOutImages;
+                uint64_t* const ready = &image_ready[r * kOutImages + img];
+                uint64_t* const freed = &image_free[r * kOutImages + img];
+                if (leader && use != 0) {
+                    tma_store_wait_read<kOutImages - 1>();
+                    mbar_arrive(freed);
                 }
-                ok = guard.wait(&image_free[r], (stores & 1u) ^ 1u, kSiteStore);
+                ok = guard.wait(freed, (use & 1u) ^ 1u, kSiteStore);
                 if (!ok) break;
+                uint8_t* const image = images + img * kOutImageBytes;
+                uint8_t* const image_row = image + row * 64;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
@@ -1294,9 +1309,9 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&image_ready[r]);
+                if (lane == 0) mbar_arrive(ready);
                 if (leader) {
-                    ok = guard.wait(&image_ready[r], stores & 1u, kSiteStore, 1);
+                    ok = guard.wait(ready, use & 1u, kSiteStore, 1);
                     if (ok) {
                         tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0, tc.b);
                         tma_store_commit();
@@ -1489,13 +1504,14 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
         p.staging_bytes = boxes * 16 * (rows + 2) * box_w * 2;   // a multiple of 256 bytes
         // Ring depths: two weight slots, three raw halo tiles in flight and two record slots at least; what is left of the
         // shared memory goes to a third weight slot (a step of one tile holds a slot only half as long), then a fourth raw tile.
-        const int fixed_bytes = 2 * kOutImageBytes + (6 * kMaxSlots + 8) * 8 + 16 + 1024;
+        const int fixed_bytes = 2 * kOutImages * kOutImageBytes + (6 * kMaxSlots + 4 + 4 * kOutImages) * 8 + 16 + 1024;
         const int budget = 227 * 1024 - fixed_bytes;
         p.weight_slots = 2;
-        p.raw_slots = 3;
+        p.raw_slots = 2;
         p.rec_slots = 2;
         auto ring_bytes = [&] { return p.weight_slots * kWeightStageBytes + p.raw_slots * p.staging_bytes + p.rec_slots * p.act_stage_bytes; };
         if (ring_bytes() > budget) return 1;
+        if (ring_bytes() + p.staging_bytes <= budget) p.raw_slots = 3;
         if (ring_bytes() + kWeightStageBytes <= budget) p.weight_slots = 3;
         if (ring_bytes() + p.staging_bytes <= budget) p.raw_slots = 4;
         if (ring_bytes() + p.act_stage_bytes <= budget) p.rec_slots = 3;
