@@ -63,6 +63,7 @@ struct Params {
     int tiles_n;
     uint32_t idesc;
     int band;               // pair kernel: row tiles per band of the tile walk
+    int bulk_out;           // pair kernel: the output goes through shared-memory images and bulk tensor stores (N_out % 8 == 0, c 16-byte aligned)
 };
 
 template <int BN>
@@ -458,15 +459,17 @@ struct PairSmem {
     static constexpr int kRawOff = kAOff + kPairLoadStages * kATileBytes;
     static constexpr int kOperandOff = kRawOff + kPairLoadStages * kRawBytes;
     static constexpr int kColumnOff = kOperandOff + kPairOperandStages * kOperandBytes;  // 2 x (256 scales + 256 biases), fp32
-    static constexpr int kBarOff = kColumnOff + 2 * 2 * kPairN * 4;
-    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 6;
+    static constexpr int kImageBytes = kBlockM * 64;         // 128 rows x 32 output columns of 16 bits: what one bulk tensor store writes
+    static constexpr int kImageOff = kColumnOff + 2 * 2 * kPairN * 4;   // two images: one is written while the copy engine reads the other
+    static constexpr int kBarOff = kImageOff + 2 * kImageBytes;
+    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 6 + 4;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
 };
 
 template <bool kTransposedB, bool kOutBf16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
-int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const Params p) {
     using L = PairSmem;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -478,6 +481,8 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* const tmem_full = operand_empty + kPairOperandStages;
     uint64_t* const tmem_empty = tmem_full + 2;                      // CTA 0 only
     uint64_t* const columns_full = tmem_empty + 2;                   // local: the tile's column scales and biases are staged
+    uint64_t* const image_ready = columns_full + 2;                  // local: the four epilogue warps have written an output image
+    uint64_t* const image_free = image_ready + 2;                    // local: the copy engine has read it
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
@@ -502,10 +507,13 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
             mbar_init(&columns_full[s], kEpilogueWarps);
+            mbar_init(&image_ready[s], kEpilogueWarps);
+            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_a);
         tma_prefetch_desc(&map_b);
+        if (p.bulk_out) tma_prefetch_desc(&map_c);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, 2 * kPairN);
@@ -597,6 +605,13 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool wide_rows = (p.N_out % 8) == 0;
         const bool has_scale = !kTransposedB && p.b_scale != nullptr;
         const bool has_bias = !kTransposedB && p.bias != nullptr;
+        // With `bulk_out` a chunk of 128 rows x 32 columns goes into a 64-byte-swizzled shared-memory image that one thread hands
+        // to the copy engine (which clips at M and N_out): a lane holds one row, so the direct stores are 32 requests of 16
+        // bytes per warp instruction, 4096 per tile, and the drain of a pair's last tile has nothing to hide behind.
+        const bool leader = quarter == 0 && lane == 0;
+        const int image_row_index = quarter * 32 + lane;
+        const int twist = (image_row_index >> 1) & 3;
+        uint32_t stores = 0;
         Ring acc;
         bool ok = true;
         grid_dependency_wait();   // the row scales come from the kernel before this one
@@ -660,7 +675,36 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     v[g * 4] = pack_out<kOutBf16>(f[0], f[1]);
                     v[g * 4 + 1] = pack_out<kOutBf16>(f[2], f[3]);
                 }
-                if (row < p.M) {
+                if (p.bulk_out) {
+                    if (col0 >= p.N_out) continue;   // uniform over the four warps
+                    const uint32_t img = stores & 1u;
+                    const uint32_t use = stores >> 1;
+                    if (leader && use != 0) {
+                        tma_store_wait_read<1>();     // all but the newest store have been read: this image's last one too
+                        mbar_arrive(&image_free[img]);
+                    }
+                    ok = guard.wait(&image_free[img], (use & 1u) ^ 1u, kSiteStore);
+                    if (!ok) break;
+                    uint8_t* const image = smem + L::kImageOff + img * L::kImageBytes;
+                    uint8_t* const image_row = image + image_row_index * 64;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        *reinterpret_cast<uint4*>(image_row + ((g ^ twist) << 4)) = make_uint4(v[g * 8], v[g * 8 + 1], v[g * 8 + 4], v[g * 8 + 5]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&image_ready[img]);
+                    if (leader) {
+                        ok = guard.wait(&image_ready[img], use & 1u, kSiteStore, 1);
+                        if (ok) {
+                            tma_store_2d(&map_c, image, col0, m0);
+                            tma_store_commit();
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    ++stores;
+                } else if (row < p.M) {
                     if (wide_rows) {
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
@@ -680,6 +724,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             acc.advance(2);
         }
+        if (p.bulk_out && leader) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
     } else {
         // ------------------------------------------------------------------ weight re-layout warps (this CTA's 128 operand rows)
         constexpr int kTeamThreads = kPairRelayoutWarps * 32 / kPairTeams;
@@ -818,6 +863,12 @@ inline bool pdl_off() {
     return off;
 }
 
+// FEATHER_INT8_BULK_OUT_OFF=1 keeps the pair kernel's direct output stores (A/B measurements). Read once per process.
+inline bool bulk_out_off() {
+    static const bool off = env_switch("FEATHER_INT8_BULK_OUT_OFF");
+    return off;
+}
+
 template <bool kTransposedB, bool kOutBf16>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
@@ -883,6 +934,15 @@ bool launch_pair_instance(const LaunchArgs& args) {
     }
     p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
     p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
+    // the output as a 2-D tensor with a box of 32 columns x 128 rows (64-byte swizzle): what the epilogue's bulk stores write
+    CUtensorMap map_c = map_a;   // unused without bulk_out
+    p.bulk_out = (args.N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(args.c) & 15u) == 0 && !bulk_out_off()) ? 1 : 0;
+    if (p.bulk_out) {
+        const uint64_t c_dims[2] = {static_cast<uint64_t>(args.N_out), static_cast<uint64_t>(args.M)};
+        const uint64_t c_strides[1] = {static_cast<uint64_t>(args.N_out) * 2};
+        const uint32_t c_box[2] = {32, kBlockM};
+        if (!encode_map(&map_c, kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.c, c_dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_64B)) return false;
+    }
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int grid = 2 * (num_tiles < pairs ? num_tiles : pairs);
     // Programmatic dependent launch: the kernel may start while the one before it in the stream (in the ConvRot linear
@@ -898,7 +958,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     attr[0].val.programmaticStreamSerializationAllowed = pdl_off() ? 0 : 1;
     config.attrs = attr;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, map_a, map_b, p) == cudaSuccess;
+    return cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, p) == cudaSuccess;
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -755,7 +755,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
             const int n0 = tile_n * kPairN;
             ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
-            if (!ok) break;
+            if (!kSplitK && !ok) break;   // the K-split path below meets its named barrier whatever the wait returned
             tc_fence_after_sync();
             const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
@@ -764,7 +764,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 // this pair's partial of the tile goes to scratch; a warp writes 512 consecutive bytes per instruction
                 float* const part = p.partials + ((static_cast<int64_t>(tile) * 2 + cta) * p.splits + my_split) * (kBlockM * kPairN) + (quarter * 32 + lane) * 4;
 #pragma unroll 1
-                for (int c = 0; c < kPairN / 32; ++c) {
+                for (int c = 0; ok && c < kPairN / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32(taddr + c * 32, v);
                     tmem_wait_ld();
@@ -774,8 +774,10 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     }
                 }
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps: this CTA's half of the partial is out
-                if (threadIdx.x == kFirstEpilogueWarp * 32) {
+                // the four epilogue warps: this CTA's half of the partial is out. Every warp comes here, also one whose wait gave
+                // up (it wrote nothing and the tile is not counted in: the reducers then run out of their own bounded wait).
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == kFirstEpilogueWarp * 32 && !guard.aborted()) {
                     __threadfence();
                     atomicAdd(p.counters + tile * 2 + static_cast<int>(cta), 1u);
                 }
