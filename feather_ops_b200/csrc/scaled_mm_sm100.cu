@@ -77,6 +77,7 @@ struct Params {
     float* partials;      // [splits][M][N] fp32
     uint32_t* counters;   // [tiles_m * tiles_n] tickets, zero before the launch and zero again after it
     int single_item;      // every CTA has exactly one (tile, split) item: the whole CTA adds the partials, not four warps
+    int bulk_out;         // pair kernel: the output goes through shared-memory images and bulk tensor stores
 };
 
 template <int BN>
@@ -612,10 +613,14 @@ struct PairSmem {
     static constexpr int kAOff = 0;
     static constexpr int kOperandOff = kAOff + kPairLoadStages * kATileBytes;
     static constexpr int kRawOff = kOperandOff + kPairOperandStages * kOperandBytes;
-    static constexpr int kBarOff = kRawOff + kPairLoadStages * kRawBytes;
-    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 4;
+    static constexpr int kImageBytes = kBlockM * 64;   // 128 rows x 32 output columns of 16 bits: what one bulk tensor store writes
+    static constexpr int kImageOff = kRawOff + kPairLoadStages * kRawBytes;   // two images: one is written while the copy engine reads the other
+    static constexpr int kBarOff = kImageOff + 2 * kImageBytes;
+    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 4 + 4;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
+    static_assert(kImageOff % 1024 == 0, "swizzled images sit on a 1 KB boundary");
+    static_assert(kDynamic <= 227 * 1024, "a CTA's shared memory");
 };
 
 // kSplitK: every pair has exactly ONE work item (tile, K split) instead of walking tiles; compiled apart so that the plain
@@ -627,7 +632,7 @@ struct PairSmem {
 // (one per row half) and one "done" counter, whose last arriver puts all three back to zero for the next launch.
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const Params p) {
     using L = PairSmem;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -638,6 +643,8 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint64_t* const operand_empty = operand_full + kPairOperandStages;
     uint64_t* const tmem_full = operand_empty + kPairOperandStages;
     uint64_t* const tmem_empty = tmem_full + 2;                        // used in CTA 0 only
+    uint64_t* const image_ready = tmem_empty + 2;                      // local: the four epilogue warps have written an output image
+    uint64_t* const image_free = image_ready + 2;                      // local: the copy engine has read it
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
@@ -659,10 +666,13 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
+            mbar_init(&image_ready[s], kEpilogueWarps);
+            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_a);
         tma_prefetch_desc(&map_b);
+        if (!kSplitK && p.bulk_out) tma_prefetch_desc(&map_c);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_slot, 2 * kPairN);
@@ -747,6 +757,13 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
         const int quarter = warp % 4;
         const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+        // With `bulk_out` a chunk of 128 rows x 32 columns goes into a 64-byte-swizzled shared-memory image that one thread hands
+        // to the copy engine (which clips at M and N): a lane holds one row, so the direct stores are 32 requests of 16 bytes
+        // per warp instruction, and the drain of a pair's last tile has nothing to hide behind.
+        const bool leader = quarter == 0 && lane == 0;
+        const int image_row_index = quarter * 32 + lane;
+        const int twist = (image_row_index >> 1) & 3;
+        uint32_t stores = 0;
         Ring acc;
         bool ok = true;
         for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
@@ -794,10 +811,11 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), 0));
                 }
                 const int col0 = n0 + c * 32;
+                uint32_t out_words[16];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const int col = col0 + g * 8;
-                    uint32_t o[4];
+                    uint32_t* const o = out_words + 4 * g;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         o[i] = pack_out<kOutBf16>(__uint_as_float(v[g * 8 + 2 * i]) * scale, __uint_as_float(v[g * 8 + 2 * i + 1]) * scale);
@@ -823,13 +841,44 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                             o[i] = pack_out<kOutBf16>(x.x + b.x, x.y + b.y);
                         }
                     }
-                    if (row < p.M && col < p.N) {
+                    if (!p.bulk_out && row < p.M && col < p.N) {
                         *reinterpret_cast<uint4*>(c_row + col) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
+                }
+                if (p.bulk_out) {
+                    if (col0 >= p.N) continue;   // uniform over the four warps
+                    const uint32_t img = stores & 1u;
+                    const uint32_t use = stores >> 1;
+                    if (leader && use != 0) {
+                        tma_store_wait_read<1>();     // all but the newest store have been read: this image's last one too
+                        mbar_arrive(&image_free[img]);
+                    }
+                    ok = guard.wait(&image_free[img], (use & 1u) ^ 1u, kSiteStore);
+                    if (!ok) break;
+                    uint8_t* const image = smem + L::kImageOff + img * L::kImageBytes;
+                    uint8_t* const image_row = image + image_row_index * 64;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        *reinterpret_cast<uint4*>(image_row + ((g ^ twist) << 4)) = make_uint4(out_words[4 * g], out_words[4 * g + 1], out_words[4 * g + 2], out_words[4 * g + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&image_ready[img]);
+                    if (leader) {
+                        ok = guard.wait(&image_ready[img], use & 1u, kSiteStore, 1);
+                        if (ok) {
+                            tma_store_2d(&map_c, image, col0, m0);
+                            tma_store_commit();
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                    if (!ok) break;
+                    ++stores;
                 }
             }
             acc.advance(2);
         }
+        if (!kSplitK && p.bulk_out && leader) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
     } else {
         // ------------------------------------------------------------------ upcast warps (this CTA's weight half)
         // The warps form kPairTeams teams that take the k blocks in turn, so a team has kPairTeams k-block times
@@ -1357,6 +1406,12 @@ inline bool skinny_wmma_off() {
 inline int64_t pair_tiles(int64_t M, int64_t N) { return ((M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((N + kPairN - 1) / kPairN); }
 constexpr int kPairMaxSplits = kPairN / 32;   // a split owns at least one 32-column chunk of the reduction
 
+// FEATHER_SCALED_MM_BULK_OUT_OFF=1 keeps the pair kernel's direct output stores (A/B measurements). Read once per process.
+inline bool bulk_out_off() {
+    static const bool off = env_switch("FEATHER_SCALED_MM_BULK_OUT_OFF");
+    return off;
+}
+
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
@@ -1415,6 +1470,15 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.tiles_n = static_cast<int>((args.N + kPairN - 1) / kPairN);
     p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
+    // the output as a 2-D tensor with a box of 32 columns x 128 rows (64-byte swizzle): what the epilogue's bulk stores write
+    CUtensorMap map_c = map_a;   // unused without bulk_out
+    p.bulk_out = (!kSplitK && args.N % 8 == 0 && (reinterpret_cast<uintptr_t>(args.c) & 15u) == 0 && !bulk_out_off()) ? 1 : 0;
+    if (p.bulk_out) {
+        const uint64_t c_dims[2] = {static_cast<uint64_t>(args.N), static_cast<uint64_t>(args.M)};
+        const uint64_t c_strides[1] = {static_cast<uint64_t>(args.N) * 2};
+        const uint32_t c_box[2] = {32, kBlockM};
+        if (!encode_map(&map_c, kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.c, c_dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_64B)) return false;
+    }
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int margin_pairs = (g_sm_margin.load(std::memory_order_relaxed) + 1) / 2;
     const int usable = pairs - margin_pairs > 0 ? pairs - margin_pairs : 1;
@@ -1427,11 +1491,11 @@ bool launch_pair_instance(const LaunchArgs& args) {
         p.band = p.tiles_m;   // one item per pair: no walk to order
         const int64_t items = static_cast<int64_t>(num_tiles) * p.splits;
         if (p.splits < 2 || items > usable) return false;   // the caller falls back to the one-CTA split kernel
-        kernel<<<static_cast<unsigned>(2 * items), kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
+        kernel<<<static_cast<unsigned>(2 * items), kThreads, L::kDynamic, args.stream>>>(map_a, map_b, map_c, p);
         return cudaGetLastError() == cudaSuccess;
     }
     const int grid = 2 * (num_tiles < usable ? num_tiles : usable);
-    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, p);
+    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, map_c, p);
     return cudaGetLastError() == cudaSuccess;
 }
 
