@@ -782,6 +782,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 float* const part = p.partials + ((static_cast<int64_t>(tile) * 2 + cta) * p.splits + my_split) * (kBlockM * kPairN) + (quarter * 32 + lane) * 4;
 #pragma unroll 1
                 for (int c = 0; ok && c < kPairN / 32; ++c) {
+                    if (c % p.splits == my_split) continue;   // this CTA adds these chunks itself and takes its own share from tensor memory
                     uint32_t v[32];
                     tmem_ld_32x32(taddr + c * 32, v);
                     tmem_wait_ld();
@@ -959,7 +960,10 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
             const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
             const int group = t / kBlockM;
-            const int r = t % kBlockM;
+            // a warp reads the tensor-memory lanes 32 * (warp % 4) .. + 31, so its threads take those rows of the tile
+            const int r = (warp % 4) * 32 + lane;
+            const uint32_t own_taddr = tmem_base + (static_cast<uint32_t>((warp % 4) * 32) << 16);   // one item per pair: accumulator buffer 0
+            tc_fence_after_sync();
             int tile_m, tile_n;
             banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
             const int row = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM + r;
@@ -974,6 +978,15 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
                 for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
                 for (int sp = 0; sp < p.splits; ++sp) {   // split order: the sum does not depend on who adds it
+                    if (sp == my_split) {
+                        // this CTA's own partial of the chunk never left tensor memory
+                        uint32_t own[32];
+                        tmem_ld_32x32(own_taddr + c * 32, own);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[i] += __uint_as_float(own[i]);
+                        continue;
+                    }
                     const float* const src = half_base + static_cast<int64_t>(sp) * (kBlockM * kPairN);
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
