@@ -366,6 +366,8 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&tmem_empty[acc.idx]);
                     }
+                    // with one item per CTA the chunks this CTA adds itself stay in tensor memory (nothing reuses the buffer)
+                    if (p.single_item != 0 && c % splits == split) continue;
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
                         __stcg(reinterpret_cast<uint4*>(part_tile + (c * 8 + g) * (kBlockM * 4) + slot_row),
@@ -528,7 +530,10 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
                 const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
                 const int group = t / kBlockM;
-                const int r = t % kBlockM;
+                // a warp reads the tensor-memory lanes 32 * (warp % 4) .. + 31, so its threads take those rows of the tile
+                const int r = (warp % 4) * 32 + lane;
+                const uint32_t own_taddr = tmem_base + (static_cast<uint32_t>((warp % 4) * 32) << 16);   // the item's accumulator: buffer 0
+                tc_fence_after_sync();
                 const int row = (tile % p.tiles_m) * kBlockM + r;
                 const int n0 = (tile / p.tiles_m) * BN;
                 const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
@@ -541,6 +546,15 @@ scaled_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
                     for (int sp = 0; sp < splits; ++sp) {  // split order: the sum does not depend on who adds it
+                        if (sp == split) {
+                            // this CTA's own partial of the chunk never left tensor memory
+                            uint32_t own[32];
+                            tmem_ld_32x32(own_taddr + c * 32, own);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) sum[i] += __uint_as_float(own[i]);
+                            continue;
+                        }
                         const float* const src = p.partials + (static_cast<int64_t>(sp) * num_tiles + tile) * kTileFloats + r * 4;
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
