@@ -1,0 +1,68 @@
+"""The A/B switches select older code paths of the same arithmetic: with a switch set, the results must not change by a bit.
+
+The switches are read once per process, so every setting runs in a child process that writes its outputs to a file; the parent
+computes the same calls with the defaults and compares. Covered: the direct output stores of the CTA-pair GEMMs (the default
+sends the output through bulk tensor stores) and the conv kernels that gather from global memory (the default stages halo
+tiles through the copy engine).
+"""
+
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+CHILD = textwrap.dedent(
+    """
+    import sys
+    import torch
+    sys.path.insert(0, sys.argv[2])
+    import feather_ops_b200 as fo
+    from feather_ops_b200 import int8_convrot as ic
+    from oracle import conv2d as oc
+    from oracle import scaled_mm as osm
+
+    dev = torch.device("cuda", 0)
+    out = {}
+    for m, n, k in ((600, 2304, 1536), (4096, 1024, 512)):
+        a, packed, scale, bias = (t.to(dev) for t in osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, seed=m + n))
+        out[f"smm{m}"] = fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16).cpu()
+    gen = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn((520, 1280), device=dev, generator=gen).to(torch.bfloat16)
+    g = torch.randn((520, 768), device=dev, generator=gen).to(torch.bfloat16)
+    w = (torch.randn((768, 1280), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    wq, ws = ic.quantize_convrot_weight(w)
+    packed8 = ic.prepack_int8_weight(wq)
+    out["i8f"] = ic.convrot_int8_linear(x, packed8, ws, None, torch.bfloat16, weight_packed=True).cpu()
+    out["i8b"] = ic.convrot_int8_dgrad(g, packed8, ws, torch.bfloat16, rotate_activation=False, weight_packed=True).cpu()
+    for c_out, hw in ((272, 40), (96, 264)):
+        xc, wc, bc = oc.make_inputs(2, 24, c_out, 9, hw, torch.bfloat16, seed=c_out)
+        out[f"conv{c_out}"] = fo.conv3x3_prepacked(xc.to(dev), fo.prepack_conv2d_weight_3x3(wc.to(dev)), bc.to(dev)).cpu()
+    torch.cuda.synchronize()
+    torch.save(out, sys.argv[1])
+    """
+)
+
+
+def _run(tmp_path, name, env):
+    target = tmp_path / f"{name}.pt"
+    full_env = dict(os.environ)
+    full_env.update(env)
+    done = subprocess.run([sys.executable, "-c", CHILD, str(target), ROOT], env=full_env, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    return torch.load(target, weights_only=True)
+
+
+def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
+    default = _run(tmp_path, "default", {})
+    switched = _run(tmp_path, "switched", {"FEATHER_SCALED_MM_BULK_OUT_OFF": "1", "FEATHER_INT8_BULK_OUT_OFF": "1", "FEATHER_CONV_STAGING_OFF": "1",
+                                           "FEATHER_INT8_PDL_OFF": "1"})
+    assert set(default) == set(switched)
+    for key, value in default.items():
+        assert torch.equal(value, switched[key]), key
