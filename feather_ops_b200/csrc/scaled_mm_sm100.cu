@@ -78,6 +78,7 @@ struct Params {
     uint32_t* counters;   // [tiles_m * tiles_n] tickets, zero before the launch and zero again after it
     int single_item;      // every CTA has exactly one (tile, split) item: the whole CTA adds the partials, not four warps
     int bulk_out;         // pair kernel: the output goes through shared-memory images and bulk tensor stores
+    int cluster_reduce;   // pair kernel with a K split: the CTAs of a tile form one cluster and exchange partials through distributed shared memory
 };
 
 template <int BN>
@@ -644,8 +645,11 @@ struct PairSmem {
 // CTA reading every partial through its own L2 port. All pairs of the grid are resident at once (the launcher checks), so the
 // wait cannot starve. Scratch: [tile][row half][split][chunk][4-column group][row][4] fp32; tickets: two "in" counters per tile
 // (one per row half) and one "done" counter, whose last arriver puts all three back to zero for the next launch.
+// With at most four splits, and when every cluster of the launch fits the device at once, the pairs of a tile are launched as ONE
+// cluster instead (`cluster_reduce`): partials go from tensor memory straight into the shared memory of the CTA that adds them, and
+// neither scratch nor tickets are touched. Both ways add in split order, so they give the same bits.
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const Params p) {
     using L = PairSmem;
     extern __shared__ uint8_t smem_dyn[];
@@ -664,7 +668,10 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
     const int lane = static_cast<int>(threadIdx.x) % 32;
-    const uint32_t cta = cluster_cta_rank();
+    // The cluster is one CTA pair, or with `cluster_reduce` all the pairs of a tile: ranks 2 i and 2 i + 1 are pair i.
+    const uint32_t cluster_rank = cluster_cta_rank();
+    const uint32_t cta = cluster_rank & 1u;
+    const uint32_t pair_base = cluster_rank & ~1u;
     const WaitGuard guard{abort_flag, g_status};
 
     if (threadIdx.x == 0) {
@@ -755,15 +762,15 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     }
 #pragma unroll
                     for (uint32_t dst = 0; dst < 2; ++dst) {
-                        umma_commit_pair(map_to_cta(smem_u32(&load_empty[slot.idx]), dst));
-                        umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
+                        umma_commit_pair(map_to_cta(smem_u32(&load_empty[slot.idx]), pair_base + dst));
+                        umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), pair_base + dst));
                     }
                     slot.advance(kPairLoadStages);
                     operand.advance(kPairOperandStages);
                 }
                 if (!ok) break;
 #pragma unroll
-                for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc.idx]), dst));
+                for (uint32_t dst = 0; dst < 2; ++dst) umma_commit_pair(map_to_cta(smem_u32(&tmem_full[acc.idx]), pair_base + dst));
                 acc.advance(2);
             }
         }
@@ -792,6 +799,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
             uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
             if constexpr (kSplitK) {
+                if (p.cluster_reduce) break;   // the accumulator is complete; the exchange below reads it from tensor memory
                 // this pair's partial of the tile goes to scratch; a warp writes 512 consecutive bytes per instruction
                 float* const part = p.partials + ((static_cast<int64_t>(tile) * 2 + cta) * p.splits + my_split) * (kBlockM * kPairN) + (quarter * 32 + lane) * 4;
 #pragma unroll 1
@@ -823,7 +831,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (c == kPairN / 32 - 1) {
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), 0));
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), pair_base));
                 }
                 const int col0 = n0 + c * 32;
                 uint32_t out_words[16];
@@ -940,7 +948,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), 0));
+                    if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[operand.idx]), pair_base));
                 }
                 turn = turn + 1 == kPairTeams ? 0 : turn + 1;
                 slot.advance(kPairLoadStages);
@@ -950,6 +958,79 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
 
     if constexpr (kSplitK) {
+      if (p.cluster_reduce) {
+        // The cluster holds every CTA of the tile (pair s = split s). Each CTA sends the 32-column chunks it does not add itself
+        // (chunk c belongs to split c % splits) from tensor memory straight into the owner's shared memory, which the main loop
+        // no longer needs, and then adds what it received to its own chunks in split order: no scratch, no tickets, and the
+        // partials never pass through the L2. Receive buffer of a CTA: [source split][owned chunk c / splits][4-column group]
+        // [row][4] fp32, so that the 32 lanes of a warp (32 rows) write and read 512 consecutive bytes per instruction.
+        constexpr int kGroups = (kThreads - kFirstEpilogueWarp * 32) / kBlockM;   // 128 threads (one per row) each
+        constexpr int kChunkBytes = 8 * kBlockM * 16;                              // one chunk of 128 rows x 32 columns
+        const int max_owned = (kPairN / 32 + p.splits - 1) / p.splits;
+        const int t = static_cast<int>(threadIdx.x) - kFirstEpilogueWarp * 32;
+        const int group = t / kBlockM;
+        // a warp reads the tensor-memory lanes 32 * (warp % 4) .. + 31, so its threads take those rows of the tile
+        const int r = (warp % 4) * 32 + lane;
+        const uint32_t own_taddr = tmem_base + (static_cast<uint32_t>((warp % 4) * 32) << 16);   // one item per pair: accumulator buffer 0
+        __syncthreads();
+        cluster_sync_all();   // every CTA of the tile has left its role loops: its operand rings are free
+        if (t >= 0) {
+            tc_fence_after_sync();
+            int sent = 0;
+            for (int c = 0; c < kPairN / 32; ++c) {
+                const int owner = c % p.splits;
+                if (owner == my_split) continue;
+                if (sent++ % kGroups != group) continue;
+                uint32_t v[32];
+                tmem_ld_32x32(own_taddr + c * 32, v);
+                tmem_wait_ld();
+                const uint32_t local = smem_u32(smem + (my_split * max_owned + c / p.splits) * kChunkBytes + r * 16);
+                const uint32_t remote = map_to_cta(local, static_cast<uint32_t>(2 * owner) + cta);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) st_shared_cluster_v4(remote + g * (kBlockM * 16), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+            }
+        }
+        cluster_sync_all();   // release / acquire over the cluster: every partial has landed
+        if (t >= 0 && !guard.aborted()) {
+            const int tile = first_tile;
+            int tile_m, tile_n;
+            banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
+            const int row = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM + r;
+            const int n0 = tile_n * kPairN;
+            const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
+            uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N;
+            int owned = 0;
+            for (int c = my_split; c < kPairN / 32; c += p.splits, ++owned) {
+                if (owned % kGroups != group) continue;
+                float sum[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum[i] = 0.0f;
+                for (int sp = 0; sp < p.splits; ++sp) {   // split order: the sum does not depend on who adds it
+                    if (sp == my_split) {
+                        uint32_t own[32];
+                        tmem_ld_32x32(own_taddr + c * 32, own);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) sum[i] += __uint_as_float(own[i]);
+                        continue;
+                    }
+                    const uint8_t* const src = smem + (sp * max_owned + owned) * kChunkBytes + r * 16;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 x = *reinterpret_cast<const float4*>(src + g * (kBlockM * 16));
+                        sum[4 * g] += x.x;
+                        sum[4 * g + 1] += x.y;
+                        sum[4 * g + 2] += x.z;
+                        sum[4 * g + 3] += x.w;
+                    }
+                }
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(sum[i]);
+                finish_columns<kOutBf16>(p, v, scale, row, n0 + c * 32, c_row);
+            }
+        }
+      } else {
         // Every role loop has ended. Wait until all splits of this CTA's half of the tile are in (bounded), then add the
         // partials of this CTA's share of the chunks: chunk c belongs to split c % splits. Twenty warps, one row per thread.
         __syncthreads();
@@ -1028,6 +1109,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 *done = 0u;
             }
         }
+      }
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -1433,6 +1515,54 @@ inline bool skinny_wmma_off() {
 inline int64_t pair_tiles(int64_t M, int64_t N) { return ((M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((N + kPairN - 1) / kPairN); }
 constexpr int kPairMaxSplits = kPairN / 32;   // a split owns at least one 32-column chunk of the reduction
 
+// FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF=1 keeps the K split of the pair kernel on scratch and tickets (A/B measurements). Read once per process.
+inline bool cluster_reduce_off() {
+    static const bool off = env_switch("FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF");
+    return off;
+}
+
+// The pair kernel takes its cluster size from the launch: 2 (one CTA pair), or all the pairs of a tile when they reduce a K
+// split among themselves. `cluster_reduce` is stored in the parameters the kernel sees. False if the launch is refused (a
+// cluster of that size does not fit the device), with the error cleared.
+template <typename Kernel>
+bool launch_clustered(Kernel* kernel, int cluster_ctas, unsigned grid, bool cluster_reduce, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                      const CUtensorMap& map_c, Params p, int margin_sms = 0) {
+    p.cluster_reduce = cluster_reduce ? 1 : 0;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = PairSmem::kDynamic;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_ctas);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    if (cluster_ctas > 2) {
+        // Every cluster of the launch has to be resident at once, or a second wave of clusters waits for the first (a cluster
+        // needs up to eight free SMs of ONE GPC with 214 KB of shared memory each, so fewer fit than SMs / size): asked once per
+        // device, kernel and cluster size.
+        static PerDeviceState fits[9];
+        const int resident = fits[cluster_ctas].get([&] {   // clusters that fit + 1
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess || clusters < 0) {
+                (void)cudaGetLastError();
+                clusters = 0;
+            }
+            return clusters + 1;
+        }) - 1;
+        const int needed = static_cast<int>(grid) / cluster_ctas;
+        if (needed > resident - (margin_sms + cluster_ctas - 1) / cluster_ctas) return false;
+    }
+    if (cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_c, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+
 // FEATHER_SCALED_MM_BULK_OUT_OFF=1 keeps the pair kernel's direct output stores (A/B measurements). Read once per process.
 inline bool bulk_out_off() {
     static const bool off = env_switch("FEATHER_SCALED_MM_BULK_OUT_OFF");
@@ -1517,13 +1647,17 @@ bool launch_pair_instance(const LaunchArgs& args) {
         p.counters = args.counters;
         p.band = p.tiles_m;   // one item per pair: no walk to order
         const int64_t items = static_cast<int64_t>(num_tiles) * p.splits;
-        if (p.splits < 2 || items > usable) return false;   // the caller falls back to the one-CTA split kernel
-        kernel<<<static_cast<unsigned>(2 * items), kThreads, L::kDynamic, args.stream>>>(map_a, map_b, map_c, p);
-        return cudaGetLastError() == cudaSuccess;
+        if (p.splits < 2) return false;
+        // Up to four splits the tile's pairs form ONE cluster (at most eight CTAs, the portable limit) and exchange their partials
+        // through distributed shared memory: no scratch, no tickets, and clusters need not all be resident at once.
+        if (p.splits <= 4 && !cluster_reduce_off() && launch_clustered(kernel, 2 * p.splits, static_cast<unsigned>(2 * items), true, args.stream, map_a, map_b, map_c, p, 2 * margin_pairs)) {
+            return true;
+        }
+        if (items > usable) return false;   // the caller falls back to the one-CTA split kernel
+        return launch_clustered(kernel, 2, static_cast<unsigned>(2 * items), false, args.stream, map_a, map_b, map_c, p);
     }
     const int grid = 2 * (num_tiles < usable ? num_tiles : usable);
-    kernel<<<grid, kThreads, L::kDynamic, args.stream>>>(map_a, map_b, map_c, p);
-    return cudaGetLastError() == cudaSuccess;
+    return launch_clustered(kernel, 2, static_cast<unsigned>(grid), false, args.stream, map_a, map_b, map_c, p);
 }
 
 // `split`: the K-split variant (one (tile, split) item per pair); false when the items do not fit the resident pairs.

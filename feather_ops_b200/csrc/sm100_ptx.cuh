@@ -288,6 +288,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
     return remote;
 }
 
+// 16 bytes into another CTA's shared memory (distributed shared memory; the address comes from map_to_cta)
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 // Arrive on a barrier given by its shared::cluster address (this CTA's or the peer's). Plain release
 // semantics: a cluster-scope release here costs over a thousand cycles per arrive and is not needed,
 // the operand data is published to the async proxy by the fence that precedes the arrive.

@@ -36,9 +36,10 @@ def _soak(run, copies, status):
 
 
 # rows, columns, depth: the vector kernel, the warp-MMA kernel, the skinny kernel, K splits on one row tile (128- and 256-wide),
-# K splits on CTA pairs, the one-CTA kernel, the CTA-pair kernel with a ragged last tile
+# K splits on CTA pairs (through scratch, and with two splits inside one cluster per tile), the one-CTA kernel, the CTA-pair kernel
+# with a ragged last tile
 @pytest.mark.parametrize("shape", [(1, 12288, 3072), (16, 4096, 4096), (40, 256, 2048), (100, 1024, 4096), (128, 12288, 3072), (256, 4096, 4096),
-                                   (96, 384, 1024), (600, 2304, 1536)])
+                                   (512, 4096, 4096), (96, 384, 1024), (600, 2304, 1536)])
 def test_scaled_mm_repeats(cuda_device, shape):
     import feather_ops_b200 as fo
 

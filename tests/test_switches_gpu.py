@@ -2,8 +2,9 @@
 
 The switches are read once per process, so every setting runs in a child process that writes its outputs to a file; the parent
 computes the same calls with the defaults and compares. Covered: the direct output stores of the CTA-pair GEMMs (the default
-sends the output through bulk tensor stores) and the conv kernels that gather from global memory (the default stages halo
-tiles through the copy engine).
+sends the output through bulk tensor stores), the K split through scratch and tickets (the default exchanges the partials inside a
+cluster where every cluster of the launch fits the device) and the conv kernels that gather from global memory (the default stages
+halo tiles through the copy engine).
 """
 
 import os
@@ -30,7 +31,9 @@ CHILD = textwrap.dedent(
 
     dev = torch.device("cuda", 0)
     out = {}
-    for m, n, k in ((600, 2304, 1536), (4096, 1024, 512)):
+    # the CTA-pair kernel, and its K split with two and three splits, where the tile's pairs form one cluster and exchange their
+    # partials through distributed shared memory unless the switch sends them through scratch and tickets
+    for m, n, k in ((600, 2304, 1536), (4096, 1024, 512), (512, 4096, 4096), (256, 5120, 5120), (300, 2048, 6144), (516, 2560, 4096)):
         a, packed, scale, bias = (t.to(dev) for t in osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, seed=m + n))
         out[f"smm{m}"] = fo.scaled_mm_hip(a, packed, scale, bias, torch.bfloat16).cpu()
     gen = torch.Generator(device=dev).manual_seed(5)
@@ -62,7 +65,7 @@ def _run(tmp_path, name, env):
 def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
     default = _run(tmp_path, "default", {})
     switched = _run(tmp_path, "switched", {"FEATHER_SCALED_MM_BULK_OUT_OFF": "1", "FEATHER_INT8_BULK_OUT_OFF": "1", "FEATHER_CONV_STAGING_OFF": "1",
-                                           "FEATHER_INT8_PDL_OFF": "1"})
+                                           "FEATHER_INT8_PDL_OFF": "1", "FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF": "1"})
     assert set(default) == set(switched)
     for key, value in default.items():
         assert torch.equal(value, switched[key]), key
