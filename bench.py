@@ -246,6 +246,7 @@ def cpu_baselines_for_cases() -> dict:
     out["cfg3 convrot_int8_linear"] = {**stand_in, "value": 2.0 * m * n * k / (best_g + best_q) / 1e12, "ms": (best_g + best_q) * 1e3,
                                        "sample": "recipe quantizer + fp32 matmul of the codes, all 4096 rows"}
     out["int8_scaled_mm 8192x8192x8192"] = {**stand_in, "sample": "rate of the 4096x3072x3072 stand-in (the 8192^3 product is not run on the host)"}
+    out["int8_scaled_mm_plain 8192x8192x8192"] = out["int8_scaled_mm 8192x8192x8192"]
 
     for channels, size in ((512, 128), (256, 256), (128, 512)):
         for dtype in (torch.bfloat16, torch.float16):

@@ -31,6 +31,7 @@ if not _BUILDING or "feather_ops_b200._C" in sys.modules:
         convrot_int8_linear,
         dequantize_convrot_weight,
         int8_scaled_mm,
+        int8_scaled_mm_plain,
         prepack_int8_weight,
         quantize_convrot_activation,
         quantize_convrot_weight,
@@ -45,6 +46,7 @@ if not _BUILDING or "feather_ops_b200._C" in sys.modules:
         "convrot_int8_linear",
         "dequantize_convrot_weight",
         "int8_scaled_mm",
+        "int8_scaled_mm_plain",
         "prepack_b_for_scaled_mm",
         "prepack_conv2d_weight_3x3",
         "prepack_int8_weight",

@@ -286,14 +286,35 @@ def bench_int8(device, peaks) -> list[dict]:
     record = {"case": "cfg3 convrot_int8_linear 4096x3072x3072 (quantize + GEMM, the public call)", "op": "convrot_int8_linear", "M": m, "N": n, "K": k, "cold": True,
               "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
     out.append(_rates(record, time_launches(linear, sets), flop=flop, algorithmic_bytes=float(m * k * 2 + n * k + m * n * 2), bound="tensor", peaks=peaks, int8=True))
-    del xs, qs, ss, outs, packs
+    del packs
+
+    # The same three over the unpacked [N, K] weight (`weight_packed=False`): the copy engine's boxes are operands as they land
+    weights = [wq.clone() for _ in range(sets)]
+
+    def gemm_plain(i, transposed=False):
+        j = i % sets
+        torch.ops.feather_ops.int8_scaled_mm_plain.default(qs[j], weights[j], ss[j], None if transposed else ws, None, outs[j], transposed)
+
+    def linear_plain(i):
+        j = i % sets
+        outs[j] = ic.convrot_int8_linear(xs[j], weights[j], ws, None, torch.bfloat16)
+
+    plain = []
+    for transposed in (False, True):
+        record = {"vendor_same_shape_tops": _round(vendor_here, 1), "vendor_same_shape_us": None if not vendor_here else _round(flop / vendor_here / 1e6, 2),
+                  "case": f"cfg3 int8_scaled_mm_plain 4096x3072x3072 {'backward (transposed_b)' if transposed else 'forward'}, unpacked weight", "op": "int8_scaled_mm_plain",
+                  "M": m, "N": n, "K": k, "cold": True, "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
+        plain.append(_rates(record, time_launches(lambda i, t=transposed: gemm_plain(i, t), sets), flop=flop, algorithmic_bytes=gemm_bytes, bound="tensor", peaks=peaks, int8=True))
+    record = {"case": "cfg3 convrot_int8_linear 4096x3072x3072, unpacked weight (quantize + GEMM, the public call with weight_packed=False)", "op": "convrot_int8_linear",
+              "M": m, "N": n, "K": k, "cold": True, "buffer_sets": sets, "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
+    plain.append(_rates(record, time_launches(linear_plain, sets), flop=flop, algorithmic_bytes=float(m * k * 2 + n * k + m * n * 2), bound="tensor", peaks=peaks, int8=True))
+    del xs, qs, ss, outs, weights
 
     # a large square GEMM: many waves of tiles, so the steady state of the kernel shows
     m = n = k = 8192
     a8 = torch.randint(-127, 128, (m, k), device=device, dtype=torch.int8)
     w8 = torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8)
     packed8 = ic.prepack_int8_weight(w8).reshape(-1)
-    del w8
     a_scale = torch.rand((m,), device=device) + 0.5
     w_scale = torch.rand((n,), device=device) + 0.5
     out8 = [torch.empty((m, n), device=device, dtype=torch.bfloat16) for _ in range(2)]
@@ -302,7 +323,11 @@ def bench_int8(device, peaks) -> list[dict]:
               "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
     out.append(_rates(record, time_launches(lambda i: torch.ops.feather_ops.int8_scaled_mm.default(a8, packed8, a_scale, w_scale, None, out8[i % 2], False, *tile8), 2),
                       flop=2.0 * m * n * k, algorithmic_bytes=None, bound="tensor", peaks=peaks, int8=True))
-    return out
+    record = {"case": "int8_scaled_mm_plain 8192x8192x8192, unpacked weight (steady state)", "op": "int8_scaled_mm_plain", "M": m, "N": n, "K": k, "cold": True, "buffer_sets": 2,
+              "peak_source": "vendor int8 GEMM (torch._int_mm 8192^3) timed in this run"}
+    plain.append(_rates(record, time_launches(lambda i: torch.ops.feather_ops.int8_scaled_mm_plain.default(a8, w8, a_scale, w_scale, None, out8[i % 2], False), 2),
+                        flop=2.0 * m * n * k, algorithmic_bytes=None, bound="tensor", peaks=peaks, int8=True))
+    return out + plain
 
 
 # ------------------------------------------------------------------------------------------------------------- conv

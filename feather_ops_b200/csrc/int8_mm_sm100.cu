@@ -452,33 +452,53 @@ constexpr int kPairRelayoutWarps = 8;
 constexpr int kPairThreads = 32 * (kFirstRelayoutWarp + kPairRelayoutWarps);
 constexpr int kRawBoxBytes = 32 * 128;
 
-struct PairSmem {
-    static constexpr int kRawBytes = 4 * kRawBoxBytes;       // 16 KB: 32 x 32 micro-tiles
+#ifndef FEATHER_I8_PLAIN_STAGES
+#define FEATHER_I8_PLAIN_STAGES 6
+#endif
+constexpr int kPlainLoadStages = FEATHER_I8_PLAIN_STAGES;
+constexpr int kPlainRelayWarp = kFirstEpilogueWarp + 2 * kEpilogueWarps;   // after two groups of epilogue warps
+constexpr int kPlainThreads = 32 * (kPlainRelayWarp + 1);
+
+// `kPlainB`: the weight is the released row-major `[N, K]` matrix, whose 128 x 128 byte boxes are UMMA operands as the copy engine
+// delivers them (forward: K-major, backward: MN-major). No re-layout ring then, and a deeper load ring instead.
+template <bool kPlainB>
+struct PairSmemT {
+    static constexpr int kLoadStages = kPlainB ? kPlainLoadStages : kPairLoadStages;
+    static constexpr int kOperandStages = kPlainB ? 0 : kPairOperandStages;
+    static constexpr int kOperandBars = kPlainB ? kPlainLoadStages : kPairOperandStages;   // plain: "both CTAs' loads have landed"
+    static constexpr int kRawBytes = 4 * kRawBoxBytes;       // 16 KB: 32 x 32 micro-tiles, or one 128 x 128 box of the plain weight
     static constexpr int kOperandBytes = kPairHalfN * 128;  // 16 KB
     static constexpr int kAOff = 0;
-    static constexpr int kRawOff = kAOff + kPairLoadStages * kATileBytes;
-    static constexpr int kOperandOff = kRawOff + kPairLoadStages * kRawBytes;
-    static constexpr int kColumnOff = kOperandOff + kPairOperandStages * kOperandBytes;  // 2 x (256 scales + 256 biases), fp32
+    static constexpr int kRawOff = kAOff + kLoadStages * kATileBytes;
+    static constexpr int kOperandOff = kRawOff + kLoadStages * kRawBytes;
+    static constexpr int kColumnOff = kOperandOff + kOperandStages * kOperandBytes;  // 2 x (256 scales + 256 biases), fp32
     static constexpr int kImageBytes = kBlockM * 64;         // 128 rows x 32 output columns of 16 bits: what one bulk tensor store writes
     static constexpr int kImageOff = kColumnOff + 2 * 2 * kPairN * 4;   // two images: one is written while the copy engine reads the other
     static constexpr int kBarOff = kImageOff + 2 * kImageBytes;
-    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 6 + 4;
+    static constexpr int kNumBars = 2 * kLoadStages + 2 * kOperandBars + 6 + 4;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
+    static_assert(kDynamic <= 227 * 1024, "the pair kernel's shared memory exceeds an SM's");
 };
+using PairSmem = PairSmemT<false>;
 
-template <bool kTransposedB, bool kOutBf16>
+template <bool kTransposedB, bool kOutBf16, bool kPlainB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const Params p) {
-    using L = PairSmem;
+    using L = PairSmemT<kPlainB>;
+    constexpr int kLoadStages = L::kLoadStages;
+    constexpr int kOperandBars = L::kOperandBars;
+    // Plain weight: the warps that would re-lay the weight are free, so two groups of four epilogue warps convert the two
+    // 128-column halves of a tile at once (a tile's drain is half as long, which shows at the end of the launch).
+    constexpr int kEpiWarps = kPlainB ? 2 * kEpilogueWarps : kEpilogueWarps;
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
     uint64_t* const load_full = bars;                                // local: TMA bytes of this CTA's halves
-    uint64_t* const load_empty = load_full + kPairLoadStages;        // signalled in both CTAs by CTA 0's commits
-    uint64_t* const operand_full = load_empty + kPairLoadStages;     // CTA 0 only: both CTAs' warps arrive here
-    uint64_t* const operand_empty = operand_full + kPairOperandStages;
-    uint64_t* const tmem_full = operand_empty + kPairOperandStages;
+    uint64_t* const load_empty = load_full + kLoadStages;        // signalled in both CTAs by CTA 0's commits
+    uint64_t* const operand_full = load_empty + kLoadStages;     // CTA 0 only: both CTAs' warps arrive here
+    uint64_t* const operand_empty = operand_full + kOperandBars;
+    uint64_t* const tmem_full = operand_empty + kOperandBars;
     uint64_t* const tmem_empty = tmem_full + 2;                      // CTA 0 only
     uint64_t* const columns_full = tmem_empty + 2;                   // local: the tile's column scales and biases are staged
     uint64_t* const image_ready = columns_full + 2;                  // local: the four epilogue warps have written an output image
@@ -493,20 +513,21 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         *abort_flag = 0u;
-        for (int s = 0; s < kPairLoadStages; ++s) {
+        for (int s = 0; s < kLoadStages; ++s) {
             mbar_init(&load_full[s], 1);
             mbar_init(&load_empty[s], 1);
         }
-        for (int s = 0; s < kPairOperandStages; ++s) {
+        for (int s = 0; s < kOperandBars; ++s) {
             // complete when the team's warps of both CTAs have written their halves; a warp arrives only after
-            // its CTA's load (activation tile included) has landed, so the MMA thread needs no other wait
-            mbar_init(&operand_full[s], 2 * kPairRelayoutWarps / kPairTeams);
+            // its CTA's load (activation tile included) has landed, so the MMA thread needs no other wait.
+            // Plain weight: one arrival per CTA, by the thread that watches that CTA's loads.
+            mbar_init(&operand_full[s], kPlainB ? 2 : 2 * kPairRelayoutWarps / kPairTeams);
             mbar_init(&operand_empty[s], 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
-            mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
-            mbar_init(&columns_full[s], kEpilogueWarps);
+            mbar_init(&tmem_empty[s], 2 * kEpiWarps);
+            mbar_init(&columns_full[s], kEpiWarps);
             mbar_init(&image_ready[s], kEpilogueWarps);
             mbar_init(&image_free[s], 1);
         }
@@ -554,9 +575,18 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int x0 = kTransposedB ? kb * (kBlockK * 4) : n0 * 4;
                     const int y0 = kTransposedB ? n0 / 4 : kb * (kBlockK / 4);
                     uint8_t* const raw = smem + L::kRawOff + slot.idx * L::kRawBytes;
+                    if constexpr (kPlainB) {
+                        // map_b: x = weight column (the contraction forward, the output backward), y = weight row; one 128 x 128 box
+                        if constexpr (kTransposedB) {
+                            tma_load_2d(raw, &map_b, &load_full[slot.idx], n0, kb * kBlockK);
+                        } else {
+                            tma_load_2d(raw, &map_b, &load_full[slot.idx], kb * kBlockK, n0);
+                        }
+                    } else {
 #pragma unroll
-                    for (int box = 0; box < 4; ++box) tma_load_2d(raw + box * kRawBoxBytes, &map_b, &load_full[slot.idx], x0 + box * 128, y0);
-                    slot.advance(kPairLoadStages);
+                        for (int box = 0; box < 4; ++box) tma_load_2d(raw + box * kRawBoxBytes, &map_b, &load_full[slot.idx], x0 + box * 128, y0);
+                    }
+                    slot.advance(kLoadStages);
                 }
             }
         }
@@ -575,19 +605,22 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(smem + L::kAOff + slot.idx * kATileBytes);
-                    const uint32_t b_addr = smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
+                    const uint32_t b_addr = kPlainB ? smem_u32(smem + L::kRawOff + slot.idx * L::kRawBytes)
+                                                    : smem_u32(smem + L::kOperandOff + operand.idx * L::kOperandBytes);
 #pragma unroll
                     for (int k = 0; k < kBlockK / 32; ++k) {
-                        umma_i8_pair(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), make_desc_sw128_kmajor(b_addr + k * 32), p.idesc,
-                                     (kb | k) != 0 ? 1u : 0u);
+                        // plain weight, backward: the box holds 128 contraction rows of 128 output bytes, i.e. an MN-major operand
+                        // whose 8-row groups are 1024 bytes apart; a 32-deep step is four of them
+                        const uint64_t desc_b = kPlainB && kTransposedB ? make_desc_sw128_mnmajor(b_addr + k * 32 * 128) : make_desc_sw128_kmajor(b_addr + k * 32);
+                        umma_i8_pair(tmem_d, make_desc_sw128_kmajor(a_addr + k * 32), desc_b, p.idesc, (kb | k) != 0 ? 1u : 0u);
                     }
 #pragma unroll
                     for (uint32_t dst = 0; dst < 2; ++dst) {
                         umma_commit_pair(map_to_cta(smem_u32(&load_empty[slot.idx]), dst));
-                        umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
+                        if constexpr (!kPlainB) umma_commit_pair(map_to_cta(smem_u32(&operand_empty[operand.idx]), dst));
                     }
-                    slot.advance(kPairLoadStages);
-                    operand.advance(kPairOperandStages);
+                    slot.advance(kLoadStages);
+                    operand.advance(kOperandBars);
                 }
                 if (!ok) break;
 #pragma unroll
@@ -595,13 +628,17 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 acc.advance(2);
             }
         }
-    } else if (warp < kFirstRelayoutWarp) {
+    } else if (warp < kFirstEpilogueWarp + kEpiWarps) {
         // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
         // The column scales and biases of a tile are staged in shared memory once (each epilogue warp writes
         // a quarter, one barrier arrival per warp) instead of being fetched per element. Two buffers, used
         // alternately like the accumulators: a warp refills a buffer only after every warp has arrived for the
         // tile in between, i.e. has finished reading it.
         const int quarter = warp % 4;
+        const int epi_warp = warp - kFirstEpilogueWarp;
+        const int half = epi_warp / kEpilogueWarps;                 // plain weight: the 128 output columns this group converts
+        const int c_begin = kPlainB ? half * (kPairN / 64) : 0;
+        const int c_end = c_begin + (kPlainB ? kPairN / 64 : kPairN / 32);
         const bool wide_rows = (p.N_out % 8) == 0;
         const bool has_scale = !kTransposedB && p.b_scale != nullptr;
         const bool has_bias = !kTransposedB && p.bias != nullptr;
@@ -624,8 +661,8 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             float* const col_bias = col_scale + kPairN;
             if (has_scale || has_bias) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int c = quarter * 64 + i * 32 + lane;
+                for (int i = 0; i < 8 / kEpiWarps; ++i) {
+                    const int c = kPlainB ? epi_warp * 32 + lane : quarter * 64 + i * 32 + lane;
                     const int col = n0 + c;
                     col_scale[c] = has_scale && col < p.N_out ? __ldg(p.b_scale + col) : 1.0f;
                     col_bias[c] = has_bias && col < p.N_out ? out_bits_to_float<kOutBf16>(__ldg(p.bias + col)) : 0.0f;
@@ -643,11 +680,11 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.idx * kPairN;
             uint16_t* const c_row = p.c + static_cast<int64_t>(row) * p.N_out;
 #pragma unroll 1
-            for (int c = 0; c < kPairN / 32; ++c) {
+            for (int c = c_begin; c < c_end; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32(taddr + c * 32, v);
                 tmem_wait_ld();
-                if (c == kPairN / 32 - 1) {
+                if (c == c_end - 1) {
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), 0));
@@ -677,10 +714,16 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 if (p.bulk_out) {
                     if (col0 >= p.N_out) continue;   // uniform over the four warps
-                    const uint32_t img = stores & 1u;
-                    const uint32_t use = stores >> 1;
+                    // two images used alternately; plain weight: one image per group of four warps
+                    const uint32_t img = kPlainB ? static_cast<uint32_t>(half) : stores & 1u;
+                    const uint32_t use = kPlainB ? stores : stores >> 1;
                     if (leader && use != 0) {
-                        tma_store_wait_read<1>();     // all but the newest store have been read: this image's last one too
+                        // all but the newest store have been read, this image's last one too (plain weight: this thread's only one)
+                        if constexpr (kPlainB) {
+                            tma_store_wait_read<0>();
+                        } else {
+                            tma_store_wait_read<1>();
+                        }
                         mbar_arrive(&image_free[img]);
                     }
                     ok = guard.wait(&image_free[img], (use & 1u) ^ 1u, kSiteStore);
@@ -725,6 +768,21 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             acc.advance(2);
         }
         if (p.bulk_out && leader) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
+    } else if constexpr (kPlainB) {
+        // ------------------------------------------------------------------ plain weight: one thread per CTA tells the MMA thread
+        // (CTA 0) that this CTA's boxes of a k block have landed; the other warps of this role have nothing to do
+        if (warp == kPlainRelayWarp && elect_one()) {
+            Ring slot;
+            bool ok = true;
+            for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = guard.wait(&load_full[slot.idx], slot.phase, kSiteLoadFull, 2);
+                    if (!ok) break;
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&operand_full[slot.idx]), 0));
+                    slot.advance(kLoadStages);
+                }
+            }
+        }
     } else {
         // ------------------------------------------------------------------ weight re-layout warps (this CTA's 128 operand rows)
         constexpr int kTeamThreads = kPairRelayoutWarps * 32 / kPairTeams;
@@ -822,6 +880,7 @@ struct LaunchArgs {
     bool transposed_b;
     bool out_bf16;
     cudaStream_t stream;
+    bool plain = false;   // `b` is the row-major [N, K] weight (the pair kernel only); the strides are unused
 };
 
 template <int BN, bool kTransposedB, bool kOutBf16>
@@ -869,10 +928,10 @@ inline bool bulk_out_off() {
     return off;
 }
 
-template <bool kTransposedB, bool kOutBf16>
+template <bool kTransposedB, bool kOutBf16, bool kPlainB>
 bool launch_pair_instance(const LaunchArgs& args) {
-    using L = PairSmem;
-    auto* kernel = &int8_mm_pair_kernel<kTransposedB, kOutBf16>;
+    using L = PairSmemT<kPlainB>;
+    auto* kernel = &int8_mm_pair_kernel<kTransposedB, kOutBf16, kPlainB>;
     // once per device: the shared-memory limit and how many CTA pairs fit at once (a persistent grid must be resident as a
     // whole, and a pair needs both SMs of a TPC)
     static PerDeviceState resident_pairs;
@@ -880,7 +939,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) != cudaSuccess) return 0;
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(static_cast<unsigned>(device_info().sm_count / 2 * 2));
-        config.blockDim = dim3(kPairThreads);
+        config.blockDim = dim3(kPlainB ? kPlainThreads : kPairThreads);
         config.dynamicSmemBytes = L::kDynamic;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -905,13 +964,23 @@ bool launch_pair_instance(const LaunchArgs& args) {
     // weight as a 2-D byte array: x runs along the micro-tile axis with stride 1 (forward: output steps,
     // backward: contraction steps), y along the other one
     CUtensorMap map_b;
-    const uint64_t fast_tiles = static_cast<uint64_t>((kTransposedB ? args.K : args.N_out) / 4);
-    const uint64_t slow_tiles = static_cast<uint64_t>((kTransposedB ? args.N_out : args.K) / 4);
-    const uint64_t slow_stride = static_cast<uint64_t>(kTransposedB ? args.stride_out : args.stride_kc);
-    const uint64_t b_dims[2] = {fast_tiles * 16, slow_tiles};
-    const uint64_t b_strides[1] = {slow_stride * 16};
-    const uint32_t b_box[2] = {128, 32};
-    if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if constexpr (kPlainB) {
+        // the row-major weight: x = column (the layer's input axis), y = row (its output axis)
+        const uint64_t weight_cols = static_cast<uint64_t>(kTransposedB ? args.N_out : args.K);
+        const uint64_t weight_rows = static_cast<uint64_t>(kTransposedB ? args.K : args.N_out);
+        const uint64_t b_dims[2] = {weight_cols, weight_rows};
+        const uint64_t b_strides[1] = {weight_cols};
+        const uint32_t b_box[2] = {128, 128};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    } else {
+        const uint64_t fast_tiles = static_cast<uint64_t>((kTransposedB ? args.K : args.N_out) / 4);
+        const uint64_t slow_tiles = static_cast<uint64_t>((kTransposedB ? args.N_out : args.K) / 4);
+        const uint64_t slow_stride = static_cast<uint64_t>(kTransposedB ? args.stride_out : args.stride_kc);
+        const uint64_t b_dims[2] = {fast_tiles * 16, slow_tiles};
+        const uint64_t b_strides[1] = {slow_stride * 16};
+        const uint32_t b_box[2] = {128, 32};
+        if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    }
 
     Params p{};
     p.b = args.b;
@@ -933,7 +1002,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
         p.band = static_cast<int>(band < 1 ? 1 : band);
     }
     p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
-    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN);
+    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN) | (kPlainB && kTransposedB ? kIdescBMajorMN : 0u);
     // the output as a 2-D tensor with a box of 32 columns x 128 rows (64-byte swizzle): what the epilogue's bulk stores write
     CUtensorMap map_c = map_a;   // unused without bulk_out
     p.bulk_out = (args.N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(args.c) & 15u) == 0 && !bulk_out_off()) ? 1 : 0;
@@ -950,7 +1019,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     // activations or the row scales. After a kernel that never signals its dependents this is an ordinary launch.
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(static_cast<unsigned>(grid));
-    config.blockDim = dim3(kPairThreads);
+    config.blockDim = dim3(kPlainB ? kPlainThreads : kPairThreads);   // plain: one warp watches the loads
     config.dynamicSmemBytes = L::kDynamic;
     config.stream = args.stream;
     cudaLaunchAttribute attr[1];
@@ -1156,10 +1225,16 @@ bool pair_eligible(const LaunchArgs& args) {
 }
 
 bool launch_pair(const LaunchArgs& args) {
-    if (args.transposed_b) {
-        return args.out_bf16 ? launch_pair_instance<true, true>(args) : launch_pair_instance<true, false>(args);
+    if (args.plain) {
+        if (args.transposed_b) {
+            return args.out_bf16 ? launch_pair_instance<true, true, true>(args) : launch_pair_instance<true, false, true>(args);
+        }
+        return args.out_bf16 ? launch_pair_instance<false, true, true>(args) : launch_pair_instance<false, false, true>(args);
     }
-    return args.out_bf16 ? launch_pair_instance<false, true>(args) : launch_pair_instance<false, false>(args);
+    if (args.transposed_b) {
+        return args.out_bf16 ? launch_pair_instance<true, true, false>(args) : launch_pair_instance<true, false, false>(args);
+    }
+    return args.out_bf16 ? launch_pair_instance<false, true, false>(args) : launch_pair_instance<false, false, false>(args);
 }
 
 template <int BN>
@@ -1199,6 +1274,25 @@ extern "C" bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const f
     }
     if (block_n >= 128) return i8mm::launch_for_block_n<128>(args);
     return i8mm::launch_for_block_n<64>(args);
+}
+
+// The same product over the released row-major weight `w` = `[N, K]` int8 (no prepack): forward `C[M, N] = A[M, K] W^T` with both
+// scales and the bias, backward (`transposed_b`) `C[M, K] = A[M, N] W` with the row scale only. The copy engine's 128 x 128 boxes of
+// `w` are tensor-core operands as they land, so the kernel has no re-layout stage. `a`, `w` and `c` must be 16-byte aligned, `K` a
+// multiple of 16 and `N` of 4 (backward: of 16, it is the activation's row length). No counterpart in the reference, whose kernels read the micro-tile prepack only. Returns false if the
+// arguments do not fit.
+extern "C" bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, const float* a_scale, const float* b_scale, const uint16_t* bias,
+                                            uint16_t* c, int64_t M, int64_t N, int64_t K, bool transposed_b, int output_dtype, cudaStream_t stream) {
+    using namespace feather;
+    if (M < 0 || N <= 0 || K <= 0 || N % (transposed_b ? 16 : 4) != 0 || K % 16 != 0) return false;
+    if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return false;
+    if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(c)) & 15u) != 0) return false;
+    if (transposed_b && (b_scale != nullptr || bias != nullptr)) return false;
+    if (M == 0) return true;
+    i8mm::LaunchArgs args{a, reinterpret_cast<const uint8_t*>(w), a_scale, b_scale, bias, c, M, transposed_b ? K : N, transposed_b ? N : K, 0, 0,
+                          transposed_b, output_dtype != 0, stream};
+    args.plain = true;
+    return i8mm::launch_pair(args);
 }
 
 // Reads and clears the int8 GEMM's wait-status record (see feather_scaled_mm_status).

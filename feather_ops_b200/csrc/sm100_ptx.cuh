@@ -374,6 +374,15 @@ __device__ __forceinline__ uint64_t make_desc_sw128_kmajor(uint32_t smem_addr) {
     return make_smem_desc(smem_addr, 16u, 1024u, kSwizzle128B);
 }
 
+// MN-major operand tile of one 128-byte swizzle span along M or N (128 bytes of 8-bit elements) and any number of
+// contraction rows: a row is the span for one contraction index, 8-row groups are 1024 bytes apart (the stride offset);
+// the leading offset would separate spans along M / N and is unused with a single one. Stepping along the contraction
+// is a start-address bump of whole 8-row groups. The instruction descriptor must carry the matching major bit.
+__device__ __forceinline__ uint64_t make_desc_sw128_mnmajor(uint32_t smem_addr) {
+    return make_smem_desc(smem_addr, 16u, 1024u, kSwizzle128B);
+}
+constexpr uint32_t kIdescBMajorMN = 1u << 16;
+
 // Tile walk of the persistent pair kernels: row tiles fastest inside a band of `band` row tiles, all column tiles
 // of a band before the next band. The activation rows of one band (sized by the host to a few tens of MB) then stay
 // in L2 while the band sweeps the weight; with row tiles fastest over the whole matrix, a tall activation matrix

@@ -248,6 +248,44 @@ void int8_scaled_mm(const Tensor& a, const Tensor& b_prepacked, const Tensor& a_
     STD_TORCH_CHECK(launched, "Unsupported config");
 }
 
+// The int8 GEMM over the released row-major `[N, K]` weight (no prepack). Not in the reference's schema list: it backs the
+// `weight_packed=False` calls of the Python API.
+void int8_scaled_mm_plain(const Tensor& a, const Tensor& weight, const Tensor& a_scale, const std::optional<Tensor>& b_scale,
+                          const std::optional<Tensor>& bias, Tensor& c, bool transposed_b) {
+    STD_TORCH_CHECK(a.is_cuda() && weight.is_cuda() && c.is_cuda(), "tensors must be CUDA tensors");
+    const auto device = a.get_device_index();
+    STD_TORCH_CHECK(weight.get_device_index() == device && c.get_device_index() == device, "tensors must be on the same device");
+    STD_TORCH_CHECK(a.scalar_type() == ScalarType::Char && weight.scalar_type() == ScalarType::Char, "a and weight must be int8");
+    STD_TORCH_CHECK(is_half_or_bf16(c.scalar_type()), "c must be float16 or bfloat16");
+    STD_TORCH_CHECK(a.dim() == 2 && weight.dim() == 2 && c.dim() == 2, "a, weight and c must be 2D");
+    const int64_t M = a.size(0);
+    const int64_t N = weight.size(0);
+    const int64_t K = weight.size(1);
+    STD_TORCH_CHECK(a.size(1) == (transposed_b ? N : K), "a's row length must equal the weight axis that is contracted");
+    STD_TORCH_CHECK(c.size(0) == M && c.size(1) == (transposed_b ? K : N), "c has the wrong shape");
+    STD_TORCH_CHECK(K % 16 == 0 && N % (transposed_b ? 16 : 4) == 0, "the weight axes must be multiples of 16 (forward: out_features of 4)");
+    STD_TORCH_CHECK(a.is_contiguous() && weight.is_contiguous() && c.is_contiguous(), "a, weight and c must be contiguous");
+    STD_TORCH_CHECK(a_scale.is_cuda() && a_scale.scalar_type() == ScalarType::Float && a_scale.get_device_index() == device, "a_scale must be float32 on a's device");
+    STD_TORCH_CHECK(a_scale.numel() == M && a_scale.is_contiguous(), "a_scale must have M contiguous elements");
+    STD_TORCH_CHECK(!transposed_b || (!b_scale.has_value() && !bias.has_value()), "transposed_b takes neither b_scale nor bias");
+    if (b_scale.has_value()) {
+        STD_TORCH_CHECK(b_scale->is_cuda() && b_scale->scalar_type() == ScalarType::Float && b_scale->get_device_index() == device, "b_scale must be float32 on a's device");
+        STD_TORCH_CHECK(b_scale->numel() == N && b_scale->is_contiguous(), "b_scale must have N contiguous elements");
+    }
+    if (bias.has_value()) {
+        STD_TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == c.scalar_type() && bias->get_device_index() == device, "bias must have c's dtype and device");
+        STD_TORCH_CHECK(bias->numel() == N && bias->is_contiguous(), "bias must have N contiguous elements");
+    }
+    STD_TORCH_CHECK(aligned16(a.const_data_ptr()) && aligned16(weight.const_data_ptr()) && aligned16(c.mutable_data_ptr()), "data pointers must be 16-byte aligned");
+    torch::stable::accelerator::DeviceGuard guard(device);
+    const bool launched = launch_int8_scaled_mm_plain(
+        static_cast<const int8_t*>(a.const_data_ptr()), static_cast<const int8_t*>(weight.const_data_ptr()), static_cast<const float*>(a_scale.const_data_ptr()),
+        b_scale.has_value() ? static_cast<const float*>(b_scale->const_data_ptr()) : nullptr,
+        bias.has_value() ? static_cast<const uint16_t*>(bias->const_data_ptr()) : nullptr, static_cast<uint16_t*>(c.mutable_data_ptr()), M, N, K, transposed_b,
+        c.scalar_type() == ScalarType::Half ? 0 : 1, current_stream(device));
+    STD_TORCH_CHECK(launched, "int8_scaled_mm_plain launch failed");
+}
+
 void convrot_quantize(const Tensor& x, const std::optional<Tensor>& col_scale, Tensor& q, Tensor& row_scale, bool rotate) {
     STD_TORCH_CHECK(x.is_cuda() && q.is_cuda() && row_scale.is_cuda(), "tensors must be CUDA tensors");
     STD_TORCH_CHECK(x.dim() == 2, "x must be 2D");
@@ -352,6 +390,7 @@ STABLE_TORCH_LIBRARY(feather_ops, m) {
     m.def(
         "int8_scaled_mm(Tensor a, Tensor b_prepacked, Tensor a_scale, Tensor? b_scale, Tensor? bias, Tensor(a!) c, bool transposed_b, "
         "int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n) -> ()");
+    m.def("int8_scaled_mm_plain(Tensor a, Tensor weight, Tensor a_scale, Tensor? b_scale, Tensor? bias, Tensor(a!) c, bool transposed_b) -> ()");
     m.def("convrot_quantize(Tensor x, Tensor? col_scale, Tensor(a!) q, Tensor(b!) row_scale, bool rotate) -> ()");
     m.def(
         "conv2d_3x3(Tensor x, Tensor w_prepacked, Tensor? bias, Tensor(a!) out, int warps_m, int warps_n, int repeat_m, int repeat_n, "
@@ -363,6 +402,7 @@ STABLE_TORCH_LIBRARY_IMPL(feather_ops, CUDA, m) {
     m.impl("scaled_mm_splitk", TORCH_BOX(&scaled_mm_splitk));
     m.impl("interleave_slabs", TORCH_BOX(&interleave_slabs));
     m.impl("int8_scaled_mm", TORCH_BOX(&int8_scaled_mm));
+    m.impl("int8_scaled_mm_plain", TORCH_BOX(&int8_scaled_mm_plain));
     m.impl("convrot_quantize", TORCH_BOX(&convrot_quantize));
     m.impl("conv2d_3x3", TORCH_BOX(&conv2d_3x3));
 }

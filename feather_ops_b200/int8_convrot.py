@@ -8,7 +8,16 @@ training step read that copy:
     backward  C[M, K] = A[M, N] @ W[N, K]      (`transposed_b=True`)
 
 Function names, arguments and error behaviour follow the reference module (`feather_ops/int8_convrot.py`).
+
+On sm_100a the released `[N, K]` matrix is itself what the tensor cores want: the copy engine's 128 x 128 byte boxes of it
+are K-major (forward) or MN-major (backward) operands as they land, while the micro-tile prepack has to pass through a
+re-layout stage in shared memory, which bounds that kernel. So the `weight_packed=False` calls, for which the reference
+permutes the weight on every call, run `int8_scaled_mm_plain` on the weight as it is, and that is the faster of the two
+paths here; `weight_packed=True` keeps accepting the reference's prepack unchanged. Both give the same bits.
 """
+
+import os
+import weakref
 
 import torch
 from torch.library import custom_op
@@ -121,6 +130,100 @@ def int8_scaled_mm(a, weight_prepacked, a_scale, weight_scale=None, bias=None, o
     return out
 
 
+# FEATHER_INT8_PLAIN_OFF=1 sends `weight_packed=False` calls through a per-call prepack again (A/B measurements). Read once.
+_PLAIN_OFF = os.environ.get("FEATHER_INT8_PLAIN_OFF", "") == "1"
+
+
+@custom_op("feather_ops::int8_scaled_mm_plain_auto", mutates_args=("out",))
+def _int8_scaled_mm_plain(
+    a: torch.Tensor,
+    weight: torch.Tensor,
+    a_scale: torch.Tensor,
+    weight_scale: torch.Tensor | None,
+    bias: torch.Tensor | None,
+    out: torch.Tensor,
+    transposed_b: bool,
+) -> None:
+    """The launch as one opaque node."""
+    torch.ops.feather_ops.int8_scaled_mm_plain.default(a, weight, a_scale, weight_scale, bias, out, transposed_b)
+
+
+def plain_weight_eligible(weight: torch.Tensor, transposed_b: bool) -> bool:
+    """Whether `int8_scaled_mm_plain` takes this `[N, K]` weight. It does at any number of rows: the permute that a prepack
+    per call costs (25 us for a 3072 x 3072 weight, 85-105 us for 12288 x 3072) is several times the product of a few rows
+    (13-33 us on the plain weight; 5-16 us on the warp-MMA kernel, which however reads the prepack)."""
+    if _PLAIN_OFF or weight.ndim != 2 or weight.dtype != torch.int8 or not weight.is_contiguous() or weight.data_ptr() % 16:
+        return False
+    n, k = weight.shape
+    if k % 16 or n % (16 if transposed_b else 4):
+        return False
+    return True
+
+
+def int8_scaled_mm_plain(a, weight, a_scale, weight_scale=None, bias=None, out_dtype=torch.bfloat16, transposed_b=False):
+    """`int8_scaled_mm` over the released row-major `[N, K]` weight instead of its prepack: `A @ W^T` with both scales and the
+    bias, or `A @ W` (`transposed_b`) with the row scale only. Same bits as the prepacked call. No counterpart in the
+    reference, whose kernels read the prepack only."""
+    if transposed_b and weight_scale is not None:
+        raise ValueError("transposed_b folds the weight scale into the activation quantization, so weight_scale must be None")
+    n, k = weight.shape
+    out = torch.empty((a.shape[0], k if transposed_b else n), device=a.device, dtype=out_dtype)
+    _int8_scaled_mm_plain(
+        a,
+        weight,
+        a_scale.reshape(-1).to(torch.float32),
+        None if weight_scale is None else weight_scale.reshape(-1).to(torch.float32),
+        bias,
+        out,
+        transposed_b,
+    )
+    return out
+
+
+class _UnpackedWeightCache:
+    """Row-major copies of prepacked weights, one per weight version. An entry only hits for the tensor object that created it
+    (a weak reference is kept): a freed tensor's address can come back with the same shape."""
+
+    def __init__(self, max_entries: int) -> None:
+        self._max_entries = max_entries
+        self._entries: dict = {}
+
+    def get(self, packed: torch.Tensor, n_out: int, k_in: int) -> torch.Tensor:
+        version = None if torch.is_inference_mode_enabled() else getattr(packed, "_version", None)
+        key = (packed.data_ptr(), version, packed.device, n_out, k_in)
+        hit = self._entries.get(key)
+        if hit is not None:
+            owner = hit[1]()
+            if owner is not None and owner.data_ptr() == packed.data_ptr():
+                return hit[0]
+        while len(self._entries) >= self._max_entries:
+            self._entries.pop(next(iter(self._entries)))
+        plain = unpack_int8_weight(packed.reshape(k_in // 4, n_out // 4, 4, 4)).contiguous()
+        self._entries[key] = (plain, weakref.ref(packed))
+        return plain
+
+
+_UNPACKED_CACHE: _UnpackedWeightCache | None = _UnpackedWeightCache(256) if os.environ.get("FEATHER_INT8_UNPACK_CACHE", "") == "1" else None
+_UNPACKED_MIN_ROWS = 65  # the forward product of at most 64 rows over a prepack runs on the warp-MMA kernel, which is faster still
+
+
+def cache_unpacked_weights(enabled: bool = True, max_entries: int = 256) -> None:
+    """Opt in to (or out of) row-major copies of the prepacked weights that `convrot_int8_linear` / `convrot_int8_dgrad`
+    receive with `weight_packed=True`: the first call with a weight version un-permutes it once, later calls run the faster
+    plain-weight kernel on the copy (same bits). Costs the weight's bytes a second time, hence off by default (the
+    environment variable FEATHER_INT8_UNPACK_CACHE=1 turns it on at import). No counterpart in the reference."""
+    global _UNPACKED_CACHE
+    _UNPACKED_CACHE = _UnpackedWeightCache(max_entries) if enabled else None
+
+
+def _unpacked_or_none(packed: torch.Tensor, n_out: int, k_in: int, rows: int, transposed_b: bool):
+    if _UNPACKED_CACHE is None or _PLAIN_OFF or (not transposed_b and rows < _UNPACKED_MIN_ROWS):
+        return None
+    if n_out % (16 if transposed_b else 4) or k_in % 16 or not packed.is_contiguous():
+        return None
+    return _UNPACKED_CACHE.get(packed, n_out, k_in)
+
+
 _HADAMARD_CACHE: dict = {}
 
 
@@ -209,18 +312,26 @@ def convrot_int8_linear(x, weight, weight_scale, bias=None, out_dtype=torch.bflo
     if x.shape[-1] != k_in:
         raise ValueError(f"activation has {x.shape[-1]} features, the weight {k_in}")
     q, scale = quantize_convrot_activation(x.reshape(-1, k_in), rotate=rotate_activation)
-    packed = weight if weight_packed else prepack_int8_weight(weight)
-    out = int8_scaled_mm(q, packed, scale, weight_scale.reshape(-1), bias, out_dtype, False)
+    plain = _unpacked_or_none(weight, n_out, k_in, q.shape[0], False) if weight_packed else (weight if plain_weight_eligible(weight, False) else None)
+    if plain is not None:
+        out = int8_scaled_mm_plain(q, plain, scale, weight_scale.reshape(-1), bias, out_dtype, False)
+    else:
+        packed = weight if weight_packed else prepack_int8_weight(weight)
+        out = int8_scaled_mm(q, packed, scale, weight_scale.reshape(-1), bias, out_dtype, False)
     return out.reshape(*x.shape[:-1], n_out)
 
 
 def convrot_int8_dgrad(grad_out, weight, weight_scale, out_dtype=torch.bfloat16, groupsize=CONVROT_GROUP, rotate_activation=True, weight_packed=False):
     """Input gradient `g @ W` (then rotated back): the per-channel weight scale cannot leave a sum over
     channels, so it is folded into the row-wise quantization of `grad_out`."""
-    _, k_in = _weight_extent(weight, weight_scale)
+    n_out, k_in = _weight_extent(weight, weight_scale)
     q, scale = quantize_convrot_activation(grad_out.reshape(-1, grad_out.shape[-1]), False, col_scale=weight_scale.reshape(-1))
-    packed = weight if weight_packed else prepack_int8_weight(weight)
-    out = int8_scaled_mm(q, packed, scale, None, None, out_dtype, True)
+    plain = _unpacked_or_none(weight, n_out, k_in, q.shape[0], True) if weight_packed else (weight if plain_weight_eligible(weight, True) else None)
+    if plain is not None:
+        out = int8_scaled_mm_plain(q, plain, scale, None, None, out_dtype, True)
+    else:
+        packed = weight if weight_packed else prepack_int8_weight(weight)
+        out = int8_scaled_mm(q, packed, scale, None, None, out_dtype, True)
     if rotate_activation:
         out = rotate(out, build_hadamard(groupsize, device=out.device, dtype=out.dtype), groupsize)
     return out.reshape(*grad_out.shape[:-1], k_in)

@@ -111,6 +111,16 @@ bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const float* a_sca
                            bool transposed_b, int block_warps_m, int block_warps_n, int unroll_k, int repeat_m, int repeat_n,
                            int output_dtype, feather_stream_t stream);
 
+/* The same product over the released row-major weight w = [N, K] int8, without a prepack: the 128 x 128 byte boxes that the copy
+ * engine fetches from w are tensor-core operands as they land (K-major forward, MN-major backward), so the kernel has no re-layout stage.
+ * forward (transposed_b false): c[M, N] = cast(float(a[M, K] . w^T) * a_scale[m] * b_scale[n] + bias[n]);
+ * backward (transposed_b true): c[M, K] = cast(float(a[M, N] . w) * a_scale[m]), b_scale and bias must be NULL.
+ * a, w and c 16-byte aligned; K % 16 == 0, N % 4 == 0 (backward: N % 16 == 0). output_dtype: 0 = fp16, 1 = bf16.
+ * No counterpart in the reference, whose kernels read the micro-tile prepack only (csrc/hip_kernel_int8.cu:413-432); it serves the
+ * `weight_packed=False` calls of feather_ops/int8_convrot.py:344-397, for which the reference permutes the weight on every call. */
+bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, const float* a_scale, const float* b_scale, const uint16_t* bias,
+                                 uint16_t* c, int64_t M, int64_t N, int64_t K, bool transposed_b, int output_dtype, feather_stream_t stream);
+
 /* Diagnostic for the int8 GEMM's bounded waits, as feather_scaled_mm_status. No counterpart in the reference. */
 int feather_int8_mm_status(uint32_t* out);
 

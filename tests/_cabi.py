@@ -78,6 +78,16 @@ def int8_scaled_mm(a, w_prepacked, a_scale, w_scale, bias, out_dtype, transposed
     return c
 
 
+def int8_scaled_mm_plain(a, weight, a_scale, w_scale, bias, out_dtype, transposed_b):
+    """The int8 GEMM over the row-major `[N, K]` weight. Returns None if the launcher refuses the call."""
+    n, k = weight.shape
+    c = guarded_empty((a.shape[0], k if transposed_b else n), a.device, out_dtype)
+    ok = _lib.load().launch_int8_scaled_mm_plain(
+        _ptr(a), _ptr(weight), _ptr(a_scale), _ptr(w_scale), _ptr(bias), _ptr(c), a.shape[0], n, k, transposed_b, int(out_dtype == torch.bfloat16), _stream()
+    )
+    return c if ok else None
+
+
 def conv3x3(x, w_prepacked, bias, tile=(4, 4, 2, 4, 1)):
     b, c_in, h, w = x.shape
     c_out = w_prepacked.shape[1]

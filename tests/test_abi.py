@@ -37,6 +37,9 @@ def test_launchers_reject_bad_arguments_without_touching_a_device(lib):
     assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 32, 32, 0, 0, True, True, True, 9, 9, 9, 9, 9, False, None)
     assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 40, 32, 0, 0, True, True, True, 1, 8, 4, 8, 2, False, None)
     assert not lib.launch_int8_scaled_mm(None, None, None, None, None, None, 16, 32, 32, 8, 1, False, 7, 7, 7, 7, 7, 1, None)
+    assert not lib.launch_int8_scaled_mm_plain(None, None, None, None, None, None, 16, 32, 40, False, 1, None)   # K % 16
+    assert not lib.launch_int8_scaled_mm_plain(None, None, None, None, None, None, 16, 36, 64, True, 1, None)    # backward: N % 16
+    assert lib.launch_int8_scaled_mm_plain(None, None, None, None, None, None, 0, 32, 64, False, 1, None)        # no rows: nothing to launch
     assert not lib.launch_convrot_quantize(None, None, None, None, 4, 300, 0, True, None)
     assert lib.feather_conv3x3_launch(None, None, None, None, 1, 8, 8, 8, 8, 0, 9, 9, 9, 9, 1, 1, 0, None) == 1
     assert lib.feather_conv3x3_launch(None, None, None, None, 1, 8, 8, 8, 9, 0, 4, 4, 2, 2, 2, 1, 0, None) == 1  # two rows, odd W

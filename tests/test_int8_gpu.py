@@ -160,6 +160,105 @@ def test_gemm_against_the_fp64_oracle(cuda_device, shape, transposed, out_dtype)
     assert _max_rel(out, ref) < 0.02
 
 
+PLAIN_SHAPES = SHAPES + [(1, 256, 256), (130, 132, 144), (257, 2064, 1040), (700, 640, 4112)]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("shape", PLAIN_SHAPES)
+def test_gemm_over_the_plain_weight(cuda_device, shape, transposed, out_dtype):
+    # the row-major [N, K] weight through the copy engine, no prepack: fp64 oracle, and the same bits as the prepacked kernel
+    m, n, k = shape
+    w, a, a_scale, w_scale, bias, n_out = _gemm_case(m, n, k, transposed, out_dtype, seed=m + n + 1)
+    dev = lambda t: None if t is None else t.to(cuda_device)  # noqa: E731
+    out = _cabi.int8_scaled_mm_plain(dev(a), dev(w), dev(a_scale), dev(w_scale), dev(bias), out_dtype, transposed)
+    if k % 16 or n % (16 if transposed else 4):
+        assert out is None   # refused: the rows of the weight (and of the activation) must be multiples of 16 bytes
+        return
+    _cabi.assert_clean(STATUS)
+    ref = o8.int8_scaled_mm(a, w, a_scale, w_scale, bias, out_dtype, transposed)
+    assert _max_rel(out, ref) < 0.02
+    packed = _cabi.int8_scaled_mm(dev(a), dev(o8.prepack_int8_weight(w)), dev(a_scale), dev(w_scale), dev(bias), out_dtype, transposed, n_out)
+    _cabi.assert_clean(STATUS)
+    assert torch.equal(out, packed)
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_plain_weight_int32_accumulators_are_exact(cuda_device, transposed):
+    gen = torch.Generator().manual_seed(3)
+    n, k, m = (512, 384, 300) if transposed else (384, 512, 300)
+    w = torch.randint(-2, 3, (n, k), generator=gen, dtype=torch.int8)
+    a = torch.randint(-2, 3, (m, n if transposed else k), generator=gen, dtype=torch.int8)
+    ones = torch.ones(max(m, n, k), device=cuda_device)
+    out = _cabi.int8_scaled_mm_plain(a.to(cuda_device), w.to(cuda_device), ones[:m].contiguous(), None if transposed else ones[:n].contiguous(), None,
+                                     torch.float16, transposed)
+    acc = o8.int8_accumulators(a, w, transposed)
+    assert acc.abs().max().item() < 2048
+    assert torch.equal(out.cpu().float().long(), acc)
+
+
+def test_plain_weight_operator_and_dispatch(cuda_device, monkeypatch):
+    import feather_ops_b200 as fo
+    from feather_ops_b200 import int8_convrot as ic
+
+    op = torch.ops.feather_ops.int8_scaled_mm_plain.default
+    a = torch.zeros((8, 64), device=cuda_device, dtype=torch.int8)
+    w = torch.zeros((32, 64), device=cuda_device, dtype=torch.int8)
+    s = torch.ones(8, device=cuda_device)
+    c = torch.zeros((8, 32), device=cuda_device, dtype=torch.bfloat16)
+    op(a, w, s, None, None, c, False)
+    with pytest.raises(RuntimeError, match="a and weight must be int8"):
+        op(a, w.to(torch.uint8), s, None, None, c, False)
+    with pytest.raises(RuntimeError, match="row length must equal"):
+        op(a, w, s, None, None, c, True)
+    with pytest.raises(RuntimeError, match="c has the wrong shape"):
+        op(a, w, s, None, None, torch.zeros((8, 64), device=cuda_device, dtype=torch.bfloat16), False)
+    with pytest.raises(RuntimeError, match="takes neither b_scale nor bias"):
+        op(torch.zeros((8, 32), device=cuda_device, dtype=torch.int8), w, s, torch.ones(32, device=cuda_device), None,
+           torch.zeros((8, 64), device=cuda_device, dtype=torch.bfloat16), True)
+    with pytest.raises(RuntimeError, match="multiples of 16"):
+        op(a[:, :40].contiguous(), w[:, :40].contiguous(), s, None, None, c, False)
+    with pytest.raises(ValueError, match="weight_scale must be None"):
+        fo.int8_scaled_mm_plain(a, w, s, torch.ones(32, device=cuda_device), None, torch.bfloat16, True)
+    # which calls take the plain weight: unpacked weights whose rows the copy engine can address
+    assert ic.plain_weight_eligible(w, False) and ic.plain_weight_eligible(w, True)
+    assert not ic.plain_weight_eligible(w[:, :40].contiguous(), False)
+    assert not ic.plain_weight_eligible(w.t(), False)
+    assert ic.plain_weight_eligible(torch.zeros((36, 64), device=cuda_device, dtype=torch.int8), False)
+    assert not ic.plain_weight_eligible(torch.zeros((36, 64), device=cuda_device, dtype=torch.int8), True)
+    calls = []
+    real = ic.int8_scaled_mm_plain
+    monkeypatch.setattr(ic, "int8_scaled_mm_plain", lambda *args: calls.append(args[6]) or real(*args))
+    gen = torch.Generator().manual_seed(8)
+    x = torch.randn((96, 512), generator=gen).to(torch.bfloat16).to(cuda_device)
+    wq, ws = fo.quantize_convrot_weight((torch.randn((768, 512), generator=gen) * 0.02).to(torch.bfloat16).to(cuda_device))
+    y = ic.convrot_int8_linear(x, wq, ws)
+    dx = ic.convrot_int8_dgrad(torch.randn((96, 768), generator=gen).to(torch.bfloat16).to(cuda_device), wq, ws)
+    assert calls == [False, True] and y.shape == (96, 768) and dx.shape == (96, 512)
+    ic.convrot_int8_linear(x[:3], wq, ws)                                           # a few rows too: a permute per call costs more
+    ic.convrot_int8_linear(x, fo.prepack_int8_weight(wq), ws, weight_packed=True)   # a prepacked weight stays on the kernels that read it
+    assert calls == [False, True, False]
+    # opt-in: a row-major copy of a prepacked weight, made once per weight version, then the plain-weight kernel (same bits)
+    packed = fo.prepack_int8_weight(wq)
+    y_packed = ic.convrot_int8_linear(x, packed, ws, weight_packed=True)
+    ic.cache_unpacked_weights(True)
+    try:
+        assert torch.equal(ic.convrot_int8_linear(x, packed, ws, weight_packed=True), y_packed)
+        assert torch.equal(ic.convrot_int8_linear(x, packed.reshape(-1), ws, weight_packed=True), y_packed)   # a flattened view: the same entry
+        ic.convrot_int8_linear(x, packed, ws, weight_packed=True)
+        ic.convrot_int8_dgrad(torch.zeros((4, 768), device=cuda_device, dtype=torch.bfloat16), packed, ws, weight_packed=True)
+        ic.convrot_int8_linear(x[:8], packed, ws, weight_packed=True)   # few rows: the warp-MMA kernel on the prepack
+        assert calls == [False, True, False, False, False, False, True]
+        assert len(ic._UNPACKED_CACHE._entries) == 1
+        packed.add_(1)                                                   # a new version of the weight: a new copy
+        assert torch.equal(ic.convrot_int8_linear(x, packed, ws, weight_packed=True),
+                           ic.convrot_int8_linear(x, fo.unpack_int8_weight(packed).contiguous(), ws))
+        assert len(ic._UNPACKED_CACHE._entries) == 2
+    finally:
+        ic.cache_unpacked_weights(False)
+    _cabi.assert_clean(STATUS)
+
+
 @pytest.mark.parametrize("transposed", [False, True])
 def test_every_tile_in_both_directions(cuda_device, transposed):
     from feather_ops_b200.tiles import INT8_TILES

@@ -64,3 +64,6 @@ def test_int8_linear_and_dgrad_repeat(cuda_device, shape):
     gs = [g.clone() for _ in range(3)]
     _soak(lambda i: ic.convrot_int8_linear(xs[i], packed, ws, None, torch.bfloat16, weight_packed=True), 3, "feather_int8_mm_status")
     _soak(lambda i: ic.convrot_int8_dgrad(gs[i], packed, ws, torch.bfloat16, rotate_activation=False, weight_packed=True), 3, "feather_int8_mm_status")
+    # the same over the unpacked weight (no re-layout stage; above 64 rows)
+    _soak(lambda i: ic.convrot_int8_linear(xs[i], wq, ws, None, torch.bfloat16), 3, "feather_int8_mm_status")
+    _soak(lambda i: ic.convrot_int8_dgrad(gs[i], wq, ws, torch.bfloat16, rotate_activation=False), 3, "feather_int8_mm_status")

@@ -4,7 +4,8 @@ The switches are read once per process, so every setting runs in a child process
 computes the same calls with the defaults and compares. Covered: the direct output stores of the CTA-pair GEMMs (the default
 sends the output through bulk tensor stores), the K split through scratch and tickets (the default exchanges the partials inside a
 cluster where every cluster of the launch fits the device) and the conv kernels that gather from global memory (the default stages
-halo tiles through the copy engine).
+halo tiles through the copy engine) and the int8 GEMM over an unpacked weight (the default reads the row-major weight through the copy
+engine, the switch permutes it per call and runs the re-layout kernel).
 """
 
 import os
@@ -44,6 +45,9 @@ CHILD = textwrap.dedent(
     packed8 = ic.prepack_int8_weight(wq)
     out["i8f"] = ic.convrot_int8_linear(x, packed8, ws, None, torch.bfloat16, weight_packed=True).cpu()
     out["i8b"] = ic.convrot_int8_dgrad(g, packed8, ws, torch.bfloat16, rotate_activation=False, weight_packed=True).cpu()
+    # the unpacked weight: straight through the copy engine, or (switched) permuted per call and through the re-layout kernel
+    out["i8f_plain"] = ic.convrot_int8_linear(x, wq, ws, None, torch.bfloat16).cpu()
+    out["i8b_plain"] = ic.convrot_int8_dgrad(g, wq, ws, torch.bfloat16, rotate_activation=False).cpu()
     for c_out, hw in ((272, 40), (96, 264)):
         xc, wc, bc = oc.make_inputs(2, 24, c_out, 9, hw, torch.bfloat16, seed=c_out)
         out[f"conv{c_out}"] = fo.conv3x3_prepacked(xc.to(dev), fo.prepack_conv2d_weight_3x3(wc.to(dev)), bc.to(dev)).cpu()
@@ -65,7 +69,8 @@ def _run(tmp_path, name, env):
 def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
     default = _run(tmp_path, "default", {})
     switched = _run(tmp_path, "switched", {"FEATHER_SCALED_MM_BULK_OUT_OFF": "1", "FEATHER_INT8_BULK_OUT_OFF": "1", "FEATHER_CONV_STAGING_OFF": "1",
-                                           "FEATHER_INT8_PDL_OFF": "1", "FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF": "1"})
+                                           "FEATHER_INT8_PDL_OFF": "1", "FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF": "1", "FEATHER_INT8_PLAIN_OFF": "1"})
+    assert torch.equal(default["i8f"], default["i8f_plain"]) and torch.equal(default["i8b"], default["i8b_plain"])
     assert set(default) == set(switched)
     for key, value in default.items():
         assert torch.equal(value, switched[key]), key
