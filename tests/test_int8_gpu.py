@@ -427,6 +427,17 @@ def test_compiled_caller_matches_eager(cuda_device):
     assert torch.equal(compiled, eager)
     _cabi.assert_clean(STATUS)
 
+    # the same through the unpacked weight's operator
+    plain = fo.unpack_int8_weight(packed).contiguous()
+
+    def run_plain(a, a_scale):
+        return fo.int8_scaled_mm_plain(a, plain, a_scale, w_scale, None, torch.bfloat16, False)
+
+    torch._dynamo.reset()
+    compiled = torch.compile(run_plain, fullgraph=True, dynamic=True)(a, a_scale)
+    assert torch.equal(compiled, eager)
+    _cabi.assert_clean(STATUS)
+
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(1, 256, 64), (5, 3072, 3072), (16, 1040, 528), (9, 260, 16), (16, 12288, 1024), (17, 3072, 3072), (32, 1040, 528),
