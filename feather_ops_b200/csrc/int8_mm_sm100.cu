@@ -1052,7 +1052,9 @@ __device__ __forceinline__ void mma_m16n8k32_s8(int32_t (&d)[4], const uint32_t 
 // kRowTiles 16-row tiles per warp (1 or 2: up to 32 rows); every weight dword is fetched once and used for all of them.
 // Four tiles per warp (64 rows) were measured slower than the CTA-pair kernel at every shape tried: 128 registers, one
 // block in flight.
-template <int kRowTiles, bool kOutBf16>
+// `kPlainW`: `b` is the row-major [N, K] weight instead of the prepack. A lane's B fragment is then eight consecutive bytes of
+// weight row n (the same eight contraction indices as its A fragment), one 8-byte load; the strides are unused.
+template <int kRowTiles, bool kOutBf16, bool kPlainW>
 __global__ void __launch_bounds__(32 * kWmmaWarps, kRowTiles == 1 ? 3 : 2)
 int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b, const float* __restrict__ a_scale, const float* __restrict__ b_scale,
                     const uint16_t* __restrict__ bias, uint16_t* __restrict__ c, int M, int N, int K, int64_t stride_kc, int64_t stride_out) {
@@ -1098,7 +1100,11 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
     for (int blk = 0; blk < 4; ++blk) {
         const int n = n0 + 8 * blk + g;
         col_live[blk] = n < N;
-        w_col[blk] = b + (static_cast<int64_t>(col_live[blk] ? n / 4 : 0) * stride_out) * 16 + (n % 4) * 4;
+        if constexpr (kPlainW) {
+            w_col[blk] = b + static_cast<int64_t>(col_live[blk] ? n : 0) * K + 8 * t;
+        } else {
+            w_col[blk] = b + (static_cast<int64_t>(col_live[blk] ? n / 4 : 0) * stride_out) * 16 + (n % 4) * 4;
+        }
     }
 
     for (int s0 = s_begin; s0 < s_end; s0 += kUnroll) {
@@ -1110,9 +1116,15 @@ int8_mm_wmma_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ b,
             const bool live = s0 + u < s_end && k4 < k4_total;   // k4 + 1 exists as well: K / 4 is a multiple of 4
 #pragma unroll
             for (int blk = 0; blk < 4; ++blk) {
-                const uint8_t* const src = w_col[blk] + static_cast<int64_t>(k4) * stride_kc * 16;
-                w[u][blk][0] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src)) : 0u;
-                w[u][blk][1] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src + stride_kc * 16)) : 0u;
+                if constexpr (kPlainW) {
+                    const uint2 pair = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint2*>(w_col[blk] + (s0 + u) * 32)) : make_uint2(0u, 0u);
+                    w[u][blk][0] = pair.x;
+                    w[u][blk][1] = pair.y;
+                } else {
+                    const uint8_t* const src = w_col[blk] + static_cast<int64_t>(k4) * stride_kc * 16;
+                    w[u][blk][0] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src)) : 0u;
+                    w[u][blk][1] = (live && col_live[blk]) ? __ldg(reinterpret_cast<const uint32_t*>(src + stride_kc * 16)) : 0u;
+                }
             }
 #pragma unroll
             for (int rt = 0; rt < kRowTiles; ++rt) {
@@ -1193,24 +1205,28 @@ inline bool wmma_off() {
 
 bool wmma_eligible(const LaunchArgs& args) {
     return !args.transposed_b && args.M <= kWmmaMaxRows && (args.M <= 16 || args.N_out < kWmmaTwoTileMaxN) && args.N_out >= 256 && args.K % 16 == 0 && args.N_out % 4 == 0 &&
-           (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & 3u) == 0 &&
+           (reinterpret_cast<uintptr_t>(args.a) & 7u) == 0 && (reinterpret_cast<uintptr_t>(args.b) & (args.plain ? 7u : 3u)) == 0 &&
            (reinterpret_cast<uintptr_t>(args.c) & 3u) == 0 && !wmma_off();
 }
 
 bool launch_wmma(const LaunchArgs& args) {
     const int row_tiles = args.M <= 16 ? 1 : 2;
     const dim3 grid(static_cast<unsigned>((args.N_out + 31) / 32), static_cast<unsigned>((args.M + 16 * row_tiles - 1) / (16 * row_tiles)));
-#define FEATHER_I8_WMMA_CASE(RT, OUT)                                                                                              \
-    if (row_tiles == RT && args.out_bf16 == OUT) {                                                                                 \
-        int8_mm_wmma_kernel<RT, OUT><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c,  \
-                                                                                 static_cast<int>(args.M), static_cast<int>(args.N_out),      \
-                                                                                 static_cast<int>(args.K), args.stride_kc, args.stride_out);  \
+#define FEATHER_I8_WMMA_CASE(RT, OUT, PLAIN)                                                                                       \
+    if (row_tiles == RT && args.out_bf16 == OUT && args.plain == PLAIN) {                                                          \
+        int8_mm_wmma_kernel<RT, OUT, PLAIN><<<grid, 32 * kWmmaWarps, 0, args.stream>>>(args.a, args.b, args.a_scale, args.b_scale, args.bias, args.c, \
+                                                                                        static_cast<int>(args.M), static_cast<int>(args.N_out), \
+                                                                                        static_cast<int>(args.K), args.stride_kc, args.stride_out); \
         return cudaGetLastError() == cudaSuccess;                                                                                  \
     }
-    FEATHER_I8_WMMA_CASE(1, true)
-    FEATHER_I8_WMMA_CASE(1, false)
-    FEATHER_I8_WMMA_CASE(2, true)
-    FEATHER_I8_WMMA_CASE(2, false)
+    FEATHER_I8_WMMA_CASE(1, true, false)
+    FEATHER_I8_WMMA_CASE(1, false, false)
+    FEATHER_I8_WMMA_CASE(2, true, false)
+    FEATHER_I8_WMMA_CASE(2, false, false)
+    FEATHER_I8_WMMA_CASE(1, true, true)
+    FEATHER_I8_WMMA_CASE(1, false, true)
+    FEATHER_I8_WMMA_CASE(2, true, true)
+    FEATHER_I8_WMMA_CASE(2, false, true)
 #undef FEATHER_I8_WMMA_CASE
     return false;
 }
@@ -1292,6 +1308,7 @@ extern "C" bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, co
     i8mm::LaunchArgs args{a, reinterpret_cast<const uint8_t*>(w), a_scale, b_scale, bias, c, M, transposed_b ? K : N, transposed_b ? N : K, 0, 0,
                           transposed_b, output_dtype != 0, stream};
     args.plain = true;
+    if (i8mm::wmma_eligible(args)) return i8mm::launch_wmma(args);   // a few rows, forward: the warp-MMA kernel reads the rows of w directly
     return i8mm::launch_pair(args);
 }
 

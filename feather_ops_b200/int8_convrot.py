@@ -149,9 +149,9 @@ def _int8_scaled_mm_plain(
 
 
 def plain_weight_eligible(weight: torch.Tensor, transposed_b: bool) -> bool:
-    """Whether `int8_scaled_mm_plain` takes this `[N, K]` weight. It does at any number of rows: the permute that a prepack
-    per call costs (25 us for a 3072 x 3072 weight, 85-105 us for 12288 x 3072) is several times the product of a few rows
-    (13-33 us on the plain weight; 5-16 us on the warp-MMA kernel, which however reads the prepack)."""
+    """Whether `int8_scaled_mm_plain` takes this `[N, K]` weight. It does at any number of rows: with at most 64 the
+    warp-MMA kernel reads the rows of the weight as fast as it reads a prepack (5-30 us), and the permute that a prepack per
+    call costs (25 us for a 3072 x 3072 weight, 85-105 us for 12288 x 3072) is several times that."""
     if _PLAIN_OFF or weight.ndim != 2 or weight.dtype != torch.int8 or not weight.is_contiguous() or weight.data_ptr() % 16:
         return False
     n, k = weight.shape

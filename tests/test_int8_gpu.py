@@ -160,7 +160,9 @@ def test_gemm_against_the_fp64_oracle(cuda_device, shape, transposed, out_dtype)
     assert _max_rel(out, ref) < 0.02
 
 
-PLAIN_SHAPES = SHAPES + [(1, 256, 256), (130, 132, 144), (257, 2064, 1040), (700, 640, 4112)]
+PLAIN_SHAPES = SHAPES + [(1, 256, 256), (130, 132, 144), (257, 2064, 1040), (700, 640, 4112),
+                         # forward with at most 64 rows: the warp-MMA kernel reading the rows of the weight (ragged column blocks, half k blocks)
+                         (5, 3072, 3072), (16, 1040, 528), (9, 260, 16), (33, 260, 16), (47, 3072, 1040), (64, 3072, 3072), (16, 12288, 1024)]
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
