@@ -64,6 +64,7 @@ struct Params {
     uint32_t idesc;
     int band;               // pair kernel: row tiles per band of the tile walk
     int bulk_out;           // pair kernel: the output goes through shared-memory images and bulk tensor stores (N_out % 8 == 0, c 16-byte aligned)
+    int tile_n;             // pair kernel: output columns per tile, a multiple of 16 up to 256 (below 256 only forward over the plain weight)
 };
 
 template <int BN>
@@ -547,7 +548,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles_m = (p.M + 2 * kBlockM - 1) / (2 * kBlockM);
-    const int tiles_n = (p.N_out + kPairN - 1) / kPairN;
+    const int tiles_n = (p.N_out + p.tile_n - 1) / p.tile_n;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + kBlockK - 1) / kBlockK;
     const int first_tile = static_cast<int>(blockIdx.x) / 2;
@@ -565,11 +566,12 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 int tile_m, tile_n;
                 banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
                 const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-                const int n0 = tile_n * kPairN + static_cast<int>(cta) * kPairHalfN;
+                const int n0 = tile_n * p.tile_n + static_cast<int>(cta) * (p.tile_n / 2);
+                const uint32_t weight_bytes = kPlainB && !kTransposedB ? static_cast<uint32_t>(p.tile_n / 2) * 128u : static_cast<uint32_t>(L::kRawBytes);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
+                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + weight_bytes);
                     tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
                     // map_b: x = byte offset along the faster micro-tile axis, y = step of the slower one
                     const int x0 = kTransposedB ? kb * (kBlockK * 4) : n0 * 4;
@@ -637,8 +639,9 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp % 4;
         const int epi_warp = warp - kFirstEpilogueWarp;
         const int half = epi_warp / kEpilogueWarps;                 // plain weight: the 128 output columns this group converts
-        const int c_begin = kPlainB ? half * (kPairN / 64) : 0;
-        const int c_end = c_begin + (kPlainB ? kPairN / 64 : kPairN / 32);
+        const int chunks = (p.tile_n + 31) / 32;   // the last one may hold 16 columns only
+        const int c_begin = kPlainB ? half * ((chunks + 1) / 2) : 0;
+        const int c_end = kPlainB && half == 0 ? (chunks + 1) / 2 : chunks;
         const bool wide_rows = (p.N_out % 8) == 0;
         const bool has_scale = !kTransposedB && p.b_scale != nullptr;
         const bool has_bias = !kTransposedB && p.bias != nullptr;
@@ -656,7 +659,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int tile_m, tile_n;
             banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
             const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-            const int n0 = tile_n * kPairN;
+            const int n0 = tile_n * p.tile_n;
             float* const col_scale = reinterpret_cast<float*>(smem + L::kColumnOff) + acc.idx * 2 * kPairN;
             float* const col_bias = col_scale + kPairN;
             if (has_scale || has_bias) {
@@ -712,7 +715,8 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     v[g * 4] = pack_out<kOutBf16>(f[0], f[1]);
                     v[g * 4 + 1] = pack_out<kOutBf16>(f[2], f[3]);
                 }
-                if (p.bulk_out) {
+                const int tile_cols = p.tile_n - c * 32;   // columns of this chunk that belong to the tile: 32, or 16 in a last half chunk
+                if (p.bulk_out && tile_cols >= 32) {
                     if (col0 >= p.N_out) continue;   // uniform over the four warps
                     // two images used alternately; plain weight: one image per group of four warps
                     const uint32_t img = kPlainB ? static_cast<uint32_t>(half) : stores & 1u;
@@ -751,14 +755,14 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (wide_rows) {
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
-                            if (col0 + g * 8 < p.N_out) {
+                            if (g * 8 < tile_cols && col0 + g * 8 < p.N_out) {
                                 *reinterpret_cast<uint4*>(c_row + col0 + g * 8) = make_uint4(v[g * 8], v[g * 8 + 1], v[g * 8 + 4], v[g * 8 + 5]);
                             }
                         }
                     } else {
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
-                            if (col0 + g * 4 < p.N_out) {
+                            if (g * 4 < tile_cols && col0 + g * 4 < p.N_out) {
                                 *reinterpret_cast<uint2*>(c_row + col0 + g * 4) = make_uint2(v[g * 4], v[g * 4 + 1]);
                             }
                         }
@@ -928,6 +932,40 @@ inline bool bulk_out_off() {
     return off;
 }
 
+// FEATHER_INT8_TILE_WIDTH_OFF=1 keeps 256-column tiles for every shape (A/B measurements). Read once per process.
+inline bool tile_width_off() {
+    static const bool off = env_switch("FEATHER_INT8_TILE_WIDTH_OFF");
+    return off;
+}
+
+// Output columns per tile for the forward product over the plain weight. That kernel is bound by the tensor pipe, so a tile's time
+// goes with its width, and a narrower tile can fill the last round of the persistent grid: 4096 x 3072 with 256-wide tiles are 192
+// tiles = 2.6 rounds of 74 pairs, which take three; 176-wide ones are 288 tiles = 3.9 rounds of 0.69 the length. Cost of a launch:
+// rounds x (width + a fixed part per tile, in columns); the widest tile wins a tie.
+inline int plain_tile_width(int64_t M, int64_t N_out, int pairs) {
+    constexpr int kFixedColumns = 24;
+    if (tile_width_off() || pairs <= 0) return kPairN;
+    // FEATHER_INT8_TILE_WIDTH=<multiple of 16 in 128..256> forces the width (measurements). Read once per process.
+    static const int forced = [] {
+        const char* text = std::getenv("FEATHER_INT8_TILE_WIDTH");
+        const int value = text != nullptr ? std::atoi(text) : 0;
+        return value >= kPairN / 2 && value <= kPairN && value % 16 == 0 ? value : 0;
+    }();
+    if (forced != 0) return forced;
+    const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
+    int best = kPairN;
+    int64_t best_cost = 0;
+    for (int width = kPairN; width >= kPairN / 2; width -= 16) {
+        const int64_t tiles = tiles_m * ((N_out + width - 1) / width);
+        const int64_t cost = ((tiles + pairs - 1) / pairs) * (width + kFixedColumns);
+        if (width == kPairN || cost < best_cost) {
+            best = width;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 template <bool kTransposedB, bool kOutBf16, bool kPlainB>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmemT<kPlainB>;
@@ -963,6 +1001,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     // weight as a 2-D byte array: x runs along the micro-tile axis with stride 1 (forward: output steps,
     // backward: contraction steps), y along the other one
+    const int tile_n = kPlainB && !kTransposedB ? plain_tile_width(args.M, args.N_out, pairs) : kPairN;
     CUtensorMap map_b;
     if constexpr (kPlainB) {
         // the row-major weight: x = column (the layer's input axis), y = row (its output axis)
@@ -970,7 +1009,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
         const uint64_t weight_rows = static_cast<uint64_t>(kTransposedB ? args.K : args.N_out);
         const uint64_t b_dims[2] = {weight_cols, weight_rows};
         const uint64_t b_strides[1] = {weight_cols};
-        const uint32_t b_box[2] = {128, 128};
+        const uint32_t b_box[2] = {128, kTransposedB ? 128u : static_cast<uint32_t>(tile_n / 2)};   // forward: this CTA's output channels
         if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     } else {
         const uint64_t fast_tiles = static_cast<uint64_t>((kTransposedB ? args.K : args.N_out) / 4);
@@ -1001,8 +1040,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
         if (band > p.tiles_m) band = p.tiles_m;
         p.band = static_cast<int>(band < 1 ? 1 : band);
     }
-    p.tiles_n = static_cast<int>((args.N_out + kPairN - 1) / kPairN);
-    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, kPairN) | (kPlainB && kTransposedB ? kIdescBMajorMN : 0u);
+    p.tile_n = tile_n;
+    p.tiles_n = static_cast<int>((args.N_out + tile_n - 1) / tile_n);
+    p.idesc = make_idesc(kAccS32, kFmtS8, kFmtS8, 2 * kBlockM, static_cast<uint32_t>(tile_n)) | (kPlainB && kTransposedB ? kIdescBMajorMN : 0u);
     // the output as a 2-D tensor with a box of 32 columns x 128 rows (64-byte swizzle): what the epilogue's bulk stores write
     CUtensorMap map_c = map_a;   // unused without bulk_out
     p.bulk_out = (args.N_out % 8 == 0 && (reinterpret_cast<uintptr_t>(args.c) & 15u) == 0 && !bulk_out_off()) ? 1 : 0;
@@ -1311,6 +1351,10 @@ extern "C" bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, co
     if (i8mm::wmma_eligible(args)) return i8mm::launch_wmma(args);   // a few rows, forward: the warp-MMA kernel reads the rows of w directly
     return i8mm::launch_pair(args);
 }
+
+// Output columns per tile that `launch_int8_scaled_mm_plain` picks for the forward product of `M` rows and `N` output channels on a device
+// with `pairs` resident CTA pairs (74 on a B200). For tests and logs.
+extern "C" int feather_int8_plain_tile_width(int64_t M, int64_t N, int pairs) { return feather::i8mm::plain_tile_width(M, N, pairs); }
 
 // Reads and clears the int8 GEMM's wait-status record (see feather_scaled_mm_status).
 extern "C" int feather_int8_mm_status(uint32_t* out) {

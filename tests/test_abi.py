@@ -32,6 +32,21 @@ def test_ctypes_prototypes_cover_the_header():
     assert set(declared_functions()) <= set(_lib.PROTOTYPES)
 
 
+def test_int8_plain_tile_width_fills_the_last_round(lib):
+    # rounds of 74 CTA pairs x (width + 24): 4096 x 3072 in 256-wide tiles are 192 tiles = three rounds, of which the last is 60 % full
+    width = lib.feather_int8_plain_tile_width
+    assert width(4096, 3072, 74) == 240      # 208 tiles, three rounds of shorter tiles
+    assert width(8192, 8192, 74) == 256      # 13.8 rounds: nothing to gain
+    assert width(1024, 12288, 74) == 224     # 220 tiles = 2.97 rounds instead of 192 = 2.6
+    assert width(2048, 3072, 74) == 176      # 144 tiles = two rounds instead of 96 = 1.3
+    assert width(512, 3072, 74) == 128       # one round either way: the narrowest tile, on 48 pairs instead of 24
+    assert width(65536, 12288, 74) == 256
+    for m, n in ((1, 16), (300, 260), (4096, 12288), (100000, 4112)):
+        w = width(m, n, 74)
+        assert 128 <= w <= 256 and w % 16 == 0
+    assert width(4096, 3072, 0) == 256
+
+
 def test_launchers_reject_bad_arguments_without_touching_a_device(lib):
     # unknown tile tuple, bad divisibility: refused before any CUDA call
     assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 32, 32, 0, 0, True, True, True, 9, 9, 9, 9, 9, False, None)

@@ -57,11 +57,35 @@ CHILD = textwrap.dedent(
 )
 
 
-def _run(tmp_path, name, env):
+CHILD_INT8_PLAIN = textwrap.dedent(
+    """
+    import sys
+    import torch
+    sys.path.insert(0, sys.argv[2])
+    from feather_ops_b200 import int8_convrot as ic
+
+    dev = torch.device("cuda", 0)
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(11)
+    # forward over the unpacked weight: ragged in every axis, one round and several rounds of tiles
+    for m, n, k in ((300, 260, 272), (2048, 3072, 1024), (4096, 3072, 512), (700, 648, 4112), (1100, 12288, 256)):
+        a = torch.randint(-127, 128, (m, k), device=dev, generator=gen, dtype=torch.int8)
+        w = torch.randint(-127, 128, (n, k), device=dev, generator=gen, dtype=torch.int8)
+        s = torch.rand(m, device=dev, generator=gen) * 0.01
+        ws = torch.rand(n, device=dev, generator=gen) * 0.01
+        bias = torch.randn(n, device=dev, generator=gen).to(torch.bfloat16)
+        out[f"plain{m}"] = ic.int8_scaled_mm_plain(a, w, s, ws, bias, torch.bfloat16, False).cpu()
+    torch.cuda.synchronize()
+    torch.save(out, sys.argv[1])
+    """
+)
+
+
+def _run(tmp_path, name, env, child=CHILD):
     target = tmp_path / f"{name}.pt"
     full_env = dict(os.environ)
     full_env.update(env)
-    done = subprocess.run([sys.executable, "-c", CHILD, str(target), ROOT], env=full_env, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    done = subprocess.run([sys.executable, "-c", child, str(target), ROOT], env=full_env, cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr[-2000:]
     return torch.load(target, weights_only=True)
 
@@ -74,3 +98,14 @@ def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
     assert set(default) == set(switched)
     for key, value in default.items():
         assert torch.equal(value, switched[key]), key
+
+
+def test_int8_tile_widths_give_the_same_bits(cuda_device, tmp_path):
+    # the forward product over the unpacked weight picks its tile width by shape; every width adds the same int32 sums
+    default = _run(tmp_path, "width_default", {}, CHILD_INT8_PLAIN)
+    for name, env in (("width_256", {"FEATHER_INT8_TILE_WIDTH_OFF": "1"}), ("width_176", {"FEATHER_INT8_TILE_WIDTH": "176"}),
+                      ("width_208", {"FEATHER_INT8_TILE_WIDTH": "208"})):
+        other = _run(tmp_path, name, env, CHILD_INT8_PLAIN)
+        assert set(default) == set(other)
+        for key, value in default.items():
+            assert torch.equal(value, other[key]), (name, key)
