@@ -182,7 +182,8 @@ def int8_scaled_mm_plain(a, weight, a_scale, weight_scale=None, bias=None, out_d
 
 class _UnpackedWeightCache:
     """Row-major copies of prepacked weights, one per weight version. An entry only hits for the tensor object that created it
-    (a weak reference is kept): a freed tensor's address can come back with the same shape."""
+    (a weak reference is kept): a freed tensor's address can come back with the same shape. An entry is dropped when that tensor
+    is freed, so the cache does not outlive the weights."""
 
     def __init__(self, max_entries: int) -> None:
         self._max_entries = max_entries
@@ -190,16 +191,18 @@ class _UnpackedWeightCache:
 
     def get(self, packed: torch.Tensor, n_out: int, k_in: int) -> torch.Tensor:
         version = None if torch.is_inference_mode_enabled() else getattr(packed, "_version", None)
-        key = (packed.data_ptr(), version, packed.device, n_out, k_in)
+        key = (packed.data_ptr(), packed.device, n_out, k_in)
         hit = self._entries.get(key)
         if hit is not None:
             owner = hit[1]()
-            if owner is not None and owner.data_ptr() == packed.data_ptr():
+            if owner is not None and owner.data_ptr() == packed.data_ptr() and hit[2] == version:
                 return hit[0]
-        while len(self._entries) >= self._max_entries:
+        while key not in self._entries and len(self._entries) >= self._max_entries:
             self._entries.pop(next(iter(self._entries)))
         plain = unpack_int8_weight(packed.reshape(k_in // 4, n_out // 4, 4, 4)).contiguous()
-        self._entries[key] = (plain, weakref.ref(packed))
+        entries = self._entries
+        # one copy per weight: a new version replaces the old one, and the copy goes when the prepacked tensor does
+        self._entries[key] = (plain, weakref.ref(packed, lambda _ref, key=key: entries.pop(key, None)), version)
         return plain
 
 

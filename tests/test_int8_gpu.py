@@ -2,6 +2,8 @@
 kernel's arithmetic, GEMM against the fp64 oracle with the reference's tolerance (tests/test_int8_convrot.py
 there: max-rel < 0.02 with a 1e-3 floor), compositions bit-exact against their parts."""
 
+import gc
+
 import pytest
 import torch
 
@@ -252,10 +254,13 @@ def test_plain_weight_operator_and_dispatch(cuda_device, monkeypatch):
         ic.convrot_int8_linear(x[:8], packed, ws, weight_packed=True)   # few rows: the warp-MMA kernel on the prepack
         assert calls == [False, True, False, False, False, False, True]
         assert len(ic._UNPACKED_CACHE._entries) == 1
-        packed.add_(1)                                                   # a new version of the weight: a new copy
+        packed.add_(1)                                                   # a new version of the weight: a new copy replaces the old one
         assert torch.equal(ic.convrot_int8_linear(x, packed, ws, weight_packed=True),
                            ic.convrot_int8_linear(x, fo.unpack_int8_weight(packed).contiguous(), ws))
-        assert len(ic._UNPACKED_CACHE._entries) == 2
+        assert len(ic._UNPACKED_CACHE._entries) == 1
+        del packed
+        gc.collect()
+        assert len(ic._UNPACKED_CACHE._entries) == 0                     # the copy goes with the weight
     finally:
         ic.cache_unpacked_weights(False)
     _cabi.assert_clean(STATUS)
