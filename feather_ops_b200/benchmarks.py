@@ -466,19 +466,23 @@ def bench_cells(device, peaks, groups=None) -> list[dict]:
             if k % 16 == 0 and n % 4 == 0:
                 w8 = torch.randint(-127, 128, (n, k), device=device, dtype=torch.int8)
                 packed8 = ic.prepack_int8_weight(w8)
-                del w8
                 a8 = torch.randint(-127, 128, (m, k), device=device, dtype=torch.int8)
                 a_scale = torch.rand((m,), device=device) + 0.5
                 w_scale = torch.rand((n,), device=device) + 0.5
                 us = time_launches(lambda i: ic._int8_scaled_mm_auto(a8, packed8, a_scale, w_scale, None, c, False), 1, rounds=3, round_ms=20.0)["us"]
                 record.update(int8_forward_us=_round(us, 1), int8_forward_tops=None if us is None else _round(flop / us / 1e6, 1))
+                # the same product over the unpacked weight (what `weight_packed=False` calls run)
+                us = time_launches(lambda i: ic._int8_scaled_mm_plain(a8, w8, a_scale, w_scale, None, c, False), 1, rounds=3, round_ms=20.0)["us"]
+                record.update(int8_plain_forward_us=_round(us, 1), int8_plain_forward_tops=None if us is None else _round(flop / us / 1e6, 1))
                 if n % 16 == 0:
                     g8 = torch.randint(-127, 128, (m, n), device=device, dtype=torch.int8)
                     dx = torch.empty((m, k), device=device, dtype=torch.bfloat16)
                     us = time_launches(lambda i: ic._int8_scaled_mm_auto(g8, packed8, a_scale, None, None, dx, True), 1, rounds=3, round_ms=20.0)["us"]
                     record.update(int8_backward_us=_round(us, 1), int8_backward_tops=None if us is None else _round(flop / us / 1e6, 1))
+                    us = time_launches(lambda i: ic._int8_scaled_mm_plain(g8, w8, a_scale, None, None, dx, True), 1, rounds=3, round_ms=20.0)["us"]
+                    record.update(int8_plain_backward_us=_round(us, 1), int8_plain_backward_tops=None if us is None else _round(flop / us / 1e6, 1))
                     del g8, dx
-                del packed8, a8
+                del packed8, a8, w8
             del c
             out.append(record)
     return out
