@@ -473,10 +473,10 @@ struct PairSmemT {
     static constexpr int kRawOff = kAOff + kLoadStages * kATileBytes;
     static constexpr int kOperandOff = kRawOff + kLoadStages * kRawBytes;
     static constexpr int kColumnOff = kOperandOff + kOperandStages * kOperandBytes;  // 2 x (256 scales + 256 biases), fp32
-    static constexpr int kImageBytes = kBlockM * 64;         // 128 rows x 32 output columns of 16 bits: what one bulk tensor store writes
-    static constexpr int kImageOff = kColumnOff + 2 * 2 * kPairN * 4;   // two images: one is written while the copy engine reads the other
+    static constexpr int kImageBytes = kBlockM * 64;         // 128 rows x 32 output columns of 16 bits: four warps' images of 32 rows, one bulk tensor store each
+    static constexpr int kImageOff = kColumnOff + 2 * 2 * kPairN * 4;   // eight warp images: two per warp used alternately, or one for each of eight warps
     static constexpr int kBarOff = kImageOff + 2 * kImageBytes;
-    static constexpr int kNumBars = 2 * kLoadStages + 2 * kOperandBars + 6 + 4;
+    static constexpr int kNumBars = 2 * kLoadStages + 2 * kOperandBars + 6;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
     static_assert(kDynamic <= 227 * 1024, "the pair kernel's shared memory exceeds an SM's");
@@ -502,8 +502,6 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* const tmem_full = operand_empty + kOperandBars;
     uint64_t* const tmem_empty = tmem_full + 2;                      // CTA 0 only
     uint64_t* const columns_full = tmem_empty + 2;                   // local: the tile's column scales and biases are staged
-    uint64_t* const image_ready = columns_full + 2;                  // local: the four epilogue warps have written an output image
-    uint64_t* const image_free = image_ready + 2;                    // local: the copy engine has read it
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
@@ -529,8 +527,6 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kEpiWarps);
             mbar_init(&columns_full[s], kEpiWarps);
-            mbar_init(&image_ready[s], kEpilogueWarps);
-            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_a);
@@ -645,12 +641,11 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool wide_rows = (p.N_out % 8) == 0;
         const bool has_scale = !kTransposedB && p.b_scale != nullptr;
         const bool has_bias = !kTransposedB && p.bias != nullptr;
-        // With `bulk_out` a chunk of 128 rows x 32 columns goes into a 64-byte-swizzled shared-memory image that one thread hands
-        // to the copy engine (which clips at M and N_out): a lane holds one row, so the direct stores are 32 requests of 16
-        // bytes per warp instruction, 4096 per tile, and the drain of a pair's last tile has nothing to hide behind.
-        const bool leader = quarter == 0 && lane == 0;
-        const int image_row_index = quarter * 32 + lane;
-        const int twist = (image_row_index >> 1) & 3;
+        // With `bulk_out` a warp's 32 rows x 32 columns of a chunk go into a 64-byte-swizzled shared-memory image that its first lane
+        // hands to the copy engine (which clips at M and N_out): a lane holds one row, so the direct stores are 32 requests of 16
+        // bytes per warp instruction, 4096 per tile, and the drain of a pair's last tile has nothing to hide behind. One image per
+        // warp, so that the warps never wait for one another: two used alternately, or (plain weight, eight warps) one.
+        const int twist = (lane >> 1) & 3;   // 64-byte swizzle: the 16-byte chunk index is XORed with bits 7-8 of the address (the images are 2 KB apart)
         uint32_t stores = 0;
         Ring acc;
         bool ok = true;
@@ -717,39 +712,31 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 const int tile_cols = p.tile_n - c * 32;   // columns of this chunk that belong to the tile: 32, or 16 in a last half chunk
                 if (p.bulk_out && tile_cols >= 32) {
-                    if (col0 >= p.N_out) continue;   // uniform over the four warps
-                    // two images used alternately; plain weight: one image per group of four warps
-                    const uint32_t img = kPlainB ? static_cast<uint32_t>(half) : stores & 1u;
-                    const uint32_t use = kPlainB ? stores : stores >> 1;
-                    if (leader && use != 0) {
-                        // all but the newest store have been read, this image's last one too (plain weight: this thread's only one)
-                        if constexpr (kPlainB) {
-                            tma_store_wait_read<0>();
-                        } else {
-                            tma_store_wait_read<1>();
+                    if (col0 >= p.N_out) continue;
+                    // before the warp overwrites an image its lane's store from it must have been read: all but the newest store
+                    // with two images, every store with one
+                    if (stores >= (kPlainB ? 1u : 2u)) {
+                        if (lane == 0) {
+                            if constexpr (kPlainB) {
+                                tma_store_wait_read<0>();
+                            } else {
+                                tma_store_wait_read<1>();
+                            }
                         }
-                        mbar_arrive(&image_free[img]);
+                        __syncwarp();
                     }
-                    ok = guard.wait(&image_free[img], (use & 1u) ^ 1u, kSiteStore);
-                    if (!ok) break;
-                    uint8_t* const image = smem + L::kImageOff + img * L::kImageBytes;
-                    uint8_t* const image_row = image + image_row_index * 64;
+                    uint8_t* const image = smem + L::kImageOff + (kPlainB ? epi_warp : static_cast<int>(stores & 1u) * kEpilogueWarps + quarter) * (32 * 64);
+                    uint8_t* const image_row = image + lane * 64;
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         *reinterpret_cast<uint4*>(image_row + ((g ^ twist) << 4)) = make_uint4(v[g * 8], v[g * 8 + 1], v[g * 8 + 4], v[g * 8 + 5]);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&image_ready[img]);
-                    if (leader) {
-                        ok = guard.wait(&image_ready[img], use & 1u, kSiteStore, 1);
-                        if (ok) {
-                            tma_store_2d(&map_c, image, col0, m0);
-                            tma_store_commit();
-                        }
+                    if (lane == 0) {
+                        tma_store_2d(&map_c, image, col0, m0 + quarter * 32);
+                        tma_store_commit();
                     }
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (!ok) break;
                     ++stores;
                 } else if (row < p.M) {
                     if (wide_rows) {
@@ -771,7 +758,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
             acc.advance(2);
         }
-        if (p.bulk_out && leader) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
+        if (p.bulk_out && lane == 0) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
     } else if constexpr (kPlainB) {
         // ------------------------------------------------------------------ plain weight: one thread per CTA tells the MMA thread
         // (CTA 0) that this CTA's boxes of a k block have landed; the other warps of this role have nothing to do
@@ -1049,7 +1036,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     if (p.bulk_out) {
         const uint64_t c_dims[2] = {static_cast<uint64_t>(args.N_out), static_cast<uint64_t>(args.M)};
         const uint64_t c_strides[1] = {static_cast<uint64_t>(args.N_out) * 2};
-        const uint32_t c_box[2] = {32, kBlockM};
+        const uint32_t c_box[2] = {32, 32};   // one epilogue warp's rows of a 32-column chunk
         if (!encode_map(&map_c, kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.c, c_dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_64B)) return false;
     }
     const int num_tiles = p.tiles_m * p.tiles_n;

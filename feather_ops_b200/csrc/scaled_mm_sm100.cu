@@ -628,10 +628,10 @@ struct PairSmem {
     static constexpr int kAOff = 0;
     static constexpr int kOperandOff = kAOff + kPairLoadStages * kATileBytes;
     static constexpr int kRawOff = kOperandOff + kPairOperandStages * kOperandBytes;
-    static constexpr int kImageBytes = kBlockM * 64;   // 128 rows x 32 output columns of 16 bits: what one bulk tensor store writes
-    static constexpr int kImageOff = kRawOff + kPairLoadStages * kRawBytes;   // two images: one is written while the copy engine reads the other
+    static constexpr int kImageBytes = kBlockM * 64;   // 128 rows x 32 output columns of 16 bits: four warps' slices of 32 rows, one bulk tensor store each
+    static constexpr int kImageOff = kRawOff + kPairLoadStages * kRawBytes;   // two images: a warp writes its slice of one while the copy engine reads that of the other
     static constexpr int kBarOff = kImageOff + 2 * kImageBytes;
-    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 4 + 4;
+    static constexpr int kNumBars = 2 * kPairLoadStages + 2 * kPairOperandStages + 4;
     static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
     static constexpr int kDynamic = kTotal + 1024;
     static_assert(kImageOff % 1024 == 0, "swizzled images sit on a 1 KB boundary");
@@ -661,8 +661,6 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint64_t* const operand_empty = operand_full + kPairOperandStages;
     uint64_t* const tmem_full = operand_empty + kPairOperandStages;
     uint64_t* const tmem_empty = tmem_full + 2;                        // used in CTA 0 only
-    uint64_t* const image_ready = tmem_empty + 2;                      // local: the four epilogue warps have written an output image
-    uint64_t* const image_free = image_ready + 2;                      // local: the copy engine has read it
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
@@ -687,8 +685,6 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kEpilogueWarps);
-            mbar_init(&image_ready[s], kEpilogueWarps);
-            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_a);
@@ -778,12 +774,11 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         // ------------------------------------------------------------------ epilogue (this CTA's 128 rows)
         const int quarter = warp % 4;
         const float scale = p.scale != nullptr ? __ldg(p.scale) : 1.0f;
-        // With `bulk_out` a chunk of 128 rows x 32 columns goes into a 64-byte-swizzled shared-memory image that one thread hands
-        // to the copy engine (which clips at M and N): a lane holds one row, so the direct stores are 32 requests of 16 bytes
-        // per warp instruction, and the drain of a pair's last tile has nothing to hide behind.
-        const bool leader = quarter == 0 && lane == 0;
-        const int image_row_index = quarter * 32 + lane;
-        const int twist = (image_row_index >> 1) & 3;
+        // With `bulk_out` a warp's 32 rows x 32 columns of a chunk go into a 64-byte-swizzled shared-memory image that its first lane
+        // hands to the copy engine (which clips at M and N): a lane holds one row, so the direct stores are 32 requests of 16 bytes
+        // per warp instruction, and the drain of a pair's last tile has nothing to hide behind. One image per warp rather than one
+        // per chunk: the four warps then never wait for one another (two hand-offs per chunk cost a quarter of the epilogue's time).
+        const int twist = (lane >> 1) & 3;   // 64-byte swizzle: the 16-byte chunk index is XORed with bits 7-8 of the address (the slices are 2 KB apart)
         uint32_t stores = 0;
         Ring acc;
         bool ok = true;
@@ -869,39 +864,32 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     }
                 }
                 if (p.bulk_out) {
-                    if (col0 >= p.N) continue;   // uniform over the four warps
+                    if (col0 >= p.N) continue;
+                    // a warp's 32 rows of the chunk are an image of their own (2 KB, two of them used alternately) that the warp's
+                    // first lane hands to the copy engine: no hand-off between the warps, only the lane's own stores to wait for
                     const uint32_t img = stores & 1u;
-                    const uint32_t use = stores >> 1;
-                    if (leader && use != 0) {
-                        tma_store_wait_read<1>();     // all but the newest store have been read: this image's last one too
-                        mbar_arrive(&image_free[img]);
+                    if (stores >= 2) {
+                        if (lane == 0) tma_store_wait_read<1>();   // all but this lane's newest store have been read: this image's last one too
+                        __syncwarp();
                     }
-                    ok = guard.wait(&image_free[img], (use & 1u) ^ 1u, kSiteStore);
-                    if (!ok) break;
-                    uint8_t* const image = smem + L::kImageOff + img * L::kImageBytes;
-                    uint8_t* const image_row = image + image_row_index * 64;
+                    uint8_t* const image = smem + L::kImageOff + img * L::kImageBytes + quarter * (32 * 64);
+                    uint8_t* const image_row = image + lane * 64;
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         *reinterpret_cast<uint4*>(image_row + ((g ^ twist) << 4)) = make_uint4(out_words[4 * g], out_words[4 * g + 1], out_words[4 * g + 2], out_words[4 * g + 3]);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&image_ready[img]);
-                    if (leader) {
-                        ok = guard.wait(&image_ready[img], use & 1u, kSiteStore, 1);
-                        if (ok) {
-                            tma_store_2d(&map_c, image, col0, m0);
-                            tma_store_commit();
-                        }
+                    if (lane == 0) {
+                        tma_store_2d(&map_c, image, col0, m0 + quarter * 32);
+                        tma_store_commit();
                     }
-                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                    if (!ok) break;
                     ++stores;
                 }
             }
             acc.advance(2);
         }
-        if (!kSplitK && p.bulk_out && leader) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
+        if (!kSplitK && p.bulk_out && lane == 0) tma_store_wait<0>();   // the images must outlive the copy engine's reads, and the stores the kernel
     } else {
         // ------------------------------------------------------------------ upcast warps (this CTA's weight half)
         // The warps form kPairTeams teams that take the k blocks in turn, so a team has kPairTeams k-block times
@@ -1633,7 +1621,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     if (p.bulk_out) {
         const uint64_t c_dims[2] = {static_cast<uint64_t>(args.N), static_cast<uint64_t>(args.M)};
         const uint64_t c_strides[1] = {static_cast<uint64_t>(args.N) * 2};
-        const uint32_t c_box[2] = {32, kBlockM};
+        const uint32_t c_box[2] = {32, 32};   // one epilogue warp's rows of a 32-column chunk
         if (!encode_map(&map_c, kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.c, c_dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_64B)) return false;
     }
     const int num_tiles = p.tiles_m * p.tiles_n;
