@@ -398,8 +398,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const __grid_const
 // taps 0..8), so the results are bit-identical to the other kernels.
 //
 // Output: a lane holds one output channel, so storing straight to NCHW makes every warp store 32 requests of 16 bytes.
-// The epilogue warps instead lay 128 channels x 32 pixels into a swizzled shared-memory image that one thread hands to
-// the copy engine (a 4-D bulk tensor store, which also clips at the image edge and at C_out).
+// Every epilogue warp instead lays its 32 channels x 32 pixels into a swizzled shared-memory image of its own that its first
+// lane hands to the copy engine (a 4-D bulk tensor store, which also clips at the image edge and at C_out).
 //
 // The re-layout is ONE team that visits every use of every slot: it waits on barriers that the copy engine
 // completes, in any order across slots, and a parity wait cannot tell "my phase has completed" from "the phase before
@@ -419,7 +419,7 @@ constexpr int kStagedEpilogueWarps = 8;
 constexpr int kStagedFirstGatherWarp = kFirstEpilogueWarp + kStagedEpilogueWarps;
 constexpr int kStagedThreads = 32 * (kStagedFirstGatherWarp + kGatherWarps);
 constexpr int kOutImageBytes = 128 * 64;   // 128 output channels x 32 pixels of 16 bits: what one bulk tensor store writes
-constexpr int kOutImages = 2;              // per half of the epilogue warps: one is written while the copy engine reads the other
+constexpr int kOutImages = 2;              // per half of the epilogue warps: a warp writes its slice of one while the copy engine reads that of the other
 
 struct TileRange {
     int begin, end;
@@ -492,9 +492,7 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
     uint64_t* const rec_empty = rec_full + kMaxSlots;          // MMA commit: the records have been read
     uint64_t* const tmem_full = rec_empty + kMaxSlots;
     uint64_t* const tmem_empty = tmem_full + 2;
-    uint64_t* const image_ready = tmem_empty + 2;              // [half][image]: the half's four warps have written the output image
-    uint64_t* const image_free = image_ready + 2 * kOutImages;  // [half][image]: the copy engine has read it
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2 * kOutImages);
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
@@ -517,10 +515,6 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], kStagedEpilogueWarps);
-        }
-        for (int s = 0; s < 2 * kOutImages; ++s) {
-            mbar_init(&image_ready[s], kStagedEpilogueWarps / 2);
-            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_w);
@@ -624,8 +618,7 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp % 4;                            // the lane quarter of tensor memory this warp may read
         const int half = (warp - kFirstEpilogueWarp) / 4;        // which half of a tile's chunks it takes
-        const bool leader = quarter == 0 && lane == 0;           // issues this half's bulk stores and waits for them
-        uint32_t stores = 0;                                     // bulk stores of this half so far
+        uint32_t stores = 0;                                     // bulk stores of this warp so far
         uint32_t q = 0;
         bool ok = true;
         for (int tile = range.begin; ok && tile < range.end; ++tile, ++q) {
@@ -640,9 +633,8 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccColumns;
             const int chunks = p.bn / 32;                       // per output row; rows * chunks is even
             const int mine = p.rows * chunks / 2;
-            const int row = quarter * 32 + lane;                 // this lane's output channel inside the tile
             uint8_t* const images = out_smem + half * kOutImages * kOutImageBytes;
-            const int twist = (row >> 1) & 3;                    // the 64-byte swizzle of the tensor map: 16-byte chunk ^= bits 7..8 of the offset
+            const int twist = (lane >> 1) & 3;                   // the 64-byte swizzle of the tensor map: 16-byte chunk ^= bits 7..8 of the offset
 #pragma unroll 1
             for (int i = half * mine; i < (half + 1) * mine; ++i) {
                 const int r = i / chunks;
@@ -658,22 +650,17 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
                 }
                 if (h >= p.H || tc.w0 + c * 32 >= p.W) continue;   // uniform over the four warps of this half
                 // A lane storing its channel's pixels straight to global memory makes every warp store 32 requests of 16
-                // bytes. Instead the four warps of a half lay 128 channels x 32 pixels into a shared-memory image (64-byte
-                // rows, swizzled so that a quarter warp covers all banks) and one thread hands it to the copy engine, which
-                // also clips at the image edge and at C_out. The hand-offs are mbarriers with bounded waits, like every
-                // other wait of the kernel.
-                const uint32_t img = stores % kOutImages;       // this store's image and which use of it this is
-                const uint32_t use = stores / kOutImages;
-                uint64_t* const ready = &image_ready[half * kOutImages + img];
-                uint64_t* const freed = &image_free[half * kOutImages + img];
-                if (leader && use != 0) {
-                    tma_store_wait_read<kOutImages - 1>();        // all but the newest stores have been read: this image's last one too
-                    mbar_arrive(freed);
+                // bytes. Instead a warp lays its 32 channels x 32 pixels into a shared-memory image (64-byte rows, swizzled
+                // so that a quarter warp covers all banks) and its first lane hands it to the copy engine, which also clips
+                // at the image edge and at C_out. One image per warp (of two used alternately): the warps of a half never
+                // wait for one another, only a lane for the copy engine's read of its own store before last.
+                const uint32_t img = stores % kOutImages;       // this store's image
+                if (stores >= kOutImages) {
+                    if (lane == 0) tma_store_wait_read<kOutImages - 1>();   // all but this lane's newest stores have been read: this image's last one too
+                    __syncwarp();
                 }
-                ok = guard.wait(freed, (use & 1u) ^ 1u, kSiteStore);
-                if (!ok) break;
-                uint8_t* const image = images + img * kOutImageBytes;
-                uint8_t* const image_row = image + row * 64;
+                uint8_t* const image = images + img * kOutImageBytes + quarter * (32 * 64);   // this warp's 32 channels
+                uint8_t* const image_row = image + lane * 64;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
@@ -685,20 +672,14 @@ __global__ void __launch_bounds__(kStagedThreads, 1) conv3x3_staged_kernel(const
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(ready);
-                if (leader) {
-                    ok = guard.wait(ready, use & 1u, kSiteStore, 1);
-                    if (ok) {
-                        tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0, tc.b);
-                        tma_store_commit();
-                    }
+                if (lane == 0) {
+                    tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0 + quarter * 32, tc.b);
+                    tma_store_commit();
                 }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
                 ++stores;
             }
         }
-        if (leader) tma_store_wait<0>();   // the image must outlive the copy engine's reads, and the stores the kernel
+        if (lane == 0) tma_store_wait<0>();   // the image must outlive the copy engine's reads, and the stores the kernel
     } else {
         // ------------------------------------------------------------------ re-layout warps
         // A raw box is [16 channels][halo_rows][box_w pixels]; halo column hc is staged pixel hc + 7 (pixel i of the tile's
@@ -784,13 +765,13 @@ inline bool encode_weight_map(CUtensorMap* map, const void* wp, int C_out, int g
 // The NCHW input as a 4-D tensor [W][H][C_in][B] with a box of `box_w` pixels x `box_h` rows x 16 channels of one image:
 // what the staged kernels fetch per 16-channel group. Coordinates outside the image (the padding ring, the rounded-up
 // box, channels past C_in) read as zero. Needs W % 8 == 0 (strides are multiples of 16 bytes).
-// The NCHW output as a 4-D tensor [W][H][C_out][B] with a box of 32 pixels x 128 channels of one row and image, 64-byte
+// The NCHW output as a 4-D tensor [W][H][C_out][B] with a box of 32 pixels x 32 channels (one epilogue warp's) of one row and image, 64-byte
 // swizzle (the image rows in shared memory are 64 bytes): what the staged kernels' epilogues store. The copy engine
 // clips the box at W and at C_out. Needs W % 8 == 0.
 inline bool encode_output_map(CUtensorMap* map, void* y, int B, int C_out, int H, int W, bool bf16) {
     const uint64_t dims[4] = {static_cast<uint64_t>(W), static_cast<uint64_t>(H), static_cast<uint64_t>(C_out), static_cast<uint64_t>(B)};
     const uint64_t strides[3] = {static_cast<uint64_t>(W) * 2, static_cast<uint64_t>(H) * W * 2, static_cast<uint64_t>(C_out) * H * W * 2};
-    const uint32_t box[4] = {32u, 1u, static_cast<uint32_t>(kBlockM), 1u};
+    const uint32_t box[4] = {32u, 1u, 32u, 1u};   // one epilogue warp's 32 channels
     return encode_map(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, y, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
@@ -1099,7 +1080,7 @@ constexpr int kPairWeightSlots = 3;
 constexpr int kPairActSlots = 3;
 constexpr int kPairStagedItems = (2 * kPairHaloRows * (kPairBN / 2 + 2) + kGatherWarps * 32 - 1) / (kGatherWarps * 32);
 constexpr int kPairStagedSmemBytes = kPairWeightSlots * kWeightStageBytes + 2 * kOutImages * kOutImageBytes + kPairActSlots * (kPairActStageBytes + kPairStagingBytes) +
-                                     (2 * kPairWeightSlots + 3 * kPairActSlots + 4 + 4 * kOutImages) * 8 + 16 + 1024;
+                                     (2 * kPairWeightSlots + 3 * kPairActSlots + 4) * 8 + 16 + 1024;
 static_assert(kPairStagedSmemBytes <= 227 * 1024, "a CTA's shared memory");
 
 template <bool kBf16>
@@ -1119,9 +1100,7 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     uint64_t* const act_empty = act_full + kPairActSlots;           // signalled in both CTAs by CTA 0's commits
     uint64_t* const tmem_full = act_empty + kPairActSlots;
     uint64_t* const tmem_empty = tmem_full + 2;                     // CTA 0 only
-    uint64_t* const image_ready = tmem_empty + 2;                   // local, [row][image]: the row's four warps have written the output image
-    uint64_t* const image_free = image_ready + 2 * kOutImages;       // local: the copy engine has read it
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(image_free + 2 * kOutImages);
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* const abort_flag = tmem_slot + 1;
 
     const int warp = static_cast<int>(threadIdx.x) / 32;
@@ -1143,10 +1122,6 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         for (int s = 0; s < 2; ++s) {
             mbar_init(&tmem_full[s], 1);
             mbar_init(&tmem_empty[s], 2 * kStagedEpilogueWarps);
-        }
-        for (int s = 0; s < 2 * kOutImages; ++s) {
-            mbar_init(&image_ready[s], kStagedEpilogueWarps / 2);
-            mbar_init(&image_free[s], 1);
         }
         mbar_init_fence();
         tma_prefetch_desc(&map_w);
@@ -1255,11 +1230,9 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         // ------------------------------------------------------------------ epilogue (this CTA's 128 channels; two warps per lane quarter, one output row each)
         const int quarter = warp % 4;
         const int r = (warp - kFirstEpilogueWarp) / 4;
-        const bool leader = quarter == 0 && lane == 0;           // issues this row's bulk stores and waits for them
-        const int row = quarter * 32 + lane;                     // this lane's output channel inside the CTA's 128
         uint8_t* const images = out_smem + r * kOutImages * kOutImageBytes;
-        const int twist = (row >> 1) & 3;                        // the 64-byte swizzle of the tensor map
-        uint32_t stores = 0;                                     // bulk stores of this row's warps so far
+        const int twist = (lane >> 1) & 3;                       // the 64-byte swizzle of the tensor map
+        uint32_t stores = 0;                                     // bulk stores of this warp so far
         uint32_t q = 0;
         bool ok = true;
         for (int tile = range.begin; ok && tile < range.end; ++tile, ++q) {
@@ -1287,17 +1260,12 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 if (h >= p.H || tc.w0 + c * 32 >= p.W) continue;   // uniform over the four warps of this row
                 // the output goes through a shared-memory image and a bulk tensor store, as in conv3x3_staged_kernel
                 const uint32_t img = stores % kOutImages;
-                const uint32_t use = stores / kOutImages;
-                uint64_t* const ready = &image_ready[r * kOutImages + img];
-                uint64_t* const freed = &image_free[r * kOutImages + img];
-                if (leader && use != 0) {
-                    tma_store_wait_read<kOutImages - 1>();
-                    mbar_arrive(freed);
+                if (stores >= kOutImages) {
+                    if (lane == 0) tma_store_wait_read<kOutImages - 1>();
+                    __syncwarp();
                 }
-                ok = guard.wait(freed, (use & 1u) ^ 1u, kSiteStore);
-                if (!ok) break;
-                uint8_t* const image = images + img * kOutImageBytes;
-                uint8_t* const image_row = image + row * 64;
+                uint8_t* const image = images + img * kOutImageBytes + quarter * (32 * 64);   // this warp's 32 channels
+                uint8_t* const image_row = image + lane * 64;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
@@ -1309,20 +1277,14 @@ conv3x3_pair_staged_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(ready);
-                if (leader) {
-                    ok = guard.wait(ready, use & 1u, kSiteStore, 1);
-                    if (ok) {
-                        tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0, tc.b);
-                        tma_store_commit();
-                    }
+                if (lane == 0) {
+                    tma_store_4d(&map_y, image, tc.w0 + c * 32, h, tc.m0 + quarter * 32, tc.b);
+                    tma_store_commit();
                 }
-                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-                if (!ok) break;
                 ++stores;
             }
         }
-        if (leader) tma_store_wait<0>();   // the image must outlive the copy engine's reads, and the stores the kernel
+        if (lane == 0) tma_store_wait<0>();   // the image must outlive the copy engine's reads, and the stores the kernel
     } else {
         // ------------------------------------------------------------------ re-layout warps (output row h0 + cta)
         // From the slot's staging buffer [16 channels][3 halo rows][144 pixels] (halo column hc is staged pixel hc + 7) into
@@ -1504,7 +1466,7 @@ int launch(const void* x, const void* wp, const void* bias, void* y, int B, int 
         p.staging_bytes = boxes * 16 * (rows + 2) * box_w * 2;   // a multiple of 256 bytes
         // Ring depths: two weight slots, three raw halo tiles in flight and two record slots at least; what is left of the
         // shared memory goes to a third weight slot (a step of one tile holds a slot only half as long), then a fourth raw tile.
-        const int fixed_bytes = 2 * kOutImages * kOutImageBytes + (6 * kMaxSlots + 4 + 4 * kOutImages) * 8 + 16 + 1024;
+        const int fixed_bytes = 2 * kOutImages * kOutImageBytes + (6 * kMaxSlots + 4) * 8 + 16 + 1024;
         const int budget = 227 * 1024 - fixed_bytes;
         p.weight_slots = 2;
         p.raw_slots = 2;
