@@ -38,6 +38,7 @@ PROTOTYPES = {
     ),
     "feather_scaled_mm_set_sm_margin": (_c_int, [_c_int]),
     "launch_interleave_slabs": (_c_bool, [_ptr, _ptr, _i64, _i64, _i64, _ptr]),
+    "feather_scaled_mm_pair_tile_width": (_c_int, [_i64, _i64, _c_int]),
     "feather_scaled_mm_status": (_c_int, [_ptr]),
     "launch_convrot_quantize": (_c_bool, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _c_int, _c_bool, _ptr]),
     "launch_int8_scaled_mm": (

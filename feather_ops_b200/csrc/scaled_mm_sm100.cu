@@ -79,6 +79,7 @@ struct Params {
     int single_item;      // every CTA has exactly one (tile, split) item: the whole CTA adds the partials, not four warps
     int bulk_out;         // pair kernel: the output goes through shared-memory images and bulk tensor stores
     int cluster_reduce;   // pair kernel with a K split: the CTAs of a tile form one cluster and exchange partials through distributed shared memory
+    int tile_n;           // pair kernel without a K split: output columns per tile, a multiple of 32 from 128 to 256
 };
 
 template <int BN>
@@ -702,7 +703,8 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const uint32_t tmem_base = *tmem_slot;
 
     const int tiles_m = (p.M + 2 * kBlockM - 1) / (2 * kBlockM);
-    const int tiles_n = (p.N + kPairN - 1) / kPairN;
+    const int tile_cols = kSplitK ? kPairN : p.tile_n;   // output columns per tile; each CTA stages half of them as weight rows
+    const int tiles_n = (p.N + tile_cols - 1) / tile_cols;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + kBlockK - 1) / kBlockK;
     // plain: pair i walks tiles i, i + pairs, ...; split K: pair i has the one item (tile i / splits, split i % splits)
@@ -722,11 +724,12 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 int tile_m, tile_n;
                 banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
                 const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-                const int n0 = tile_n * kPairN + static_cast<int>(cta) * kPairHalfN;
+                const int n0 = tile_n * tile_cols + static_cast<int>(cta) * (tile_cols / 2);
+                const uint32_t raw_bytes = static_cast<uint32_t>(kSlabsPerBlock * (tile_cols / 2) * 16);   // the box: [slab][this CTA's columns][16]
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + L::kRawBytes);
+                    mbar_arrive_expect_tx(&load_full[slot.idx], kATileBytes + raw_bytes);
                     tma_load_2d(smem + L::kAOff + slot.idx * kATileBytes, &map_a, &load_full[slot.idx], kb * kBlockK, m0);
                     tma_load_2d(smem + L::kRawOff + slot.idx * L::kRawBytes, &map_b, &load_full[slot.idx], n0 * 2, kb * kSlabsPerBlock);
                     slot.advance(kPairLoadStages);
@@ -786,7 +789,7 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             int tile_m, tile_n;
             banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
             const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
-            const int n0 = tile_n * kPairN;
+            const int n0 = tile_n * tile_cols;
             ok = guard.wait(&tmem_full[acc.idx], acc.phase, kSiteTmemFull);
             if (!kSplitK && !ok) break;   // the K-split path below meets its named barrier whatever the wait returned
             tc_fence_after_sync();
@@ -818,12 +821,13 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 }
                 break;   // one item per pair
             }
+            const int chunks = tile_cols / 32;
 #pragma unroll 1
-            for (int c = 0; c < kPairN / 32; ++c) {
+            for (int c = 0; c < chunks; ++c) {
                 uint32_t v[32];
                 tmem_ld_32x32(taddr + c * 32, v);
                 tmem_wait_ld();
-                if (c == kPairN / 32 - 1) {
+                if (c == chunks - 1) {
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc.idx]), pair_base));
@@ -902,6 +906,15 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         constexpr int kUnits = kPairHalfN * kSlabsPerBlock;
         constexpr int kUnitsPerThread = kUnits / kTeamThreads;
         static_assert(kUnits % kTeamThreads == 0, "the weight half tile must split evenly over a team");
+        // a narrower tile has fewer cells per k block: cell u sits at byte 16 u of the box, and where it goes does not depend on the k block
+        const int half_cols = tile_cols / 2;
+        const int units = half_cols * kSlabsPerBlock;
+        uint32_t dst_offset[kUnitsPerThread];
+#pragma unroll
+        for (int i = 0; i < kUnitsPerThread; ++i) {
+            const int u = t + i * kTeamThreads;
+            dst_offset[i] = sw128_offset(static_cast<uint32_t>(u % half_cols), 2u * static_cast<uint32_t>(u / half_cols));
+        }
         Ring slot, operand;
         bool ok = true;
         uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
@@ -915,12 +928,12 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     uint8_t* const dst = smem + L::kOperandOff + operand.idx * L::kOperandBytes;
                     uint4 cells[kUnitsPerThread];
 #pragma unroll
-                    for (int i = 0; i < kUnitsPerThread; ++i) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kTeamThreads) * 16);
+                    for (int i = 0; i < kUnitsPerThread; ++i) {
+                        if (t + i * kTeamThreads < units) cells[i] = *reinterpret_cast<const uint4*>(raw + (t + i * kTeamThreads) * 16);
+                    }
 #pragma unroll
                     for (int i = 0; i < kUnitsPerThread; ++i) {
-                        const int u = t + i * kTeamThreads;
-                        const int row = u % kPairHalfN;
-                        const int slab = u / kPairHalfN;
+                        if (t + i * kTeamThreads >= units) continue;
                         const uint32_t w[4] = {cells[i].x, cells[i].y, cells[i].z, cells[i].w};
                         uint32_t h[8];
 #pragma unroll
@@ -931,8 +944,8 @@ scaled_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                                 h[2 * q + 1] = f16x2_to_bf16x2(h[2 * q + 1]);
                             }
                         }
-                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab)) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4*>(dst + sw128_offset(row, 2 * slab + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+                        *reinterpret_cast<uint4*>(dst + dst_offset[i]) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(dst + (dst_offset[i] ^ 16u)) = make_uint4(h[4], h[5], h[6], h[7]);
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
@@ -1557,6 +1570,40 @@ inline bool bulk_out_off() {
     return off;
 }
 
+// FEATHER_SCALED_MM_TILE_WIDTH_OFF=1 keeps 256-column tiles for every shape, FEATHER_SCALED_MM_TILE_WIDTH=<multiple of 32 in 128..256>
+// forces a width (A/B measurements). Read once per process.
+inline int forced_tile_width() {
+    static const int forced = [] {
+        if (env_switch("FEATHER_SCALED_MM_TILE_WIDTH_OFF")) return kPairN;
+        const char* text = std::getenv("FEATHER_SCALED_MM_TILE_WIDTH");
+        const int value = text != nullptr ? std::atoi(text) : 0;
+        return value >= kPairN / 2 && value <= kPairN && value % 32 == 0 ? value : 0;
+    }();
+    return forced;
+}
+
+// Output columns per tile of the pair kernel without a K split. A tile fetches its 256 activation rows whatever its width, so its time is
+// modelled as a part that goes with the width and an equal part that does not; a narrower tile pays when it fills the last round of the
+// persistent grid (1024 x 12288: 192 tiles of 256 columns are 2.6 rounds of 74 pairs and take three, 220 tiles of 224 columns are 2.97).
+// The widest tile wins a tie.
+inline int pair_tile_width(int64_t M, int64_t N, int pairs) {
+    const int forced = forced_tile_width();
+    if (forced != 0) return forced;
+    if (pairs <= 0) return kPairN;
+    const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
+    int best = kPairN;
+    int64_t best_cost = 0;
+    for (int width = kPairN; width >= kPairN / 2; width -= 32) {
+        const int64_t tiles = tiles_m * ((N + width - 1) / width);
+        const int64_t cost = ((tiles + pairs - 1) / pairs) * (width + kPairN + 48);
+        if (width == kPairN || cost < best_cost) {
+            best = width;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>
 bool launch_pair_instance(const LaunchArgs& args) {
     using L = PairSmem;
@@ -1586,6 +1633,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
         return clusters;
     });
     if (pairs <= 0) return false;
+    const int margin_pairs = (g_sm_margin.load(std::memory_order_relaxed) + 1) / 2;
+    const int usable = pairs - margin_pairs > 0 ? pairs - margin_pairs : 1;
+    const int tile_n = kSplitK ? kPairN : pair_tile_width(args.M, args.N, usable);
     CUtensorMap map_a, map_b;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(args.K), static_cast<uint64_t>(args.M)};
@@ -1600,7 +1650,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
         const uint64_t k16_rows = static_cast<uint64_t>((args.K + 127) / 128) * 8;
         const uint64_t dims[2] = {static_cast<uint64_t>(args.N) * 2, k16_rows};
         const uint64_t strides[1] = {static_cast<uint64_t>(args.N) * 16};
-        const uint32_t box[2] = {kPairHalfN * 2, kSlabsPerBlock};
+        const uint32_t box[2] = {static_cast<uint32_t>(tile_n), kSlabsPerBlock};   // a CTA's half of the tile's columns, two 8-byte words each
         if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, args.b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
     }
     Params p{};
@@ -1612,8 +1662,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
     p.K = static_cast<int>(args.K);
     p.tiles_m = static_cast<int>((args.M + 2 * kBlockM - 1) / (2 * kBlockM));
     p.band = tile_band(2 * kBlockM * args.K * 2, p.tiles_m);
-    p.tiles_n = static_cast<int>((args.N + kPairN - 1) / kPairN);
-    p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, kPairN);
+    p.tile_n = tile_n;
+    p.tiles_n = static_cast<int>((args.N + tile_n - 1) / tile_n);
+    p.idesc = make_idesc(kAccF32, args.a_bf16 ? kFmtBF16 : kFmtF16, kOperandBf16 ? kFmtBF16 : kFmtF16, 2 * kBlockM, static_cast<uint32_t>(tile_n));
     p.bias_vec = (reinterpret_cast<uintptr_t>(args.bias) & 0xfu) == 0u ? 1 : 0;
     // the output as a 2-D tensor with a box of 32 columns x 128 rows (64-byte swizzle): what the epilogue's bulk stores write
     CUtensorMap map_c = map_a;   // unused without bulk_out
@@ -1625,8 +1676,6 @@ bool launch_pair_instance(const LaunchArgs& args) {
         if (!encode_map(&map_c, kOutBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, args.c, c_dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_64B)) return false;
     }
     const int num_tiles = p.tiles_m * p.tiles_n;
-    const int margin_pairs = (g_sm_margin.load(std::memory_order_relaxed) + 1) / 2;
-    const int usable = pairs - margin_pairs > 0 ? pairs - margin_pairs : 1;
     if constexpr (kSplitK) {
         const int num_kb = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
         p.splits = effective_splits(args.K, args.splits < kPairMaxSplits ? args.splits : kPairMaxSplits);
@@ -2380,6 +2429,10 @@ extern "C" bool launch_interleave_slabs(const void* slabs, void* out, int64_t wo
                                                                                              width_bytes / 16);
     return cudaGetLastError() == cudaSuccess;
 }
+
+// Output columns per tile that the CTA-pair kernel (256-wide tile tuples, more than 128 rows, no K split) uses for `M` rows and `N` columns
+// when `pairs` CTA pairs are resident (74 on a B200). For tests and logs.
+extern "C" int feather_scaled_mm_pair_tile_width(int64_t M, int64_t N, int pairs) { return feather::smm::pair_tile_width(M, N, pairs); }
 
 // Reads (and clears) the status record the kernel's bounded waits report into: out[0] = wait site
 // (0 = every wait completed) | tag << 8, out[1] = block index. Synchronizes the device.

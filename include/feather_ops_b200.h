@@ -87,6 +87,12 @@ int feather_scaled_mm_set_sm_margin(int sms);
  * [rows][world * width] matrix. Returns false for bad arguments. No counterpart in the reference. */
 bool launch_interleave_slabs(const void* slabs, void* out, int64_t world, int64_t rows, int64_t width_bytes, feather_stream_t stream);
 
+/* Output columns per tile (a multiple of 32 from 128 to 256) that launch_scaled_mm's CTA-pair kernel uses for M rows and N columns when `pairs`
+ * CTA pairs are resident (74 on a B200): the width that minimises rounds of the persistent grid x (width + 304), i.e. a narrower tile only
+ * where it fills the last round. The tile tuple of the call only says "256 wide" (csrc/hip_kernel.cu:825-846 takes the tuple as it is).
+ * No counterpart in the reference. */
+int feather_scaled_mm_pair_tile_width(int64_t M, int64_t N, int pairs);
+
 /* Diagnostic: reads and clears the record that the scaled_mm kernel's bounded device waits report into.
  * out[0] = 0 when every wait completed, else the wait site; out[1] = block index. Synchronizes the device.
  * Returns 0 on success. No counterpart in the reference (its kernels have no device-side waits). */

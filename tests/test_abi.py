@@ -47,6 +47,21 @@ def test_int8_plain_tile_width_fills_the_last_round(lib):
     assert width(4096, 3072, 0) == 256
 
 
+def test_scaled_mm_pair_tile_width_only_narrows_to_fill_a_round(lib):
+    # rounds of 74 CTA pairs x (width + 304): a tile fetches its 256 activation rows whatever its width
+    width = lib.feather_scaled_mm_pair_tile_width
+    assert width(4096, 12288, 74) == 256     # the metric shape: 768 tiles = 10.4 rounds, nothing narrower pays
+    assert width(4096, 3072, 74) == 256
+    assert width(65536, 12288, 74) == 256
+    assert width(1024, 12288, 74) == 224     # 220 tiles = 2.97 rounds instead of 192 = 2.6
+    assert width(2048, 3072, 74) == 192      # 128 tiles = 1.7 rounds instead of 96 = 1.3
+    assert width(512, 3072, 74) == 128       # one round either way
+    for m, n in ((129, 16), (300, 272), (4096, 9216), (100000, 4112)):
+        w = width(m, n, 74)
+        assert 128 <= w <= 256 and w % 32 == 0
+    assert width(4096, 3072, 0) == 256
+
+
 def test_launchers_reject_bad_arguments_without_touching_a_device(lib):
     # unknown tile tuple, bad divisibility: refused before any CUDA call
     assert not lib.launch_scaled_mm(None, None, None, None, None, 16, 32, 32, 0, 0, True, True, True, 9, 9, 9, 9, 9, False, None)

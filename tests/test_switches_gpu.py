@@ -57,6 +57,28 @@ CHILD = textwrap.dedent(
 )
 
 
+CHILD_SCALED_MM_PAIR = textwrap.dedent(
+    """
+    import sys
+    import torch
+    sys.path.insert(0, sys.argv[2])
+    import feather_ops_b200  # noqa: F401
+    from oracle import scaled_mm as osm
+
+    dev = torch.device("cuda", 0)
+    out = {}
+    # the CTA-pair kernel without a K split (256-wide tile tuple, more than 128 rows): ragged in every axis, one and several rounds of tiles
+    for m, n, k in ((300, 272, 272), (2048, 3072, 512), (1100, 12288, 256), (4112, 1536, 1024), (516, 2576, 4096)):
+        a, packed, scale, bias = (t.to(dev) for t in osm.make_inputs(m, n, k, torch.bfloat16, torch.float8_e5m2, torch.bfloat16, seed=m + n))
+        c = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+        torch.ops.feather_ops.scaled_mm.default(a, packed, scale, bias, c, 1, 8, 4, 8, 2, False)
+        out[f"pair{m}"] = c.cpu()
+    torch.cuda.synchronize()
+    torch.save(out, sys.argv[1])
+    """
+)
+
+
 CHILD_INT8_PLAIN = textwrap.dedent(
     """
     import sys
@@ -106,6 +128,16 @@ def test_int8_tile_widths_give_the_same_bits(cuda_device, tmp_path):
     for name, env in (("width_256", {"FEATHER_INT8_TILE_WIDTH_OFF": "1"}), ("width_176", {"FEATHER_INT8_TILE_WIDTH": "176"}),
                       ("width_208", {"FEATHER_INT8_TILE_WIDTH": "208"})):
         other = _run(tmp_path, name, env, CHILD_INT8_PLAIN)
+        assert set(default) == set(other)
+        for key, value in default.items():
+            assert torch.equal(value, other[key]), (name, key)
+
+
+def test_scaled_mm_tile_widths_give_the_same_bits(cuda_device, tmp_path):
+    # the pair kernel picks its tile width by shape; a tile's columns are accumulated in the same order whatever its width
+    default = _run(tmp_path, "smm_width_default", {}, CHILD_SCALED_MM_PAIR)
+    for name, env in (("smm_width_256", {"FEATHER_SCALED_MM_TILE_WIDTH_OFF": "1"}), ("smm_width_160", {"FEATHER_SCALED_MM_TILE_WIDTH": "160"})):
+        other = _run(tmp_path, name, env, CHILD_SCALED_MM_PAIR)
         assert set(default) == set(other)
         for key, value in default.items():
             assert torch.equal(value, other[key]), (name, key)
