@@ -46,7 +46,7 @@ PROTOTYPES = {
         [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _c_bool, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
     ),
     "launch_int8_scaled_mm_plain": (_c_bool, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _c_bool, _c_int, _ptr]),
-    "feather_int8_plain_tile_width": (_c_int, [_i64, _i64, _c_int]),
+    "feather_int8_plain_tile_width": (_c_int, [_i64, _i64, _c_int, _c_bool]),
     "feather_int8_mm_status": (_c_int, [_ptr]),
     "feather_conv3x3_launch": (
         _c_int,

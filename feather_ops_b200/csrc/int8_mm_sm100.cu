@@ -929,7 +929,9 @@ inline bool tile_width_off() {
 // goes with its width, and a narrower tile can fill the last round of the persistent grid: 4096 x 3072 with 256-wide tiles are 192
 // tiles = 2.6 rounds of 74 pairs, which take three; 176-wide ones are 288 tiles = 3.9 rounds of 0.69 the length. Cost of a launch:
 // rounds x (width + a fixed part per tile, in columns); the widest tile wins a tie.
-inline int plain_tile_width(int64_t M, int64_t N_out, int pairs) {
+// `step`: 16 forward. Backward 64: a CTA's half of the tile's columns is the x coordinate of its weight boxes, which the copy engine wants on
+// a 16-byte boundary (so 32 at least), and an MN-major operand of 80 or 112 columns per CTA was measured a third slower than one of 96 or 128.
+inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) {
     constexpr int kFixedColumns = 24;
     if (tile_width_off() || pairs <= 0) return kPairN;
     // FEATHER_INT8_TILE_WIDTH=<multiple of 16 in 128..256> forces the width (measurements). Read once per process.
@@ -938,11 +940,11 @@ inline int plain_tile_width(int64_t M, int64_t N_out, int pairs) {
         const int value = text != nullptr ? std::atoi(text) : 0;
         return value >= kPairN / 2 && value <= kPairN && value % 16 == 0 ? value : 0;
     }();
-    if (forced != 0) return forced;
+    if (forced != 0) return forced % step == 0 ? forced : kPairN;
     const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
     int best = kPairN;
     int64_t best_cost = 0;
-    for (int width = kPairN; width >= kPairN / 2; width -= 16) {
+    for (int width = kPairN; width >= kPairN / 2; width -= step) {
         const int64_t tiles = tiles_m * ((N_out + width - 1) / width);
         const int64_t cost = ((tiles + pairs - 1) / pairs) * (width + kFixedColumns);
         if (width == kPairN || cost < best_cost) {
@@ -988,7 +990,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     // weight as a 2-D byte array: x runs along the micro-tile axis with stride 1 (forward: output steps,
     // backward: contraction steps), y along the other one
-    const int tile_n = kPlainB && !kTransposedB ? plain_tile_width(args.M, args.N_out, pairs) : kPairN;
+    const int tile_n = kPlainB ? plain_tile_width(args.M, args.N_out, pairs, kTransposedB ? 64 : 16) : kPairN;
     CUtensorMap map_b;
     if constexpr (kPlainB) {
         // the row-major weight: x = column (the layer's input axis), y = row (its output axis)
@@ -1339,9 +1341,11 @@ extern "C" bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, co
     return i8mm::launch_pair(args);
 }
 
-// Output columns per tile that `launch_int8_scaled_mm_plain` picks for the forward product of `M` rows and `N` output channels on a device
-// with `pairs` resident CTA pairs (74 on a B200). For tests and logs.
-extern "C" int feather_int8_plain_tile_width(int64_t M, int64_t N, int pairs) { return feather::i8mm::plain_tile_width(M, N, pairs); }
+// Output columns per tile that `launch_int8_scaled_mm_plain` picks for a product of `M` rows and `N` output columns (backward: the weight's
+// input features) on a device with `pairs` resident CTA pairs (74 on a B200). For tests and logs.
+extern "C" int feather_int8_plain_tile_width(int64_t M, int64_t N, int pairs, bool transposed_b) {
+    return feather::i8mm::plain_tile_width(M, N, pairs, transposed_b ? 64 : 16);
+}
 
 // Reads and clears the int8 GEMM's wait-status record (see feather_scaled_mm_status).
 extern "C" int feather_int8_mm_status(uint32_t* out) {

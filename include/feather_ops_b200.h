@@ -127,10 +127,11 @@ bool launch_int8_scaled_mm(const int8_t* a, const uint8_t* b, const float* a_sca
 bool launch_int8_scaled_mm_plain(const int8_t* a, const int8_t* w, const float* a_scale, const float* b_scale, const uint16_t* bias,
                                  uint16_t* c, int64_t M, int64_t N, int64_t K, bool transposed_b, int output_dtype, feather_stream_t stream);
 
-/* Output columns per tile (a multiple of 16 in 128..256) that launch_int8_scaled_mm_plain picks for the forward product of M rows and N
- * output channels when `pairs` CTA pairs are resident (74 on a B200): the width that minimises rounds of the persistent grid x (width + a
- * fixed part per tile). No counterpart in the reference (its tile tuples are picked in Python, feather_ops/int8_convrot.py:28-82). */
-int feather_int8_plain_tile_width(int64_t M, int64_t N, int pairs);
+/* Output columns per tile (forward: a multiple of 16 in 128..256; backward: 128, 192 or 256) that launch_int8_scaled_mm_plain picks for a
+ * product of M rows and N output columns when `pairs` CTA pairs are resident (74 on a B200): the width that minimises rounds of the
+ * persistent grid x (width + a fixed part per tile). No counterpart in the reference (its tile tuples are picked in Python,
+ * feather_ops/int8_convrot.py:28-82). */
+int feather_int8_plain_tile_width(int64_t M, int64_t N, int pairs, bool transposed_b);
 
 /* Diagnostic for the int8 GEMM's bounded waits, as feather_scaled_mm_status. No counterpart in the reference. */
 int feather_int8_mm_status(uint32_t* out);

@@ -34,7 +34,9 @@ def test_ctypes_prototypes_cover_the_header():
 
 def test_int8_plain_tile_width_fills_the_last_round(lib):
     # rounds of 74 CTA pairs x (width + 24): 4096 x 3072 in 256-wide tiles are 192 tiles = three rounds, of which the last is 60 % full
-    width = lib.feather_int8_plain_tile_width
+    def width(m, n, pairs, transposed=False):
+        return lib.feather_int8_plain_tile_width(m, n, pairs, transposed)
+
     assert width(4096, 3072, 74) == 240      # 208 tiles, three rounds of shorter tiles
     assert width(8192, 8192, 74) == 256      # 13.8 rounds: nothing to gain
     assert width(1024, 12288, 74) == 224     # 220 tiles = 2.97 rounds instead of 192 = 2.6
@@ -42,8 +44,10 @@ def test_int8_plain_tile_width_fills_the_last_round(lib):
     assert width(512, 3072, 74) == 128       # one round either way: the narrowest tile, on 48 pairs instead of 24
     assert width(65536, 12288, 74) == 256
     for m, n in ((1, 16), (300, 260), (4096, 12288), (100000, 4112)):
-        w = width(m, n, 74)
-        assert 128 <= w <= 256 and w % 16 == 0
+        assert 128 <= width(m, n, 74) <= 256 and width(m, n, 74) % 16 == 0
+        # backward: a CTA's half of the columns is the x coordinate of its weight boxes (16-byte rule), and 80 or 112 columns per CTA are slow
+        assert width(m, n, 74, True) in (128, 192, 256)
+    assert width(2048, 3072, 74, True) == 192 and width(512, 3072, 74, True) == 128 and width(4096, 3072, 74, True) == 256
     assert width(4096, 3072, 0) == 256
 
 

@@ -97,6 +97,9 @@ CHILD_INT8_PLAIN = textwrap.dedent(
         ws = torch.rand(n, device=dev, generator=gen) * 0.01
         bias = torch.randn(n, device=dev, generator=gen).to(torch.bfloat16)
         out[f"plain{m}"] = ic.int8_scaled_mm_plain(a, w, s, ws, bias, torch.bfloat16, False).cpu()
+        if n % 16 == 0:
+            g = torch.randint(-127, 128, (m, n), device=dev, generator=gen, dtype=torch.int8)
+            out[f"plain_backward{m}"] = ic.int8_scaled_mm_plain(g, w, s, None, None, torch.bfloat16, True).cpu()
     torch.cuda.synchronize()
     torch.save(out, sys.argv[1])
     """
@@ -123,10 +126,11 @@ def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
 
 
 def test_int8_tile_widths_give_the_same_bits(cuda_device, tmp_path):
-    # the forward product over the unpacked weight picks its tile width by shape; every width adds the same int32 sums
+    # the products over the unpacked weight pick their tile width by shape (backward: 128, 192 or 256 only, a forced 176 or 208 leaves it at 256);
+    # every width adds the same int32 sums
     default = _run(tmp_path, "width_default", {}, CHILD_INT8_PLAIN)
     for name, env in (("width_256", {"FEATHER_INT8_TILE_WIDTH_OFF": "1"}), ("width_176", {"FEATHER_INT8_TILE_WIDTH": "176"}),
-                      ("width_208", {"FEATHER_INT8_TILE_WIDTH": "208"})):
+                      ("width_208", {"FEATHER_INT8_TILE_WIDTH": "208"}), ("width_192", {"FEATHER_INT8_TILE_WIDTH": "192"})):
         other = _run(tmp_path, name, env, CHILD_INT8_PLAIN)
         assert set(default) == set(other)
         for key, value in default.items():
