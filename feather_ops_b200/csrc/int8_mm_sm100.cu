@@ -932,7 +932,9 @@ inline bool tile_width_off() {
 // `step`: 16 forward. Backward 64: a CTA's half of the tile's columns is the x coordinate of its weight boxes, which the copy engine wants on
 // a 16-byte boundary (so 32 at least), and an MN-major operand of 80 or 112 columns per CTA was measured a third slower than one of 96 or 128.
 inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) {
-    constexpr int kFixedColumns = 24;
+    // the part of a tile's time that does not go with its width, in columns: small forward; backward a 192-column tile was measured at 0.84 of a
+    // 256-column one (its boxes still fetch 128-byte rows)
+    const int kFixedColumns = step == 16 ? 24 : 144;
     if (tile_width_off() || pairs <= 0) return kPairN;
     // FEATHER_INT8_TILE_WIDTH=<multiple of 16 in 128..256> forces the width (measurements). Read once per process.
     static const int forced = [] {
@@ -941,18 +943,24 @@ inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) 
         return value >= kPairN / 2 && value <= kPairN && value % 16 == 0 ? value : 0;
     }();
     if (forced != 0) return forced % step == 0 ? forced : kPairN;
+    // backward with a few rows streams the weight once and is bound by that: a narrower tile's boxes still fetch 128-byte rows, so it
+    // would only fetch more (16 x 5376 x 5376: 17.6 us at 256 columns, 22.8 at 128)
+    if (step != 16 && M <= 64) return kPairN;
     const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
     int best = kPairN;
     int64_t best_cost = 0;
+    int64_t full_cost = 0;
     for (int width = kPairN; width >= kPairN / 2; width -= step) {
         const int64_t tiles = tiles_m * ((N_out + width - 1) / width);
         const int64_t cost = ((tiles + pairs - 1) / pairs) * (width + kFixedColumns);
+        if (width == kPairN) full_cost = cost;
         if (width == kPairN || cost < best_cost) {
             best = width;
             best_cost = cost;
         }
     }
-    return best;
+    // a narrower tile must promise at least 4 %: below that the model's error decides
+    return best_cost * 100 <= full_cost * 96 ? best : kPairN;
 }
 
 template <bool kTransposedB, bool kOutBf16, bool kPlainB>

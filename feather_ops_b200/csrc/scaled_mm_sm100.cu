@@ -1593,15 +1593,18 @@ inline int pair_tile_width(int64_t M, int64_t N, int pairs) {
     const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
     int best = kPairN;
     int64_t best_cost = 0;
+    int64_t full_cost = 0;
     for (int width = kPairN; width >= kPairN / 2; width -= 32) {
         const int64_t tiles = tiles_m * ((N + width - 1) / width);
         const int64_t cost = ((tiles + pairs - 1) / pairs) * (width + kPairN + 48);
+        if (width == kPairN) full_cost = cost;
         if (width == kPairN || cost < best_cost) {
             best = width;
             best_cost = cost;
         }
     }
-    return best;
+    // a narrower tile must promise at least 4 %: below that the model's error decides
+    return best_cost * 100 <= full_cost * 96 ? best : kPairN;
 }
 
 template <bool kE5M2, bool kOperandBf16, bool kOutBf16, bool kSplitK = false>

@@ -48,6 +48,8 @@ def test_int8_plain_tile_width_fills_the_last_round(lib):
         # backward: a CTA's half of the columns is the x coordinate of its weight boxes (16-byte rule), and 80 or 112 columns per CTA are slow
         assert width(m, n, 74, True) in (128, 192, 256)
     assert width(2048, 3072, 74, True) == 192 and width(512, 3072, 74, True) == 128 and width(4096, 3072, 74, True) == 256
+    assert width(4128, 3840, 74, True) == 256 and width(4096, 4096, 74, True) == 256   # five rounds of 192 columns do not beat four of 256
+    assert width(16, 5376, 74, True) == 256   # a few rows: bound by streaming the weight, and a narrower tile's boxes fetch as much
     assert width(4096, 3072, 0) == 256
 
 
