@@ -563,7 +563,10 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 banded_tile(tile, tiles_m, tiles_n, p.band, tile_m, tile_n);
                 const int m0 = tile_m * 2 * kBlockM + static_cast<int>(cta) * kBlockM;
                 const int n0 = tile_n * p.tile_n + static_cast<int>(cta) * (p.tile_n / 2);
-                const uint32_t weight_bytes = kPlainB && !kTransposedB ? static_cast<uint32_t>(p.tile_n / 2) * 128u : static_cast<uint32_t>(L::kRawBytes);
+                // what the weight boxes of a k block deliver: plain forward one box of this CTA's output channels; plain backward one
+                // full box; prepack forward one 4 KB box per 32 output channels; prepack backward four boxes of (channels / 4) rows
+                const uint32_t half_cols = static_cast<uint32_t>(p.tile_n / 2);
+                const uint32_t weight_bytes = kPlainB ? (kTransposedB ? static_cast<uint32_t>(L::kRawBytes) : half_cols * 128u) : half_cols * 128u;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = guard.wait(&load_empty[slot.idx], slot.phase ^ 1u, kSiteLoadEmpty);
                     if (!ok) break;
@@ -582,7 +585,12 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     } else {
 #pragma unroll
-                        for (int box = 0; box < 4; ++box) tma_load_2d(raw + box * kRawBoxBytes, &map_b, &load_full[slot.idx], x0 + box * 128, y0);
+                        for (int box = 0; box < 4; ++box) {
+                            // forward: box = 32 output channels (fewer boxes for a narrower tile); backward: box = 32 contraction steps
+                            if (kTransposedB || box * 32 < static_cast<int>(half_cols)) {
+                                tma_load_2d(raw + box * kRawBoxBytes, &map_b, &load_full[slot.idx], x0 + box * 128, y0);
+                            }
+                        }
                     }
                     slot.advance(kLoadStages);
                 }
@@ -782,6 +790,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int team = relayout_thread / kTeamThreads;
         const int t = relayout_thread % kTeamThreads;
         const uint32_t l = static_cast<uint32_t>(t) & 7u;
+        const uint32_t live_groups = static_cast<uint32_t>(p.tile_n / 8);   // groups of four operand rows in this CTA's half of the tile
         Ring slot, operand;
         bool ok = true;
         uint32_t turn = 0;  // k blocks since the start of the kernel, modulo the number of teams
@@ -798,6 +807,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int i = 0; i < kUnitsPerThread; ++i) {
                         const uint32_t set = static_cast<uint32_t>(t + i * kTeamThreads) >> 3;  // 0..31
                         const uint32_t group = 8u * (set & 3u) + l;
+                        if (group >= live_groups) continue;   // a narrower tile: fewer operand rows
                         const uint32_t chunk = l ^ (set >> 2);
 #pragma unroll
                         for (uint32_t j = 0; j < 4; ++j) {
@@ -816,6 +826,7 @@ int8_mm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int i = 0; i < kUnitsPerThread; ++i) {
                         const uint32_t set = static_cast<uint32_t>(t + i * kTeamThreads) >> 3;
                         const uint32_t group = 8u * (set & 3u) + l;
+                        if (group >= live_groups) continue;
                         const uint32_t chunk = l ^ (set >> 2);
                         uint32_t rows[4][4];  // rows[j][r]: contraction bytes 4 j .. 4 j + 3 of operand row 4 group + r
 #pragma unroll
@@ -931,10 +942,10 @@ inline bool tile_width_off() {
 // rounds x (width + a fixed part per tile, in columns); the widest tile wins a tie.
 // `step`: 16 forward. Backward 64: a CTA's half of the tile's columns is the x coordinate of its weight boxes, which the copy engine wants on
 // a 16-byte boundary (so 32 at least), and an MN-major operand of 80 or 112 columns per CTA was measured a third slower than one of 96 or 128.
-inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) {
+inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16, int fixed_columns = 0) {
     // the part of a tile's time that does not go with its width, in columns: small forward; backward a 192-column tile was measured at 0.84 of a
     // 256-column one (its boxes still fetch 128-byte rows)
-    const int kFixedColumns = step == 16 ? 24 : 144;
+    const int kFixedColumns = fixed_columns > 0 ? fixed_columns : (step == 16 ? 24 : 144);
     if (tile_width_off() || pairs <= 0) return kPairN;
     // FEATHER_INT8_TILE_WIDTH=<multiple of 16 in 128..256> forces the width (measurements). Read once per process.
     static const int forced = [] {
@@ -945,7 +956,7 @@ inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) 
     if (forced != 0) return forced % step == 0 ? forced : kPairN;
     // backward with a few rows streams the weight once and is bound by that: a narrower tile's boxes still fetch 128-byte rows, so it
     // would only fetch more (16 x 5376 x 5376: 17.6 us at 256 columns, 22.8 at 128)
-    if (step != 16 && M <= 64) return kPairN;
+    if (step != 16 && fixed_columns == 0 && M <= 64) return kPairN;
     const int64_t tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM);
     int best = kPairN;
     int64_t best_cost = 0;
@@ -962,6 +973,10 @@ inline int plain_tile_width(int64_t M, int64_t N_out, int pairs, int step = 16) 
     // a narrower tile must promise at least 4 %: below that the model's error decides
     return best_cost * 100 <= full_cost * 96 ? best : kPairN;
 }
+
+// The same choice for the kernel over the prepack, among 128, 192 and 256 columns (a weight box is 32 output channels forward). That kernel
+// is bound by the shared-memory traffic of a k block, a third of which (the activation tile in and out) does not go with the tile's width.
+inline int prepack_tile_width(int64_t M, int64_t N_out, int pairs) { return plain_tile_width(M, N_out, pairs, 64, 128); }
 
 template <bool kTransposedB, bool kOutBf16, bool kPlainB>
 bool launch_pair_instance(const LaunchArgs& args) {
@@ -998,7 +1013,7 @@ bool launch_pair_instance(const LaunchArgs& args) {
     if (!encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     // weight as a 2-D byte array: x runs along the micro-tile axis with stride 1 (forward: output steps,
     // backward: contraction steps), y along the other one
-    const int tile_n = kPlainB ? plain_tile_width(args.M, args.N_out, pairs, kTransposedB ? 64 : 16) : kPairN;
+    const int tile_n = kPlainB ? plain_tile_width(args.M, args.N_out, pairs, kTransposedB ? 64 : 16) : prepack_tile_width(args.M, args.N_out, pairs);
     CUtensorMap map_b;
     if constexpr (kPlainB) {
         // the row-major weight: x = column (the layer's input axis), y = row (its output axis)
@@ -1014,7 +1029,9 @@ bool launch_pair_instance(const LaunchArgs& args) {
         const uint64_t slow_stride = static_cast<uint64_t>(kTransposedB ? args.stride_out : args.stride_kc);
         const uint64_t b_dims[2] = {fast_tiles * 16, slow_tiles};
         const uint64_t b_strides[1] = {slow_stride * 16};
-        const uint32_t b_box[2] = {128, 32};
+        // forward: 32 contraction steps of 32 output channels (one box per 32 channels of the CTA's half); backward: 32 contraction steps
+        // (128 bytes) of all the CTA's output steps
+        const uint32_t b_box[2] = {128, kTransposedB ? static_cast<uint32_t>(tile_n / 8) : 32u};
         if (!encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, args.b, b_dims, b_strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     }
 

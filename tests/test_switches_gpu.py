@@ -5,7 +5,8 @@ computes the same calls with the defaults and compares. Covered: the direct outp
 sends the output through bulk tensor stores), the K split through scratch and tickets (the default exchanges the partials inside a
 cluster where every cluster of the launch fits the device) and the conv kernels that gather from global memory (the default stages
 halo tiles through the copy engine) and the int8 GEMM over an unpacked weight (the default reads the row-major weight through the copy
-engine, the switch permutes it per call and runs the re-layout kernel).
+engine, the switch permutes it per call and runs the re-layout kernel) and the pair kernels' tile width (the default picks it by shape, the
+switches keep 256 columns).
 """
 
 import os
@@ -118,7 +119,8 @@ def _run(tmp_path, name, env, child=CHILD):
 def test_switched_paths_give_the_same_bits(cuda_device, tmp_path):
     default = _run(tmp_path, "default", {})
     switched = _run(tmp_path, "switched", {"FEATHER_SCALED_MM_BULK_OUT_OFF": "1", "FEATHER_INT8_BULK_OUT_OFF": "1", "FEATHER_CONV_STAGING_OFF": "1",
-                                           "FEATHER_INT8_PDL_OFF": "1", "FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF": "1", "FEATHER_INT8_PLAIN_OFF": "1"})
+                                           "FEATHER_INT8_PDL_OFF": "1", "FEATHER_SCALED_MM_CLUSTER_REDUCE_OFF": "1", "FEATHER_INT8_PLAIN_OFF": "1",
+                                           "FEATHER_INT8_TILE_WIDTH_OFF": "1", "FEATHER_SCALED_MM_TILE_WIDTH_OFF": "1"})
     assert torch.equal(default["i8f"], default["i8f_plain"]) and torch.equal(default["i8b"], default["i8b_plain"])
     assert set(default) == set(switched)
     for key, value in default.items():
