@@ -158,7 +158,12 @@ def _scaled_mm_path(m, n, k):
     if m <= 128:
         return f"skinny tcgen05 kernel, {smm.select_scaled_mm_splits(m, n, k)} K splits"
     width = 16 * smm.select_scaled_mm_config(m, n, k)[1] * smm.select_scaled_mm_config(m, n, k)[4]
-    return "CTA-pair kernel, 256x256 tiles" if width >= 256 else f"one-CTA kernel, 128x{width} tiles"
+    if width >= 256:
+        from . import _lib
+
+        columns = _lib.load().feather_scaled_mm_pair_tile_width(m, n, smm.sm_count() // 2)   # the launcher narrows the tile where that fills a round
+        return f"CTA-pair kernel, 256x{columns} tiles"
+    return f"one-CTA kernel, 128x{width} tiles"
 
 
 def scaled_mm_case(key, m, n, k, a_dtype, out_dtype, cold, device, peaks, bound=None) -> dict:
